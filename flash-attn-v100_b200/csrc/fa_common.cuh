@@ -1,0 +1,64 @@
+// Shared declarations of the library's translation units: the C-ABI header,
+// error plumbing, and the per-family launch entry points host_api.cu routes to.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include "../../include/fa_b200.h"
+#include "philox.cuh"
+
+namespace fa {
+
+// Thread-local detail string behind fa_b200_last_error().
+void set_error(const char* fmt, ...);
+
+#define FA_CUDA_CHECK(expr)                                                        \
+    do {                                                                           \
+        cudaError_t _e = (expr);                                                   \
+        if (_e != cudaSuccess) {                                                   \
+            fa::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),  \
+                          __FILE__, __LINE__);                                     \
+            return FA_ECUDA;                                                       \
+        }                                                                          \
+    } while (0)
+
+// ---- dtype helpers ---------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T x);
+template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+static inline size_t dtype_bytes(int dtype) { return dtype == FA_B200_F32 ? 4 : 2; }
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---- workspace layout (backward) -------------------------------------------
+// [ delta : B*H*Nq fp32 | pad to 256 | dq_accum : B*Nq*H*D fp32 (tcgen05 only) ]
+struct BwdWorkspace {
+    size_t delta_off, delta_bytes;
+    size_t dq_accum_off, dq_accum_bytes;
+    size_t total;
+};
+BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant);
+
+// ---- kernel families ---------------------------------------------------------
+// CUDA-core tiles (simt_kernels.cu)
+int simt_fwd(const fa_b200_params& p);
+int simt_bwd(const fa_b200_params& p, const BwdWorkspace& ws);
+bool simt_supports(const fa_b200_params& p);
+
+// TMA + tcgen05 (fwd_sm100.cu, bwd_sm100.cu)
+int sm100_fwd(const fa_b200_params& p);
+int sm100_bwd(const fa_b200_params& p, const BwdWorkspace& ws);
+bool sm100_supports(const fa_b200_params& p, bool backward, const char** why);
+
+int launch_dropout_mask(uint64_t seed, uint64_t offset, float p, int B, int H, int Nq, int Nk,
+                        uint8_t* out, cudaStream_t stream);
+
+}  // namespace fa

@@ -1,0 +1,275 @@
+// C-ABI layer of libfa_b200.so: argument validation, kernel-family choice,
+// workspace layout, the static tile table, error strings and the host side of
+// the dropout stream.  Everything here is O(1) host work per call: no tensor
+// scans and no device synchronisation (the reference's launchers do both:
+// utils.py:227-254, kernels/forward_kernel.py:308-313).
+#include "fa_common.cuh"
+#include <stdarg.h>
+#include <string.h>
+
+namespace fa {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant) {
+    BwdWorkspace w;
+    w.delta_off = 0;
+    w.delta_bytes = (size_t)p.B * p.H * p.Nq * sizeof(float);
+    w.dq_accum_off = align_up(w.delta_bytes, 256);
+    w.dq_accum_bytes = 0;
+    if (variant == FA_B200_VARIANT_TCGEN05) {
+        // fp32 dQ accumulator, rows padded to whole 128-row tiles per (b, h)
+        size_t nq_pad = align_up((size_t)p.Nq, 128);
+        w.dq_accum_bytes = (size_t)p.B * p.H * nq_pad * p.D * sizeof(float);
+    }
+    w.total = w.dq_accum_off + w.dq_accum_bytes;
+    if (w.total == 0) w.total = 256;
+    return w;
+}
+
+namespace {
+
+struct GuardDevice {
+    int prev = -1;
+    bool ok = true;
+    explicit GuardDevice(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    }
+    ~GuardDevice() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+int check_tensor(const fa_b200_tensor& t, const char* name, bool required) {
+    if (!t.ptr) {
+        if (required) { set_error("%s pointer is null", name); return FA_EINVAL; }
+        return FA_OK;
+    }
+    return FA_OK;
+}
+
+int validate_common(const fa_b200_params* p, bool backward) {
+    if (!p) { set_error("params is null"); return FA_EINVAL; }
+    if (p->struct_bytes != sizeof(fa_b200_params)) {
+        set_error("struct_bytes %zu does not match this library's fa_b200_params (%zu bytes)",
+                  p->struct_bytes, sizeof(fa_b200_params));
+        return FA_EINVAL;
+    }
+    if (p->B < 0 || p->Nq < 0 || p->Nk < 0 || p->H <= 0 || p->Hkv <= 0 || p->D <= 0) {
+        set_error("sizes must be non-negative and H, Hkv, D positive (B=%d Nq=%d Nk=%d H=%d Hkv=%d D=%d)",
+                  p->B, p->Nq, p->Nk, p->H, p->Hkv, p->D);
+        return FA_EINVAL;
+    }
+    if (p->H % p->Hkv != 0) {
+        set_error("H (%d) must be a multiple of Hkv (%d)", p->H, p->Hkv);
+        return FA_EINVAL;
+    }
+    if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_F32) {
+        set_error("unknown dtype %d", p->dtype);
+        return FA_EINVAL;
+    }
+    if (p->variant < FA_B200_VARIANT_AUTO || p->variant > FA_B200_VARIANT_TCGEN05) {
+        set_error("unknown variant %d", p->variant);
+        return FA_EINVAL;
+    }
+    if (!(p->dropout_p >= 0.f && p->dropout_p < 1.f)) {
+        set_error("dropout_p must be in [0, 1), got %g", (double)p->dropout_p);
+        return FA_EINVAL;
+    }
+    if (!(p->scale == p->scale)) { set_error("scale is NaN"); return FA_EINVAL; }
+    if (p->B == 0 || p->Nq == 0) return FA_OK;   // empty problem: nothing else to check
+    int rc;
+    if ((rc = check_tensor(p->q, "q", true))) return rc;
+    if ((rc = check_tensor(p->o, "o", true))) return rc;
+    if (p->Nk > 0) {
+        if ((rc = check_tensor(p->k, "k", true))) return rc;
+        if ((rc = check_tensor(p->v, "v", true))) return rc;
+    }
+    if (!p->lse) { set_error("lse pointer is null"); return FA_EINVAL; }
+    if (backward) {
+        if ((rc = check_tensor(p->d_o, "d_o", true))) return rc;
+        if ((rc = check_tensor(p->dq, "dq", true))) return rc;
+        if (p->Nk > 0) {
+            if ((rc = check_tensor(p->dk, "dk", true))) return rc;
+            if ((rc = check_tensor(p->dv, "dv", true))) return rc;
+        }
+    }
+    return FA_OK;
+}
+
+// Kernel family for a call: an explicit request is honoured or refused, AUTO
+// prefers the tensor-core family and falls back to CUDA-core tiles for shapes
+// it does not cover.
+int choose_variant(const fa_b200_params& p, bool backward, int* variant) {
+    const char* why = "";
+    bool tc = sm100_supports(p, backward, &why);
+    if (p.variant == FA_B200_VARIANT_TCGEN05) {
+        if (!tc) { set_error("tcgen05 kernels do not cover this call: %s", why); return FA_EUNSUPPORTED; }
+        *variant = FA_B200_VARIANT_TCGEN05;
+        return FA_OK;
+    }
+    if (p.variant == FA_B200_VARIANT_AUTO && tc) { *variant = FA_B200_VARIANT_TCGEN05; return FA_OK; }
+    if (!simt_supports(p)) {
+        set_error("no kernel covers D=%d (CUDA-core tiles need D <= 128; tensor-core tiles: %s)", p.D, why);
+        return FA_EUNSUPPORTED;
+    }
+    *variant = FA_B200_VARIANT_SIMT;
+    return FA_OK;
+}
+
+}  // namespace
+}  // namespace fa
+
+using namespace fa;
+
+extern "C" {
+
+int fa_b200_version(void) { return FA_B200_ABI_VERSION; }
+
+const char* fa_b200_last_error(void) { return g_err; }
+
+const char* fa_b200_strerror(int status) {
+    switch (status) {
+        case FA_OK:           return "ok";
+        case FA_EINVAL:       return "invalid argument";
+        case FA_EUNSUPPORTED: return "unsupported shape or dtype";
+        case FA_EALIGN:       return "pointer or stride not aligned as the kernel requires";
+        case FA_EWORKSPACE:   return "workspace missing or too small";
+        case FA_ECUDA:        return "CUDA call failed";
+        case FA_ETIMEOUT:     return "bounded device-side wait ran out";
+        default:              return "unknown status";
+    }
+}
+
+int fa_b200_fwd(const fa_b200_params* p) {
+    int rc = validate_common(p, false);
+    if (rc) return rc;
+    if (p->B == 0 || p->Nq == 0) return FA_OK;
+    if (p->Nk == 0) { set_error("Nk = 0: softmax over an empty key set is undefined"); return FA_EINVAL; }
+    int variant;
+    if ((rc = choose_variant(*p, false, &variant))) return rc;
+    GuardDevice g(p->device);
+    if (!g.ok) { set_error("cudaSetDevice(%d) failed", p->device); return FA_ECUDA; }
+    return variant == FA_B200_VARIANT_TCGEN05 ? sm100_fwd(*p) : simt_fwd(*p);
+}
+
+size_t fa_b200_bwd_workspace_bytes(const fa_b200_params* p) {
+    if (!p || p->struct_bytes != sizeof(fa_b200_params)) return 0;
+    if (p->B <= 0 || p->Nq <= 0 || p->H <= 0 || p->Hkv <= 0 || p->D <= 0) return 256;
+    int variant = FA_B200_VARIANT_SIMT;
+    fa_b200_params q = *p;
+    // Size for the largest family the call could be routed to, so that the
+    // answer does not depend on pointer alignment (pointers may be null here).
+    const char* why = "";
+    q.variant = FA_B200_VARIANT_AUTO;
+    if (sm100_supports(q, true, &why)) variant = FA_B200_VARIANT_TCGEN05;
+    return bwd_workspace_layout(*p, variant).total;
+}
+
+int fa_b200_bwd(const fa_b200_params* p) {
+    int rc = validate_common(p, true);
+    if (rc) return rc;
+    if (p->B == 0 || (p->Nq == 0 && p->Nk == 0)) return FA_OK;
+    if (p->Nk == 0) { set_error("Nk = 0: softmax over an empty key set is undefined"); return FA_EINVAL; }
+    int variant;
+    if ((rc = choose_variant(*p, true, &variant))) return rc;
+    BwdWorkspace ws = bwd_workspace_layout(*p, variant);
+    if (!p->workspace || p->workspace_bytes < ws.total) {
+        set_error("backward needs %zu bytes of workspace, got %zu", ws.total,
+                  p->workspace ? p->workspace_bytes : (size_t)0);
+        return FA_EWORKSPACE;
+    }
+    if (((uintptr_t)p->workspace & 255u) != 0) {
+        set_error("workspace must be 256-byte aligned");
+        return FA_EALIGN;
+    }
+    GuardDevice g(p->device);
+    if (!g.ok) { set_error("cudaSetDevice(%d) failed", p->device); return FA_ECUDA; }
+    if (p->Nq == 0) {
+        // no queries: dK = dV = 0
+        size_t eb = dtype_bytes(p->dtype);
+        for (int b = 0; b < p->B; ++b)
+            for (int j = 0; j < p->Nk; ++j) {
+                FA_CUDA_CHECK(cudaMemset2DAsync((char*)p->dk.ptr + ((int64_t)b * p->dk.stride_b + (int64_t)j * p->dk.stride_n) * eb,
+                                                p->dk.stride_h * eb, 0, p->D * eb, p->Hkv, (cudaStream_t)p->stream));
+                FA_CUDA_CHECK(cudaMemset2DAsync((char*)p->dv.ptr + ((int64_t)b * p->dv.stride_b + (int64_t)j * p->dv.stride_n) * eb,
+                                                p->dv.stride_h * eb, 0, p->D * eb, p->Hkv, (cudaStream_t)p->stream));
+            }
+        return FA_OK;
+    }
+    return variant == FA_B200_VARIANT_TCGEN05 ? sm100_bwd(*p, ws) : simt_bwd(*p, ws);
+}
+
+// Static tile table.  Tensor-core rows hold the tile shapes the sm_100a
+// kernels are compiled for; everything else is served by 64x64 CUDA-core tiles.
+int fa_b200_tile_config(int D, int dtype, int causal, int backward, fa_b200_tile* out) {
+    if (!out) { set_error("out is null"); return FA_EINVAL; }
+    if (D <= 0 || D > 128) { set_error("no tile for D=%d", D); return FA_EUNSUPPORTED; }
+    (void)causal;
+    bool tc = (dtype == FA_B200_F16 || dtype == FA_B200_BF16) && (D == 64 || D == 128);
+    if (tc) {
+        out->variant = FA_B200_VARIANT_TCGEN05;
+        out->block_m = 128;
+        out->block_n = 128;
+        out->q_tiles_per_cta = backward ? 1 : 2;
+        out->kv_stages = backward ? 1 : (D == 64 ? 3 : 2);
+        out->num_warps = backward ? 10 : 10;
+    } else {
+        out->variant = FA_B200_VARIANT_SIMT;
+        out->block_m = 64;
+        out->block_n = 64;
+        out->q_tiles_per_cta = 1;
+        out->kv_stages = 1;
+        out->num_warps = 8;
+    }
+    return FA_OK;
+}
+
+void fa_b200_philox4x32_10(const uint32_t counter[4], const uint32_t key[2], uint32_t out[4]) {
+    philox4x32_10(counter[0], counter[1], counter[2], counter[3], key[0], key[1], out);
+}
+
+float fa_b200_dropout_effective_p(float dropout_p) { return dropout_effective_p(dropout_p); }
+
+int fa_b200_dropout_mask_host(uint64_t seed, uint64_t offset, float dropout_p,
+                              int B, int H, int Nq, int Nk, uint8_t* out) {
+    if (B < 0 || H < 0 || Nq < 0 || Nk < 0) { set_error("negative size"); return FA_EINVAL; }
+    if ((int64_t)B * H * Nq * Nk == 0) return FA_OK;
+    if (!out) { set_error("out is null"); return FA_EINVAL; }
+    if (!(dropout_p >= 0.f && dropout_p < 1.f)) { set_error("dropout_p must be in [0, 1)"); return FA_EINVAL; }
+    PhiloxKey key = philox_make_key(seed, offset);
+    uint32_t thr = dropout_threshold(dropout_p);
+    int jb_per_row = (Nk + 15) / 16;
+    for (int64_t rowid = 0; rowid < (int64_t)B * H * Nq; ++rowid) {
+        uint32_t bh = (uint32_t)(rowid / Nq), i = (uint32_t)(rowid % Nq);
+        uint8_t* dst = out + rowid * Nk;
+        for (int jb = 0; jb < jb_per_row; ++jb) {
+            uint32_t bits = thr ? dropout_keep_bits(key, bh, i, (uint32_t)jb, thr) : 0xFFFFu;
+            for (int c = 0; c < 16 && jb * 16 + c < Nk; ++c) dst[jb * 16 + c] = (bits >> c) & 1u;
+        }
+    }
+    return FA_OK;
+}
+
+int fa_b200_dropout_mask_device(uint64_t seed, uint64_t offset, float dropout_p,
+                                int B, int H, int Nq, int Nk, uint8_t* out_dev,
+                                int device, void* stream) {
+    if (B < 0 || H < 0 || Nq < 0 || Nk < 0) { set_error("negative size"); return FA_EINVAL; }
+    if ((int64_t)B * H * Nq * Nk == 0) return FA_OK;
+    if (!out_dev) { set_error("out_dev is null"); return FA_EINVAL; }
+    if (!(dropout_p >= 0.f && dropout_p < 1.f)) { set_error("dropout_p must be in [0, 1)"); return FA_EINVAL; }
+    GuardDevice g(device);
+    if (!g.ok) { set_error("cudaSetDevice(%d) failed", device); return FA_ECUDA; }
+    return launch_dropout_mask(seed, offset, dropout_p, B, H, Nq, Nk, out_dev, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,252 @@
+"""Autograd binding of the attention kernels.
+
+Keeps the contract of the reference's EnhancedFlashAttentionV100Function
+(ops/attention.py:36-333): the same 19 positional parameters of forward
+(:50-72), a Tensor or (Tensor, Tensor) result (:229-232), and a backward that
+returns one gradient slot per forward input (:313-333).  The Triton launches
+inside are replaced by calls into libfa_b200.so.
+"""
+from __future__ import annotations
+
+import contextlib
+import ctypes
+import threading
+from typing import Any, Dict, Optional, Tuple, Union
+
+import torch
+
+from ..kernels import _cabi
+from ..kernels.tile_table import dtype_enum
+from ..utils import validate_inputs, _last_dim_contiguous
+
+# --------------------------------------------------------------------------
+# dropout stream state: (seed, offset) are host integers, never read back from
+# the device (the reference draws them with two .item() syncs per call,
+# kernels/forward_kernel.py:308-313, and does not keep them for backward).
+# --------------------------------------------------------------------------
+_rng_lock = threading.Lock()
+_rng_state = {"seed": None, "offset": 0}
+
+
+def set_dropout_seed(seed: int, offset: int = 0) -> None:
+    """Fix the Philox key and the next call's counter word."""
+    with _rng_lock:
+        _rng_state["seed"] = int(seed) & 0xFFFFFFFFFFFFFFFF
+        _rng_state["offset"] = int(offset) & 0xFFFFFFFFFFFFFFFF
+
+
+def _next_dropout_stream() -> Tuple[int, int]:
+    with _rng_lock:
+        if _rng_state["seed"] is None:
+            _rng_state["seed"] = torch.initial_seed() & 0xFFFFFFFFFFFFFFFF
+        seed, offset = _rng_state["seed"], _rng_state["offset"]
+        _rng_state["offset"] = (offset + 1) & 0xFFFFFFFFFFFFFFFF
+    return seed, offset
+
+
+_variant_override = threading.local()
+
+
+@contextlib.contextmanager
+def kernel_variant(name: str):
+    """Force a kernel family ('auto', 'simt', 'tcgen05') inside the block."""
+    table = {"auto": _cabi.VARIANT_AUTO, "simt": _cabi.VARIANT_SIMT, "tcgen05": _cabi.VARIANT_TCGEN05}
+    old = getattr(_variant_override, "value", _cabi.VARIANT_AUTO)
+    _variant_override.value = table[name]
+    try:
+        yield
+    finally:
+        _variant_override.value = old
+
+
+def _tensor4(t: Optional[torch.Tensor]) -> _cabi.Tensor4:
+    r = _cabi.Tensor4()
+    if t is None or t.numel() == 0:
+        r.ptr = None if t is None else (t.data_ptr() or None)
+        if t is not None:
+            r.stride_b, r.stride_n, r.stride_h = t.stride(0), t.stride(1), t.stride(2)
+        return r
+    assert t.stride(3) == 1
+    r.ptr = t.data_ptr()
+    r.stride_b, r.stride_n, r.stride_h = t.stride(0), t.stride(1), t.stride(2)
+    return r
+
+
+def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset) -> _cabi.Params:
+    p = _cabi.Params()
+    p.struct_bytes = ctypes.sizeof(_cabi.Params)
+    p.q, p.k, p.v, p.o = _tensor4(q), _tensor4(k), _tensor4(v), _tensor4(o)
+    p.lse = lse.data_ptr() or None
+    p.B, p.Nq, p.H, p.D = q.shape
+    p.Nk, p.Hkv = k.shape[1], k.shape[2]
+    p.dtype = dtype_enum(q.dtype)
+    p.causal = int(bool(causal))
+    p.variant = getattr(_variant_override, "value", _cabi.VARIANT_AUTO)
+    p.device = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    p.scale = float(scale)
+    p.dropout_p = float(dropout_p)
+    p.seed, p.offset = int(seed), int(offset)
+    p.stream = torch.cuda.current_stream(q.device).cuda_stream or None
+    return p
+
+
+def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0):
+    """o, lse <- fa_b200_fwd.  Counterpart of flash_attention_forward_triton_enhanced
+    (kernels/forward_kernel.py:246-387); returns (o, lse)."""
+    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
+    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset)
+    rc = _cabi.load().fa_b200_fwd(ctypes.byref(p))
+    _cabi.raise_for_status(rc, "fa_b200_fwd")
+    return o, lse
+
+
+def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, offset=0):
+    """dq, dk, dv <- fa_b200_bwd.  Counterpart of
+    flash_attention_backward_triton_enhanced (kernels/backward_kernel.py:208-318)."""
+    d_o = _last_dim_contiguous(d_o)
+    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset)
+    p.d_o, p.dq, p.dk, p.dv = _tensor4(d_o), _tensor4(dq), _tensor4(dk), _tensor4(dv)
+    lib = _cabi.load()
+    nbytes = int(lib.fa_b200_bwd_workspace_bytes(ctypes.byref(p)))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), nbytes
+    rc = lib.fa_b200_bwd(ctypes.byref(p))
+    _cabi.raise_for_status(rc, "fa_b200_bwd")
+    return dq, dk, dv
+
+
+class EnhancedFlashAttentionV100Function(torch.autograd.Function):
+    """Attention as an autograd op; parameter list of reference ops/attention.py:50-72."""
+
+    @staticmethod
+    def forward(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                causal: bool = False, dropout_p: float = 0.0, bias: Optional[torch.Tensor] = None,
+                block_size_m: Optional[int] = None, block_size_n: Optional[int] = None,
+                enable_autotuning: bool = True, return_softmax_lse: bool = False,
+                enable_gradient_checkpointing: bool = False, enable_mixed_precision: bool = True,
+                num_checkpoints: Optional[int] = None, memory_efficient: bool = True,
+                performance_mode: str = "balanced", enable_multi_gpu: bool = False,
+                world_size: int = 1, rank: int = 0
+                ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
+        # block sizes, autotuning, checkpointing, mixed precision and the
+        # multi-GPU arguments are accepted for source compatibility: tiles come
+        # from the static table, the backward always recomputes P, and sharding
+        # over GPUs happens above this op (interface.py).
+        q, k, v, scale = validate_inputs(q, k, v, scale, bias, dropout_p)
+        seed = offset = 0
+        if dropout_p > 0.0:
+            seed, offset = _next_dropout_stream()
+        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.scale, ctx.causal, ctx.dropout_p = scale, bool(causal), float(dropout_p)
+        ctx.seed, ctx.offset = seed, offset
+        ctx.return_softmax_lse = bool(return_softmax_lse)
+        if return_softmax_lse:
+            ctx.mark_non_differentiable(lse)
+            return o, lse
+        return o
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor, grad_softmax_lse: Optional[torch.Tensor] = None):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = launch_backward(grad_output, q, k, v, o, lse, ctx.scale, ctx.causal,
+                                     ctx.dropout_p, ctx.seed, ctx.offset)
+        return (dq if ctx.needs_input_grad[0] else None,
+                dk if ctx.needs_input_grad[1] else None,
+                dv if ctx.needs_input_grad[2] else None) + (None,) * 16
+
+
+def flash_attention_forward_enhanced(q, k, v, scale: Optional[float] = None, causal: bool = False,
+                                     dropout_p: float = 0.0, bias: Optional[torch.Tensor] = None,
+                                     enable_multi_gpu: bool = False, performance_mode: str = "balanced",
+                                     **kwargs) -> torch.Tensor:
+    """No-grad forward (reference ops/attention.py:464-533).  With
+    return_softmax_lse=True in kwargs returns (o, lse)."""
+    q, k, v, scale = validate_inputs(q, k, v, scale, bias, dropout_p)
+    seed = offset = 0
+    if dropout_p > 0.0:
+        seed, offset = kwargs.get("dropout_stream") or _next_dropout_stream()
+    with torch.no_grad():
+        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset)
+    return (o, lse) if kwargs.get("return_softmax_lse", False) else o
+
+
+def flash_attention_backward_enhanced(grad_output, q, k, v, output, lse, max_vals=None,
+                                      scale: Optional[float] = None, causal: bool = False,
+                                      enable_multi_gpu: bool = False, **kwargs
+                                      ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Explicit backward (reference ops/attention.py:536-600).  `max_vals` is
+    accepted and ignored: the kernels recompute P from the log-sum-exp alone.
+    kwargs: dropout_p and dropout_stream=(seed, offset) to replay a mask."""
+    q, k, v, scale = validate_inputs(q, k, v, scale, None, kwargs.get("dropout_p", 0.0))
+    seed, offset = kwargs.get("dropout_stream", (0, 0))
+    with torch.no_grad():
+        return launch_backward(grad_output, q, k, v, _last_dim_contiguous(output), lse.contiguous(),
+                               scale, causal, kwargs.get("dropout_p", 0.0), seed, offset)
+
+
+def compare_with_pytorch_attention_enhanced(q, k, v, causal: bool = False,
+                                            bias: Optional[torch.Tensor] = None, dropout_p: float = 0.0,
+                                            atol: float = 1e-4, rtol: float = 1e-4) -> Dict[str, Any]:
+    """Compare the kernels with PyTorch's scaled_dot_product_attention on the
+    GPU; same result keys as the reference (ops/attention.py:603-717)."""
+    if dropout_p != 0.0:
+        raise ValueError("comparison is only defined without dropout (different random streams)")
+    import torch.nn.functional as F
+    scale = q.shape[-1] ** -0.5
+    flash = flash_attention_forward_enhanced(q, k, v, scale, causal, 0.0, bias)
+    ref = F.scaled_dot_product_attention(q.transpose(1, 2).float(), k.transpose(1, 2).float(),
+                                         v.transpose(1, 2).float(), is_causal=causal,
+                                         scale=scale).transpose(1, 2)
+    diff = (flash.float() - ref).abs()
+    denom = ref.abs().clamp_min(1e-6)
+    cos = F.cosine_similarity(flash.float().flatten(), ref.flatten(), dim=0).item()
+    stats = lambda t: {"mean": t.float().mean().item(), "std": t.float().std().item(),
+                       "min": t.float().min().item(), "max": t.float().max().item()}
+    return {
+        "allclose": bool(torch.allclose(flash.float(), ref, atol=atol, rtol=rtol)),
+        "max_absolute_difference": diff.max().item(),
+        "mean_absolute_difference": diff.mean().item(),
+        "max_relative_difference": (diff / denom).max().item(),
+        "mean_relative_difference": (diff / denom).mean().item(),
+        "cosine_similarity": cos, "atol": atol, "rtol": rtol,
+        "flash_output_stats": stats(flash), "reference_output_stats": stats(ref),
+        "input_shape": q.shape,
+        "configuration": {"causal": causal, "dropout_p": dropout_p, "has_bias": bias is not None,
+                          "dtype": str(q.dtype), "device": str(q.device)},
+    }
+
+
+@contextlib.contextmanager
+def gradient_checkpointing_mode(enable: bool = True):
+    """Placeholder kept from the reference (ops/attention.py:721-726): the
+    backward already recomputes the probabilities, nothing is checkpointed."""
+    yield
+
+
+@contextlib.contextmanager
+def mixed_precision_mode(enable: bool = True):
+    """Reference ops/attention.py:729-736: run the block under autocast."""
+    if enable and torch.cuda.is_available():
+        with torch.autocast("cuda"):
+            yield
+    else:
+        yield
+
+
+FlashAttentionV100Function = EnhancedFlashAttentionV100Function
+flash_attention_forward = flash_attention_forward_enhanced
+flash_attention_backward = flash_attention_backward_enhanced
+compare_with_pytorch_attention = compare_with_pytorch_attention_enhanced
+
+__all__ = [
+    "EnhancedFlashAttentionV100Function", "flash_attention_forward_enhanced",
+    "flash_attention_backward_enhanced", "compare_with_pytorch_attention_enhanced",
+    "gradient_checkpointing_mode", "mixed_precision_mode", "FlashAttentionV100Function",
+    "flash_attention_forward", "flash_attention_backward", "compare_with_pytorch_attention",
+    "set_dropout_seed", "kernel_variant", "launch_forward", "launch_backward",
+]

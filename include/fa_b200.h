@@ -1,0 +1,160 @@
+/*
+ * fa_b200.h — C ABI of libfa_b200.so: exact attention forward/backward for
+ * NVIDIA B200 (sm_100a).
+ *
+ * The reference project (mini-kio/flash-attn-v100) is pure Python and has no
+ * FFI of its own: its host code launches two Triton kernels directly
+ *   kernels/forward_kernel.py:246-387   flash_attention_forward_triton_enhanced
+ *   kernels/backward_kernel.py:208-318  flash_attention_backward_triton_enhanced
+ * passing raw pointers, the six sizes and per-tensor (batch, head, seq, dim)
+ * strides (kernels/forward_kernel.py:349-385).  The entry points below are the
+ * C-ABI counterpart of those two launchers plus the small amount of state the
+ * launchers derive on the host (tile choice, workspace size, dropout stream).
+ *
+ * Conventions
+ *  - Tensors q, k, v, o, dO, dQ, dK, dV use the reference's (B, N, H, D)
+ *    layout (interface.py:228-230).  The D axis must be contiguous; the batch,
+ *    sequence and head strides are given in ELEMENTS, so head- or batch-sliced
+ *    views are consumed in place.
+ *  - lse is (B, H, Nq) float32, contiguous, natural-log log-sum-exp of the
+ *    scaled, masked scores (the reference's return_softmax_lse output,
+ *    ops/attention.py:229-230).
+ *  - Every pointer is a device pointer on `device`, borrowed for the duration
+ *    of the enqueued work.  The library allocates no device memory; scratch is
+ *    passed in through `workspace`.
+ *  - Work is enqueued on `stream` (a cudaStream_t); no call synchronises.
+ *  - Functions return FA_OK or a negative fa_b200_status; they never throw or
+ *    abort.  fa_b200_strerror() describes a code, fa_b200_last_error() the
+ *    detail of the last failure on the calling thread.
+ */
+#ifndef FA_B200_H
+#define FA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_B200_ABI_VERSION 1
+
+typedef enum fa_b200_dtype {
+    FA_B200_F16  = 0,
+    FA_B200_BF16 = 1,
+    FA_B200_F32  = 2
+} fa_b200_dtype;
+
+typedef enum fa_b200_status {
+    FA_OK           =  0,
+    FA_EINVAL       = -1,  /* null pointer, bad size, bad enum, bad struct_bytes   */
+    FA_EUNSUPPORTED = -2,  /* shape/dtype combination no kernel covers             */
+    FA_EALIGN       = -3,  /* pointer or stride alignment the chosen kernel needs  */
+    FA_EWORKSPACE   = -4,  /* workspace missing or too small                       */
+    FA_ECUDA        = -5,  /* a CUDA runtime/driver call failed                    */
+    FA_ETIMEOUT     = -6   /* a bounded device-side wait ran out (status word)     */
+} fa_b200_status;
+
+/* Which kernel family serves the call.  AUTO picks from the static tile table. */
+typedef enum fa_b200_variant {
+    FA_B200_VARIANT_AUTO    = 0,
+    FA_B200_VARIANT_SIMT    = 1,  /* CUDA-core tiles: any D <= 128, all dtypes, fp32 exact */
+    FA_B200_VARIANT_TCGEN05 = 2   /* TMA + tcgen05/TMEM: fp16/bf16, D in {64, 128}         */
+} fa_b200_variant;
+
+/* One (B, N, H, D) tensor: base pointer and element strides (D stride is 1). */
+typedef struct fa_b200_tensor {
+    void*   ptr;
+    int64_t stride_b;
+    int64_t stride_n;
+    int64_t stride_h;
+} fa_b200_tensor;
+
+/*
+ * Argument block shared by forward and backward.  Replaces the positional
+ * argument list of the reference launchers (kernels/forward_kernel.py:349-385,
+ * kernels/backward_kernel.py:279-316).
+ */
+typedef struct fa_b200_params {
+    size_t         struct_bytes;   /* = sizeof(fa_b200_params); checked            */
+    fa_b200_tensor q, k, v;        /* inputs                                       */
+    fa_b200_tensor o;              /* forward: output; backward: input             */
+    fa_b200_tensor d_o;            /* backward input  (grad of o)                  */
+    fa_b200_tensor dq, dk, dv;     /* backward outputs                             */
+    float*         lse;            /* (B, H, Nq) fp32; fwd output / bwd input      */
+    void*          workspace;      /* backward scratch, >= fa_b200_bwd_workspace_bytes */
+    size_t         workspace_bytes;
+    int32_t*       status_word;    /* optional device int32, set non-zero when a
+                                      bounded device-side wait gives up            */
+    void*          stream;         /* cudaStream_t                                 */
+    uint64_t       seed, offset;   /* dropout stream (Philox key / counter word)   */
+    int32_t        B, Nq, Nk, H, Hkv, D;
+    int32_t        dtype;          /* fa_b200_dtype                                */
+    int32_t        causal;         /* key j visible to query i iff j <= i          */
+    int32_t        variant;        /* fa_b200_variant                              */
+    int32_t        device;         /* CUDA ordinal the pointers live on            */
+    float          scale;          /* scores = scale * q.k                         */
+    float          dropout_p;      /* [0, 1)                                       */
+} fa_b200_params;
+
+/* Static tile choice for a (D, dtype, causal) key; replaces the reference's
+ * run-time tuner (kernels/autotuning.py:841-952, config.py:288-348). */
+typedef struct fa_b200_tile {
+    int32_t variant;        /* fa_b200_variant actually used                  */
+    int32_t block_m;        /* query rows per tile                            */
+    int32_t block_n;        /* key rows per tile                              */
+    int32_t q_tiles_per_cta;
+    int32_t kv_stages;      /* shared-memory ring depth for K/V tiles         */
+    int32_t num_warps;
+} fa_b200_tile;
+
+/* Forward: o, lse <- attention(q, k, v).  Replaces
+ * kernels/forward_kernel.py:246-387 (launcher) and :18-243 (kernel). */
+int fa_b200_fwd(const fa_b200_params* p);
+
+/* Backward: dq, dk, dv <- grad(q, k, v, o, lse, dO).  Replaces
+ * kernels/backward_kernel.py:208-318 (launcher) and :17-205 (kernel).
+ * dq is reduced in a fixed order: two runs give bit-identical results. */
+int fa_b200_bwd(const fa_b200_params* p);
+
+/* Bytes of scratch fa_b200_bwd needs for these sizes (delta, fp32 dQ
+ * accumulator, ...).  Counterpart of the 'delta' entry of
+ * ops/memory.py:653-760 allocate_attention_workspace_enhanced. */
+size_t fa_b200_bwd_workspace_bytes(const fa_b200_params* p);
+
+/* Tile table lookup; counterpart of config.py:288-348 get_enhanced_config. */
+int fa_b200_tile_config(int D, int dtype, int causal, int backward, fa_b200_tile* out);
+
+/*
+ * Dropout keep-mask of the kernels' Philox4x32-10 stream, generated on the
+ * host: out[((b*H + h)*Nq + i)*Nk + j] = 1 if P[b,h,i,j] is kept, else 0.
+ * The reference draws its mask inside the Triton kernel
+ * (kernels/forward_kernel.py:198-203) and never replays it; here forward,
+ * backward and this function share one integer definition.
+ */
+int fa_b200_dropout_mask_host(uint64_t seed, uint64_t offset, float dropout_p,
+                              int B, int H, int Nq, int Nk, uint8_t* out);
+
+/* Same mask, generated by the device code path the kernels use, written to a
+ * device buffer of B*H*Nq*Nk bytes on `stream`. */
+int fa_b200_dropout_mask_device(uint64_t seed, uint64_t offset, float dropout_p,
+                                int B, int H, int Nq, int Nk, uint8_t* out_dev,
+                                int device, void* stream);
+
+/* Drop probability actually realised for a requested dropout_p: the keep test
+ * compares one random byte with round(p*256), so p is quantised to 1/256 and
+ * kept values are scaled by 1/(1 - effective p). */
+float fa_b200_dropout_effective_p(float dropout_p);
+
+/* Raw Philox4x32-10 block (public algorithm, Salmon et al. 2011), exposed so
+ * callers can check the generator against its published known answers. */
+void fa_b200_philox4x32_10(const uint32_t counter[4], const uint32_t key[2], uint32_t out[4]);
+
+const char* fa_b200_strerror(int status);
+const char* fa_b200_last_error(void);
+int         fa_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H */

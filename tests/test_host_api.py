@@ -1,0 +1,156 @@
+"""C-ABI surface and host logic that need no GPU."""
+import ctypes
+import inspect
+import os
+import re
+
+import pytest
+import torch
+
+import flash_attention_v100 as fa
+from flash_attention_v100.kernels import _cabi, tile_table
+from flash_attention_v100.ops import memory
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fa_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fa_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(_cabi.LIB_PATH)
+    names = _declared_symbols()
+    assert "fa_b200_fwd" in names and "fa_b200_bwd" in names
+    for n in names:
+        assert hasattr(lib, n), n
+    assert set(names) == set(_cabi.EXPORTS)
+
+
+def test_params_struct_size_is_accepted():
+    lib = _cabi.load()
+    p = _cabi.Params()
+    p.struct_bytes = ctypes.sizeof(_cabi.Params)
+    p.B, p.Nq, p.Nk, p.H, p.Hkv, p.D = 2, 128, 128, 4, 4, 64
+    p.dtype = _cabi.FA_B200_BF16
+    assert lib.fa_b200_bwd_workspace_bytes(ctypes.byref(p)) >= 2 * 4 * 128 * 4
+    p.struct_bytes = 8
+    assert lib.fa_b200_bwd_workspace_bytes(ctypes.byref(p)) == 0
+    assert lib.fa_b200_fwd(ctypes.byref(p)) == _cabi.FA_EINVAL
+    assert b"struct_bytes" in lib.fa_b200_last_error()
+
+
+@pytest.mark.parametrize("field,value,code", [
+    ("H", 0, _cabi.FA_EINVAL), ("Hkv", 3, _cabi.FA_EINVAL), ("dtype", 7, _cabi.FA_EINVAL),
+    ("dropout_p", 1.0, _cabi.FA_EINVAL), ("dropout_p", -0.1, _cabi.FA_EINVAL),
+    ("variant", 9, _cabi.FA_EINVAL), ("scale", float("nan"), _cabi.FA_EINVAL),
+])
+def test_bad_arguments_are_refused_before_any_cuda_call(field, value, code):
+    lib = _cabi.load()
+    p = _cabi.Params()
+    p.struct_bytes = ctypes.sizeof(_cabi.Params)
+    p.B, p.Nq, p.Nk, p.H, p.Hkv, p.D = 1, 16, 16, 4, 4, 64
+    p.scale = 0.125
+    setattr(p, field, value)
+    assert lib.fa_b200_fwd(ctypes.byref(p)) == code
+    assert lib.fa_b200_bwd(ctypes.byref(p)) == code
+
+
+def test_null_pointers_are_refused():
+    lib = _cabi.load()
+    p = _cabi.Params()
+    p.struct_bytes = ctypes.sizeof(_cabi.Params)
+    p.B, p.Nq, p.Nk, p.H, p.Hkv, p.D = 1, 16, 16, 4, 4, 64
+    p.scale = 0.125
+    assert lib.fa_b200_fwd(ctypes.byref(p)) == _cabi.FA_EINVAL
+    assert b"null" in lib.fa_b200_last_error()
+    with pytest.raises(ValueError):
+        _cabi.raise_for_status(_cabi.FA_EINVAL, "x")
+    with pytest.raises(RuntimeError):
+        _cabi.raise_for_status(_cabi.FA_ECUDA, "x")
+
+
+def test_empty_problem_is_ok_without_pointers():
+    lib = _cabi.load()
+    p = _cabi.Params()
+    p.struct_bytes = ctypes.sizeof(_cabi.Params)
+    p.B, p.Nq, p.Nk, p.H, p.Hkv, p.D = 0, 16, 16, 4, 4, 64
+    assert lib.fa_b200_fwd(ctypes.byref(p)) == _cabi.FA_OK
+
+
+def test_strerror_covers_all_codes():
+    lib = _cabi.load()
+    seen = {lib.fa_b200_strerror(c) for c in range(0, -7, -1)}
+    assert len(seen) == 7 and b"unknown status" not in seen
+
+
+def test_tile_table_keys_and_families():
+    cfg = fa.get_enhanced_config(4096, 128, dtype=torch.bfloat16, causal=True)
+    for key in ("BLOCK_M", "BLOCK_N", "BLOCK_K", "NUM_STAGES", "NUM_WARPS"):   # reference config.py:288-348
+        assert key in cfg
+    assert cfg["BLOCK_K"] == 128 and cfg["VARIANT"] == "tcgen05"
+    assert tile_table.lookup(64, torch.float32)["VARIANT"] == "simt"
+    assert tile_table.lookup(96, torch.float16)["VARIANT"] == "simt"
+    with pytest.raises(ValueError):
+        tile_table.lookup(256, torch.float16)
+    cfg8 = fa.get_enhanced_config(4096, 128, 8)
+    assert cfg8["ENABLE_MULTI_GPU"] and cfg8["PARALLELIZATION_STRATEGY"] == "head_parallel"
+
+
+def test_workspace_estimates():
+    n = memory.backward_workspace_bytes(4, 4096, 4096, 32, 128, torch.bfloat16)
+    assert n >= 4 * 32 * 4096 * 4
+    est = memory.estimate_peak_memory_usage(4, 4096, 4096, 32, 128, torch.bfloat16)
+    assert est["total_memory_mb"] > 8 * 128          # eight 134 MB tensors at least
+    assert est["total_memory_mb"] < 4 * 32 * 4096 * 4096 * 2 / 2 ** 20   # far below the N^2 scores
+
+
+def test_public_signatures_match_the_reference():
+    sig = inspect.signature(fa.flash_attention_v100)
+    assert list(sig.parameters) == [
+        "q", "k", "v", "causal", "scale", "dropout_p", "bias", "block_size_m", "block_size_n",
+        "enable_autotuning", "return_softmax_lse", "optimization_strategy", "enable_multi_gpu",
+        "enable_profiling", "fallback_on_error", "validate_inputs"]      # reference interface.py:199-217
+    assert sig.parameters["causal"].default is False and sig.parameters["dropout_p"].default == 0.0
+    fwd = inspect.signature(fa.FlashAttentionV100Function.forward)
+    assert list(fwd.parameters)[1:] == [
+        "q", "k", "v", "scale", "causal", "dropout_p", "bias", "block_size_m", "block_size_n",
+        "enable_autotuning", "return_softmax_lse", "enable_gradient_checkpointing",
+        "enable_mixed_precision", "num_checkpoints", "memory_efficient", "performance_mode",
+        "enable_multi_gpu", "world_size", "rank"]                          # reference ops/attention.py:50-72
+    mgr = inspect.signature(fa.FlashAttentionV100Manager.__init__)
+    assert list(mgr.parameters)[1:] == ["enable_multi_gpu", "optimization_strategy", "enable_profiling"]
+    assert fa.SUPPORTED_DTYPES == {torch.float16, torch.bfloat16, torch.float32}
+
+
+def test_validation_errors_match_the_reference():
+    q = torch.zeros(2, 8, 4, 16)
+    with pytest.raises(ValueError, match="4-dimensional"):
+        fa.flash_attention_v100(q[0], q, q)
+    with pytest.raises(ValueError, match="Batch sizes must match"):
+        fa.flash_attention_v100(q, q[:1], q)
+    with pytest.raises(ValueError, match="Head dimensions must match"):
+        fa.flash_attention_v100(q, q[..., :8], q)
+    with pytest.raises(ValueError, match="same dtype"):
+        fa.flash_attention_v100(q, q.half(), q)
+    with pytest.raises(ValueError, match="Unsupported dtype"):
+        fa.flash_attention_v100(q.double(), q.double(), q.double())
+    with pytest.raises(ValueError, match="divisible"):
+        fa.flash_attention_v100(q, q[:, :, :3], q[:, :, :3])
+    with pytest.raises(ValueError, match="dropout_p must be in"):
+        fa.utils.validate_inputs(q, q, q, None, None, 1.5, require_cuda=False)
+    with pytest.raises(ValueError, match="requires CUDA tensors"):
+        fa.flash_attention_v100(q, q, q)      # no CPU path: CPU tensors are refused, not computed
+    with pytest.raises(TypeError):
+        fa.flash_attention_v100(1, q, q)
+
+
+def test_manager_is_a_context_manager_and_caches_configs():
+    m = fa.FlashAttentionV100Manager(enable_multi_gpu=False)
+    with m as mm:
+        assert fa.get_flash_attention_manager() is mm
+    c1 = m.get_optimal_config(1024, 1024, 8, 64)
+    assert m.get_optimal_config(1024, 1024, 8, 64) is c1
+    assert m.get_optimal_config(1024, 1024, 8, 64, force_recompute=True) is not c1
