@@ -1,0 +1,305 @@
+"""Parity of the CUDA kernels (called through the C ABI) with the oracle.
+
+Tolerances (relative L2 per tensor, vs the fp32 math path evaluated on the
+dtype-rounded inputs): 2e-3 for fp16/bf16, 1e-5 for fp32.  Dropout masks and
+repeated backward runs must agree bit for bit.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import flash_attention_v100 as fa
+from flash_attention_v100.kernels import _cabi
+from flash_attention_v100.ops.attention import (launch_forward, launch_backward, kernel_variant,
+                                                flash_attention_forward, flash_attention_backward)
+from flash_attention_v100.testing import WORKLOADS, TOLERANCE, make_inputs, rel_l2
+from oracle import attention_oracle as ao
+from oracle import c_oracle
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+CASES = sorted(p for p in glob.glob(os.path.join(GOLDEN, "math_path_*.npz")) if "cfg1" not in p)
+
+
+def _tc_ok(dtype, D):
+    return dtype in (torch.float16, torch.bfloat16) and D in (64, 128)
+
+
+def _variants(dtype, D):
+    """Kernel families to run a case on; FA_B200_TEST_VARIANTS=simt narrows a debugging run."""
+    allowed = os.environ.get("FA_B200_TEST_VARIANTS", "simt,tcgen05").split(",")
+    out = [v for v in (["simt", "tcgen05"] if _tc_ok(dtype, D) else ["simt"]) if v in allowed]
+    assert out
+    return out
+
+
+def _rand(shape, dtype, seed, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(dtype)
+
+
+def _check(name, got, ref, tol):
+    """rel-L2 with an absolute floor: a reference whose RMS is below 1e-3 (e.g. the
+    exactly-zero dQ of a single-key problem) is compared on the 1e-3 RMS scale."""
+    ref64, got64 = ref.detach().double().cpu(), got.detach().double().cpu()
+    floor = 1e-3 * ref64.numel() ** 0.5
+    err = (got64 - ref64).norm().item() / max(ref64.norm().item(), floor)
+    assert err <= tol, f"{name}: rel-L2 {err:.3e} > {tol:.1e}"
+    return err
+
+
+def _run_case(device, variant, B, Nq, Nk, H, Hkv, D, dtype, causal, scale=None, dropout_p=0.0,
+              seed=0, tol=None, backward=True):
+    tol = TOLERANCE[dtype] if tol is None else tol
+    q = _rand((B, Nq, H, D), dtype, seed)
+    k = _rand((B, Nk, Hkv, D), dtype, seed + 1)
+    v = _rand((B, Nk, Hkv, D), dtype, seed + 2)
+    d_o = _rand((B, Nq, H, D), dtype, seed + 3)
+    scale = D ** -0.5 if scale is None else scale
+    keep, p_eff, stream = None, 0.0, (0, 0)
+    if dropout_p > 0:
+        stream = (0xC0FFEE + seed, 11 + seed)
+        keep_np = np.empty((B, H, Nq, Nk), np.uint8)
+        lib = _cabi.load()
+        assert lib.fa_b200_dropout_mask_host(stream[0], stream[1], dropout_p, B, H, Nq, Nk,
+                                             keep_np.ctypes.data) == 0
+        keep = torch.from_numpy(keep_np)
+        p_eff = float(lib.fa_b200_dropout_effective_p(dropout_p))
+    ro, rlse, rdq, rdk, rdv = ao.attention_forward_backward(
+        q.float(), k.float(), v.float(), d_o.float(), causal=causal, scale=scale,
+        dropout_p=p_eff, keep_mask=keep)
+    qd, kd, vd, gd = (t.to(device) for t in (q, k, v, d_o))
+    with kernel_variant(variant):
+        o, lse = launch_forward(qd, kd, vd, scale, causal, dropout_p, *stream)
+        _check("O", o, ro, tol)
+        _check("LSE", lse, rlse, tol)
+        if backward:
+            dq, dk, dv = launch_backward(gd, qd, kd, vd, o, lse, scale, causal, dropout_p, *stream)
+            _check("dQ", dq, rdq, tol)
+            _check("dK", dk, rdk, tol)
+            _check("dV", dv, rdv, tol)
+            dq2, dk2, dv2 = launch_backward(gd, qd, kd, vd, o, lse, scale, causal, dropout_p, *stream)
+            assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2), \
+                "backward is not bit-reproducible"
+
+
+@pytest.mark.parametrize("path", CASES, ids=[os.path.basename(p)[10:-4] for p in CASES])
+def test_reference_golden_vectors_fp32(device, path):
+    """The reference's own outputs and autograd gradients, fp32."""
+    z = np.load(path)
+    t = {k: torch.from_numpy(z[k]).to(device) for k in ("q", "k", "v", "d_o")}
+    causal, scale = bool(z["causal"]), float(z["scale"])
+    o, lse = launch_forward(t["q"], t["k"], t["v"], scale, causal)
+    dq, dk, dv = launch_backward(t["d_o"], t["q"], t["k"], t["v"], o, lse, scale, causal)
+    for name, got in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
+        _check(name, got, torch.from_numpy(z[name]), 1e-5)
+
+
+@pytest.mark.parametrize("path", CASES, ids=[os.path.basename(p)[10:-4] for p in CASES])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_reference_golden_inputs_rounded(device, path, dtype):
+    """Same fixtures with inputs rounded to 16 bits: every kernel family that
+    covers the shape, against the oracle on the rounded inputs."""
+    z = np.load(path)
+    t = {k: torch.from_numpy(z[k]).to(dtype) for k in ("q", "k", "v", "d_o")}
+    causal, scale = bool(z["causal"]), float(z["scale"])
+    ro, rlse, rdq, rdk, rdv = ao.attention_forward_backward(
+        *(t[k].float() for k in ("q", "k", "v", "d_o")), causal=causal, scale=scale)
+    d = {k: x.to(device) for k, x in t.items()}
+    for variant in _variants(dtype, t["q"].shape[-1]):
+        with kernel_variant(variant):
+            o, lse = launch_forward(d["q"], d["k"], d["v"], scale, causal)
+            dq, dk, dv = launch_backward(d["d_o"], d["q"], d["k"], d["v"], o, lse, scale, causal)
+        for name, got, ref in (("o", o, ro), ("lse", lse, rlse), ("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+            _check(f"{variant}:{name}", got, ref, 2e-3)
+
+
+SHAPES = [
+    # B, Nq, Nk, H, Hkv, D
+    (1, 1, 1, 1, 1, 64),          # single query, single key
+    (2, 17, 17, 3, 3, 64),        # smaller than one tile
+    (1, 128, 128, 2, 2, 64),      # exactly one 128-row tile
+    (1, 129, 129, 1, 1, 128),     # one row over a tile
+    (2, 256, 256, 2, 2, 128),     # one 2-tile CTA
+    (1, 300, 300, 2, 2, 64),      # ragged tail
+    (1, 384, 384, 1, 1, 128),     # odd number of 128-row tiles
+    (1, 200, 333, 2, 2, 64),      # Nq != Nk
+    (1, 333, 200, 2, 2, 128),
+    (2, 512, 512, 4, 4, 128),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("causal", [False, True], ids=["full", "causal"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32], ids=["fp16", "bf16", "fp32"])
+def test_small_and_ragged_shapes(device, shape, causal, dtype):
+    B, Nq, Nk, H, Hkv, D = shape
+    for variant in _variants(dtype, D):
+        _run_case(device, variant, B, Nq, Nk, H, Hkv, D, dtype, causal, seed=Nq + D)
+
+
+@pytest.mark.parametrize("D", [8, 16, 32, 40, 96, 128])
+def test_other_head_dims_cuda_core_tiles(device, D):
+    _run_case(device, "auto", 1, 150, 150, 2, 2, D, torch.float16, True, seed=D)
+    _run_case(device, "auto", 1, 70, 90, 2, 2, D, torch.float32, False, seed=D)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32], ids=["bf16", "fp32"])
+def test_grouped_kv_heads(device, dtype):
+    _run_case(device, "simt", 2, 130, 130, 8, 2, 64, dtype, True, seed=5)
+    _run_case(device, "simt", 1, 96, 160, 6, 1, 32, dtype, False, seed=6)
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 64), (torch.float16, 128), (torch.float32, 64)],
+                         ids=["bf16-d64", "fp16-d128", "fp32-d64"])
+@pytest.mark.parametrize("p", [0.1, 0.5])
+def test_dropout_against_oracle_with_injected_mask(device, dtype, D, p):
+    for variant in _variants(dtype, D):
+        _run_case(device, variant, 2, 200, 200, 3, 3, D, dtype, True, dropout_p=p, seed=int(p * 10))
+        _run_case(device, variant, 1, 130, 260, 2, 2, D, dtype, False, dropout_p=p, seed=int(p * 10) + 1)
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 37, 53), (1, 2, 256, 256), (1, 1, 130, 1000)])
+@pytest.mark.parametrize("p", [0.0, 0.1, 0.73])
+def test_dropout_mask_device_equals_host_bit_exact(device, shape, p):
+    B, H, Nq, Nk = shape
+    lib = _cabi.load()
+    seed, offset = 0x5EED, 0xFFFF_FFFF_0000_0003
+    host = np.empty(shape, np.uint8)
+    assert lib.fa_b200_dropout_mask_host(seed, offset, p, B, H, Nq, Nk, host.ctypes.data) == 0
+    dev = torch.empty(shape, dtype=torch.uint8, device=device)
+    rc = lib.fa_b200_dropout_mask_device(seed, offset, p, B, H, Nq, Nk, dev.data_ptr(), device.index or 0,
+                                         torch.cuda.current_stream(device).cuda_stream)
+    assert rc == 0
+    assert np.array_equal(dev.cpu().numpy(), host)
+    assert np.array_equal(host, c_oracle.dropout_mask(seed, offset, p, B, H, Nq, Nk))
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 64), (torch.float16, 128)])
+def test_dropout_mask_replayed_by_forward_and_backward(device, dtype, D):
+    """V = identity-like probe: with v one-hot per key, O exposes exactly which
+    probabilities the forward kept; dV with dO one-hot exposes the backward's."""
+    B, H, N = 1, 2, D            # N == D so that V can be the identity
+    p = 0.4
+    lib = _cabi.load()
+    seed, offset = 77, 5
+    keep = np.empty((B, H, N, N), np.uint8)
+    assert lib.fa_b200_dropout_mask_host(seed, offset, p, B, H, N, N, keep.ctypes.data) == 0
+    q = _rand((B, N, H, D), dtype, 1, 0.1).to(device)
+    k = _rand((B, N, H, D), dtype, 2, 0.1).to(device)
+    eye = torch.eye(N, dtype=dtype).view(1, N, 1, D).expand(B, N, H, D).contiguous().to(device)
+    for variant in _variants(dtype, D):
+        with kernel_variant(variant):
+            o, lse = launch_forward(q, k, eye, D ** -0.5, False, p, seed, offset)
+            # O[b,i,h,j] = P[b,h,i,j] * keep / (1-p): zero exactly where dropped
+            kept_fwd = (o.permute(0, 2, 1, 3) != 0).cpu().numpy().astype(np.uint8)
+            assert np.array_equal(kept_fwd, keep), variant
+            # dV[b,j,h,d] = sum_i (P o Z)[i,j] dO[i,d]; with dO = identity: dV[j,:,i] = (P o Z)[i,j]
+            _, _, dv = launch_backward(eye, q, k, eye, o, lse, D ** -0.5, False, p, seed, offset)
+            kept_bwd = (dv.permute(0, 2, 3, 1) != 0).cpu().numpy().astype(np.uint8)
+            assert np.array_equal(kept_bwd, keep), variant
+
+
+def test_strided_head_and_batch_views_are_consumed_in_place(device):
+    B, N, H, D = 3, 160, 6, 64
+    dtype = torch.bfloat16
+    full = {n: _rand((B, N, H, D), dtype, i).to(device) for i, n in enumerate(("q", "k", "v", "g"))}
+    for variant in _variants(dtype, D):
+        with kernel_variant(variant):
+            o_full, lse_full = launch_forward(full["q"], full["k"], full["v"], 0.125, True)
+            dq_f, dk_f, dv_f = launch_backward(full["g"], full["q"], full["k"], full["v"], o_full, lse_full, 0.125, True)
+            sl = (slice(1, 3), slice(None), slice(2, 5))
+            views = {n: t[sl] for n, t in full.items()}
+            assert not views["q"].is_contiguous()
+            o_v, lse_v = launch_forward(views["q"], views["k"], views["v"], 0.125, True)
+            dq_v, dk_v, dv_v = launch_backward(views["g"], views["q"], views["k"], views["v"], o_v, lse_v, 0.125, True)
+        # per-(b,h) work is identical, so shards equal the unsharded result bit for bit
+        assert torch.equal(o_v, o_full[sl]) and torch.equal(lse_v, lse_full[1:3, 2:5])
+        assert torch.equal(dq_v, dq_f[sl]) and torch.equal(dk_v, dk_f[sl]) and torch.equal(dv_v, dv_f[sl])
+
+
+def test_autograd_function_contract(device):
+    B, N, H, D = 2, 96, 4, 64
+    q, k, v = (_rand((B, N, H, D), torch.float16, i).to(device).requires_grad_(True) for i in range(3))
+    out = fa.FlashAttentionV100Function.apply(q, k, v, 0.125, True, 0.0, None, None, None, True, True)
+    assert isinstance(out, tuple) and out[0].shape == (B, N, H, D) and out[0].dtype == torch.float16
+    assert out[1].shape == (B, H, N) and out[1].dtype == torch.float32 and not out[1].requires_grad
+    (out[0].float() ** 2).sum().backward()
+    assert q.grad.shape == q.shape and k.grad.shape == k.shape and v.grad.shape == v.shape
+    assert torch.isfinite(q.grad).all() and torch.isfinite(k.grad).all() and torch.isfinite(v.grad).all()
+    o2 = fa.flash_attention_v100(q.detach(), k.detach(), v.detach(), causal=True, enable_multi_gpu=False)
+    assert torch.equal(o2, out[0].detach())
+    o3 = flash_attention_forward(q.detach(), k.detach(), v.detach(), None, True)
+    assert torch.equal(o3, o2)
+    dq, dk, dv = flash_attention_backward(torch.ones_like(o2), q.detach(), k.detach(), v.detach(), o2,
+                                          out[1], None, 0.125, True)
+    assert dq.shape == q.shape
+
+
+def test_public_api_gradients_match_oracle(device):
+    """README quick-start usage: call, backward through autograd, compare."""
+    B, N, H, D = 2, 256, 4, 64
+    qc, kc, vc, gc = (_rand((B, N, H, D), torch.bfloat16, 10 + i) for i in range(4))
+    q, k, v = (t.to(device).requires_grad_(True) for t in (qc, kc, vc))
+    o = fa.flash_attention_v100(q, k, v, causal=True, enable_multi_gpu=False)
+    o.backward(gc.to(device))
+    ro, _, rdq, rdk, rdv = ao.attention_forward_backward(qc.float(), kc.float(), vc.float(), gc.float(), causal=True)
+    for name, got, ref in (("o", o, ro), ("dq", q.grad, rdq), ("dk", k.grad, rdk), ("dv", v.grad, rdv)):
+        _check(name, got, ref, 2e-3)
+
+
+def test_dropout_through_public_api_is_replayed_in_backward(device):
+    B, N, H, D = 1, 128, 2, 64
+    fa.set_dropout_seed(123, 9)
+    qc, kc, vc, gc = (_rand((B, N, H, D), torch.bfloat16, 20 + i) for i in range(4))
+    q, k, v = (t.to(device).requires_grad_(True) for t in (qc, kc, vc))
+    o = fa.flash_attention_v100(q, k, v, causal=True, dropout_p=0.25, enable_multi_gpu=False)
+    o.backward(gc.to(device))
+    lib = _cabi.load()
+    keep = np.empty((B, H, N, N), np.uint8)
+    assert lib.fa_b200_dropout_mask_host(123, 9, 0.25, B, H, N, N, keep.ctypes.data) == 0
+    ro, _, rdq, rdk, rdv = ao.attention_forward_backward(qc.float(), kc.float(), vc.float(), gc.float(), causal=True,
+                                                         dropout_p=0.25, keep_mask=torch.from_numpy(keep))
+    for name, got, ref in (("o", o, ro), ("dq", q.grad, rdq), ("dk", k.grad, rdk), ("dv", v.grad, rdv)):
+        _check(name, got, ref, 2e-3)
+
+
+def test_softmax_range_stress_rows(device):
+    """1% of q/k rows scaled x8 (the long-context workload's distribution)."""
+    w = WORKLOADS["cfg4"].shrink(B=1, N=1024, H=2)
+    t = make_inputs(w)
+    ro, rlse, rdq, rdk, rdv = ao.attention_forward_backward(
+        *(t[n].float() for n in ("q", "k", "v", "d_o")), causal=True, scale=w.scale)
+    d = {n: x.to(device) for n, x in t.items()}
+    for variant in _variants(w.dtype, w.D):
+        with kernel_variant(variant):
+            o, lse = launch_forward(d["q"], d["k"], d["v"], w.scale, True)
+            dq, dk, dv = launch_backward(d["d_o"], d["q"], d["k"], d["v"], o, lse, w.scale, True)
+        for name, got, ref in (("o", o, ro), ("lse", lse, rlse), ("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+            _check(f"{variant}:{name}", got, ref, 2e-3)
+
+
+def test_cfg1_quickstart_shape_fp32_forward(device):
+    """B2 N1024 H12 D64 fp32 causal, seed 0: O against the reference's stored rows, LSE against the oracle."""
+    w = WORKLOADS["cfg1"]
+    t = make_inputs(w)
+    z = np.load(os.path.join(GOLDEN, "math_path_cfg1_rows.npz"))
+    o, lse = launch_forward(t["q"].to(device), t["k"].to(device), t["v"].to(device), w.scale, True)
+    _check("o rows", o[:, ::int(z["row_step"])], torch.from_numpy(z["o_rows"]), 1e-5)
+    _, rlse = ao.chunked(ao.attention_forward, t["q"], t["k"], t["v"], heads_per_chunk=4, causal=True, scale=w.scale)
+    _check("lse", lse, rlse, 1e-5)
+
+
+def test_error_codes_on_device(device):
+    q = torch.zeros(1, 16, 2, 64, device=device, dtype=torch.float16)
+    with pytest.raises(ValueError, match="tcgen05"):
+        with kernel_variant("tcgen05"):
+            launch_forward(q[..., :40].contiguous(), q[..., :40].contiguous(), q[..., :40].contiguous(), 1.0, False)
+    with pytest.raises(NotImplementedError):
+        fa.flash_attention_v100(q, q, q, bias=torch.zeros(1, 2, 16, 16, device=device))
+    # empty problems are legal and return empty tensors
+    e = torch.zeros(0, 16, 2, 64, device=device, dtype=torch.float16)
+    assert fa.flash_attention_v100(e, e, e, enable_multi_gpu=False).shape == (0, 16, 2, 64)

@@ -1,0 +1,88 @@
+"""Benchmark workloads at reduced batch/heads against the oracle, and at full
+size through size-independent properties (shards == whole, determinism,
+oracle on a sampled subset of heads)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import flash_attention_v100 as fa
+from flash_attention_v100.kernels import _cabi
+from flash_attention_v100.ops.attention import launch_forward, launch_backward
+from flash_attention_v100.testing import WORKLOADS, TOLERANCE, DROPOUT_SEED, DROPOUT_OFFSET, make_inputs, rel_l2
+from oracle import attention_oracle as ao
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_subset(w, t, b, heads, keep=None, p_eff=0.0):
+    sl = (slice(b, b + 1), slice(None), heads)
+    return ao.attention_forward_backward(*(t[n][sl].float() for n in ("q", "k", "v", "d_o")),
+                                         causal=w.causal, scale=w.scale, dropout_p=p_eff, keep_mask=keep)
+
+
+@pytest.mark.parametrize("name,shrink", [
+    ("cfg2", dict(B=1, H=2)), ("cfg3", dict(B=1, H=2)), ("cfg4", dict(N=8192, H=1)), ("cfg5", dict(B=1, H=2)),
+])
+def test_workload_shapes_reduced_vs_oracle(device, name, shrink):
+    w = WORKLOADS[name].shrink(**shrink)
+    t = make_inputs(w)
+    keep, p_eff, stream = None, 0.0, (0, 0)
+    if w.dropout_p > 0:
+        stream = (DROPOUT_SEED, DROPOUT_OFFSET)
+        lib = _cabi.load()
+        keep_np = np.empty((w.B, w.H, w.N, w.N), np.uint8)
+        assert lib.fa_b200_dropout_mask_host(*stream, w.dropout_p, w.B, w.H, w.N, w.N, keep_np.ctypes.data) == 0
+        keep, p_eff = torch.from_numpy(keep_np), float(lib.fa_b200_dropout_effective_p(w.dropout_p))
+    ref = ao.attention_forward_backward(*(t[n].float() for n in ("q", "k", "v", "d_o")), causal=w.causal,
+                                        scale=w.scale, dropout_p=p_eff, keep_mask=keep)
+    d = {n: x.to(device) for n, x in t.items()}
+    o, lse = launch_forward(d["q"], d["k"], d["v"], w.scale, w.causal, w.dropout_p, *stream)
+    dq, dk, dv = launch_backward(d["d_o"], d["q"], d["k"], d["v"], o, lse, w.scale, w.causal, w.dropout_p, *stream)
+    tol = TOLERANCE[w.dtype]
+    for nm, got, r in zip(("o", "lse", "dq", "dk", "dv"), (o, lse, dq, dk, dv), ref):
+        err = rel_l2(got, r)
+        assert err <= tol, f"{name}:{nm} rel-L2 {err:.3e}"
+
+
+@pytest.mark.parametrize("name", ["cfg2", "cfg3", "cfg5"])
+def test_full_size_properties(device, name):
+    """Full benchmark size: (1) two runs agree bit for bit, (2) a head-sharded
+    run equals the whole, (3) two sampled (b, h) columns match the oracle."""
+    w = WORKLOADS[name]
+    if "tcgen05" not in os.environ.get("FA_B200_TEST_VARIANTS", "simt,tcgen05").split(","):
+        pytest.skip("full-size runs are only practical on the tensor-core kernels")
+    t = make_inputs(w)
+    stream = (DROPOUT_SEED, DROPOUT_OFFSET) if w.dropout_p > 0 else (0, 0)
+    d = {n: x.to(device) for n, x in t.items()}
+    run = lambda q, k, v, g: (lambda o_lse: o_lse + launch_backward(g, q, k, v, o_lse[0], o_lse[1], w.scale, w.causal,
+                                                                    w.dropout_p, *stream))(
+        launch_forward(q, k, v, w.scale, w.causal, w.dropout_p, *stream))
+    a = run(d["q"], d["k"], d["v"], d["d_o"])
+    b = run(d["q"], d["k"], d["v"], d["d_o"])
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    if w.dropout_p == 0:      # the dropout stream is indexed by the global (b, h), so shards differ by design
+        h0, h1 = w.H // 2, w.H // 2 + 2
+        s = run(*(d[n][:, :, h0:h1] for n in ("q", "k", "v", "d_o")))
+        assert torch.equal(s[0], a[0][:, :, h0:h1]) and torch.equal(s[1], a[1][:, h0:h1])
+        assert all(torch.equal(s[i], a[i][:, :, h0:h1]) for i in (2, 3, 4))
+    tol = TOLERANCE[w.dtype]
+    # dropout: the stream is indexed by b*H + h, so sample low (b, h) columns whose
+    # host mask is cheap to generate; otherwise sample the first and the last column
+    samples = ((0, 0), (0, 1)) if w.dropout_p > 0 else ((0, 0), (w.B - 1, w.H - 1))
+    for bb, hh in samples:
+        keep, p_eff = None, 0.0
+        if w.dropout_p > 0:
+            lib = _cabi.load()
+            bh = bb * w.H + hh
+            tmp = np.empty((1, bh + 1, w.N, w.N), np.uint8)
+            assert lib.fa_b200_dropout_mask_host(*stream, w.dropout_p, 1, bh + 1, w.N, w.N, tmp.ctypes.data) == 0
+            keep = torch.from_numpy(tmp[:, bh:bh + 1])
+            p_eff = float(lib.fa_b200_dropout_effective_p(w.dropout_p))
+        ref = _oracle_subset(w, t, bb, slice(hh, hh + 1), keep, p_eff)
+        got = (a[0][bb:bb + 1, :, hh:hh + 1], a[1][bb:bb + 1, hh:hh + 1], a[2][bb:bb + 1, :, hh:hh + 1],
+               a[3][bb:bb + 1, :, hh:hh + 1], a[4][bb:bb + 1, :, hh:hh + 1])
+        for nm, g_, r in zip(("o", "lse", "dq", "dk", "dv"), got, ref):
+            err = rel_l2(g_, r)
+            assert err <= tol, f"{name}[b{bb},h{hh}]:{nm} rel-L2 {err:.3e}"
