@@ -1,5 +1,479 @@
+// Attention forward for sm_100a: TMA -> shared memory -> tcgen05.mma with
+// accumulators in tensor memory, warp-specialised.
+//
+// Replaces the reference's Triton forward kernel
+// (kernels/forward_kernel.py:18-243) and its launcher (:246-387).
+//
+// One CTA owns two consecutive 128-row query tiles of one (batch, head) and
+// walks the key/value sequence in 128-row blocks:
+//
+//   warps 10-11 idle (they complete the third warpgroup for setmaxnreg)
+//   warp 9      TMA producer: Q tiles once, then K_j / V_j into two rings
+//   warp 8      MMA issuer (one elected thread):
+//                   S_t = Q_t K_j^T          (SS MMA, both operands K-major)
+//                   O_t += P_t V_j           (TS MMA: P_t from TMEM, V_j MN-major)
+//               issue order  S0(0) S1(0) | PV0(j) S0(j+1) PV1(j) S1(j+1) ...
+//               so that the softmax of one tile overlaps the MMAs of the other
+//   warps 0-3   softmax of tile 0, one thread per query row (TMEM lane)
+//   warps 4-7   softmax of tile 1
+//
+// Online softmax in the log2 domain with scale*log2(e) folded into one FMA.
+// The running maximum is only refreshed when it grows by more than 2^8 (warp
+// vote), so the O accumulator in TMEM is rescaled rarely; the final division
+// by the row sum makes the result exact either way.  P is rounded to the input
+// dtype and written over S in TMEM; dropout zeroes P entries (the 1/(1-p)
+// factor is applied once to O), the row sum uses the undropped P.
+//
+// TMEM columns: S0/P0 [0,128)  S1/P1 [128,256)  O0 [256,256+D)  O1 [384,384+D).
+//
+// Every mbarrier wait is bounded; on a time-out the CTA raises its abort flag,
+// every role unwinds, TMEM is freed and the status word is set.
 #include "fa_common.cuh"
+#include "sm100_ptx.cuh"
+#include "tma_host.cuh"
+
 namespace fa {
-bool sm100_supports(const fa_b200_params& p, bool backward, const char** why) { *why = "not built yet"; return false; }
-int sm100_fwd(const fa_b200_params& p) { return FA_EUNSUPPORTED; }
+namespace {
+
+using namespace ptx;
+
+constexpr int kBlockM = 128;        // query rows per tile
+constexpr int kBlockN = 128;        // key rows per block
+constexpr int kThreads = 384;        // 2 softmax warpgroups + 1 warpgroup holding the MMA and TMA warps
+constexpr int kBoxBytes = 128 * 128;   // one TMA box: 128 rows x 64 16-bit elements
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units
+
+template <int D>
+struct FwdCfg {
+    static constexpr int kNBox = D / 64;
+    static constexpr int kTileBytes = kNBox * kBoxBytes;
+    static constexpr int kStages = (D == 128) ? 2 : 4;
+    // barrier slots
+    static constexpr int kQFull = 0;                       // [2]
+    static constexpr int kKFull = 2;                       // [kStages]
+    static constexpr int kKEmpty = kKFull + kStages;
+    static constexpr int kVFull = kKEmpty + kStages;
+    static constexpr int kVEmpty = kVFull + kStages;
+    static constexpr int kSFull = kVEmpty + kStages;       // [2]
+    static constexpr int kPFull = kSFull + 2;              // [2]
+    static constexpr int kODone = kPFull + 2;              // [2]
+    static constexpr int kEpi = kODone + 2;                // [2] epilogue rows staged
+    static constexpr int kNumBars = kEpi + 2;
+    static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + kNumBars * 8 + 64 + 1024;
+};
+
+struct FwdArgs {
+    float* lse;
+    int32_t* status;
+    int B, Nq, Nk, H, Hkv;
+    int causal;
+    float scale_log2;     // scale * log2(e)
+    uint32_t drop_thr;
+    float inv_keep;
+    PhiloxKey key;
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                 const FwdArgs a) {
+    using Cfg = FwdCfg<D>;
+    constexpr int ST = Cfg::kStages;
+    constexpr int TILE = Cfg::kTileBytes;
+    // P is rounded to the input dtype: tcgen05.mma kind::f16 wants A and B in one
+    // format (an fp16 A next to a bf16 B raises an illegal-instruction fault).
+    constexpr bool P_BF16 = BF16;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + 2 * TILE;
+    uint8_t* sV = sK + ST * TILE;
+    uint64_t* bars = (uint64_t*)(sV + ST * TILE);
+    uint32_t* tmem_slot = (uint32_t*)(bars + Cfg::kNumBars);
+    volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pair = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (a.H / a.Hkv);
+    const int q0 = pair * 2 * kBlockM;
+
+    // key blocks each tile visits (uniform over the CTA)
+    int nblk[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int row0 = q0 + t * kBlockM;
+        int kv_end = a.Nk;
+        if (a.causal && row0 + kBlockM < kv_end) kv_end = row0 + kBlockM;
+        nblk[t] = (row0 < a.Nq) ? (kv_end + kBlockN - 1) / kBlockN : 0;
+    }
+    const int nmax = nblk[0] > nblk[1] ? nblk[0] : nblk[1];
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < Cfg::kNumBars; ++i) {
+            const bool wg_bar = (i >= Cfg::kPFull && i < Cfg::kPFull + 2) || (i >= Cfg::kEpi);
+            mbar_init(&bars[i], wg_bar ? 128u : 1u);
+        }
+        *abort_flag = 0u;
+        fence_mbar_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    if (warp == 9 && lane == 0) {
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+        prefetch_tensormap(&map_o);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    // Register re-partition: the softmax warpgroups take the registers the
+    // MMA/TMA warpgroup does not need (168 * 384 = 232 * 256 + 40 * 128).
+    if (warp >= 8) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      if (warp == 9) {
+        // ------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            int k_issued = 0, v_issued = 0;     // fills armed so far (stage = index % ST)
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                if (nblk[t] > 0) {
+                    mbar_expect_tx(&bars[Cfg::kQFull + t], TILE);
+#pragma unroll
+                    for (int bx = 0; bx < Cfg::kNBox; ++bx)
+                        tma_load_4d(sQ + t * TILE + bx * kBoxBytes, &map_q, &bars[Cfg::kQFull + t],
+                                    bx * 64, h, q0 + t * kBlockM, b);
+                }
+            }
+            bool ok = true;
+            for (int j = 0; j < nmax && ok; ++j) {
+                const int s = j % ST;
+                const uint32_t ph = (uint32_t)(j / ST) & 1u;
+                ok = mbar_wait(&bars[Cfg::kKEmpty + s], ph ^ 1u, abort_flag);
+                if (!ok) break;
+                mbar_expect_tx(&bars[Cfg::kKFull + s], TILE);
+#pragma unroll
+                for (int bx = 0; bx < Cfg::kNBox; ++bx)
+                    tma_load_4d(sK + s * TILE + bx * kBoxBytes, &map_k, &bars[Cfg::kKFull + s],
+                                bx * 64, hk, j * kBlockN, b);
+                ++k_issued;
+                ok = mbar_wait(&bars[Cfg::kVEmpty + s], ph ^ 1u, abort_flag);
+                if (!ok) break;
+                mbar_expect_tx(&bars[Cfg::kVFull + s], TILE);
+#pragma unroll
+                for (int bx = 0; bx < Cfg::kNBox; ++bx)
+                    tma_load_4d(sV + s * TILE + bx * kBoxBytes, &map_v, &bars[Cfg::kVFull + s],
+                                bx * 64, hk, j * kBlockN, b);
+                ++v_issued;
+            }
+            if (!ok) {
+                // unwinding: let copies already issued land before the CTA gives up its
+                // shared memory (bounded: a copy that has not landed by now never will)
+                for (int s = 0; s < ST; ++s) {
+                    const int nk = (k_issued + ST - 1 - s) / ST, nv = (v_issued + ST - 1 - s) / ST;
+                    for (int spin = 0; spin < 4096 && nk > 0 &&
+                         !mbar_try_wait(&bars[Cfg::kKFull + s], (uint32_t)(nk - 1) & 1u); ++spin) {}
+                    for (int spin = 0; spin < 4096 && nv > 0 &&
+                         !mbar_try_wait(&bars[Cfg::kVFull + s], (uint32_t)(nv - 1) & 1u); ++spin) {}
+                }
+                for (int t = 0; t < 2; ++t)
+                    for (int spin = 0; spin < 4096 && nblk[t] > 0 && !mbar_try_wait(&bars[Cfg::kQFull + t], 0u); ++spin) {}
+            }
+        }
+        __syncwarp();
+      } else if (warp == 8) {
+        // ------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t idesc_s = make_idesc_f16(BF16, BF16, kBlockM, kBlockN, false, false);
+            constexpr uint32_t idesc_pv = make_idesc_f16(P_BF16, BF16, kBlockM, D, false, true);
+            const uint32_t sQ_u = smem_u32(sQ), sK_u = smem_u32(sK), sV_u = smem_u32(sV);
+
+            auto issue_s = [&](int t, int ks) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (uint32_t)(kk >> 2) * kBoxBytes + (uint32_t)(kk & 3) * 32u;
+                    mma_ss_f16(tmem + (uint32_t)t * 128u,
+                               make_smem_desc_sw128(sQ_u + t * TILE + off, 0, 1024),
+                               make_smem_desc_sw128(sK_u + ks * TILE + off, 0, 1024), idesc_s, kk > 0);
+                }
+            };
+            auto issue_pv = [&](int t, int vs, bool acc) {
+#pragma unroll
+                for (int kk = 0; kk < kBlockN / 16; ++kk) {
+                    mma_ts_f16(tmem + 256u + (uint32_t)t * 128u, tmem + (uint32_t)t * 128u + (uint32_t)kk * 8u,
+                               make_smem_desc_sw128(sV_u + vs * TILE + kk * 2048, kBoxBytes, 1024), idesc_pv,
+                               (acc || kk > 0) ? 1u : 0u);
+                }
+            };
+
+            bool ok = true;
+            if (nblk[0] > 0) ok = mbar_wait(&bars[Cfg::kQFull + 0], 0u, abort_flag);
+            if (ok && nblk[1] > 0) ok = mbar_wait(&bars[Cfg::kQFull + 1], 0u, abort_flag);
+            if (ok && nmax > 0) ok = mbar_wait(&bars[Cfg::kKFull + 0], 0u, abort_flag);
+            if (ok && nmax > 0) {
+                tc_fence_after_sync();
+                if (nblk[0] > 0) { issue_s(0, 0); mma_commit(&bars[Cfg::kSFull + 0]); }
+                if (nblk[1] > 0) { issue_s(1, 0); mma_commit(&bars[Cfg::kSFull + 1]); }
+                mma_commit(&bars[Cfg::kKEmpty + 0]);
+            }
+            for (int j = 0; j < nmax && ok; ++j) {
+                const int vs = j % ST;
+                const uint32_t vph = (uint32_t)(j / ST) & 1u;
+                const int ks = (j + 1) % ST;
+                const uint32_t kph = (uint32_t)((j + 1) / ST) & 1u;
+                bool k_ready = false;
+                ok = mbar_wait(&bars[Cfg::kVFull + vs], vph, abort_flag);
+                if (!ok) break;
+                if (j < nblk[0]) {
+                    ok = mbar_wait(&bars[Cfg::kPFull + 0], (uint32_t)j & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv(0, vs, j > 0);
+                    if (j == nblk[0] - 1) mma_commit(&bars[Cfg::kODone + 0]);
+                }
+                if (j + 1 < nblk[0]) {
+                    ok = mbar_wait(&bars[Cfg::kKFull + ks], kph, abort_flag);
+                    if (!ok) break;
+                    k_ready = true;
+                    tc_fence_after_sync();
+                    issue_s(0, ks);
+                    mma_commit(&bars[Cfg::kSFull + 0]);
+                }
+                if (j < nblk[1]) {
+                    ok = mbar_wait(&bars[Cfg::kPFull + 1], (uint32_t)j & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv(1, vs, j > 0);
+                    if (j == nblk[1] - 1) mma_commit(&bars[Cfg::kODone + 1]);
+                }
+                mma_commit(&bars[Cfg::kVEmpty + vs]);
+                if (j + 1 < nblk[1]) {
+                    if (!k_ready) {
+                        ok = mbar_wait(&bars[Cfg::kKFull + ks], kph, abort_flag);
+                        if (!ok) break;
+                        k_ready = true;
+                        tc_fence_after_sync();
+                    }
+                    issue_s(1, ks);
+                    mma_commit(&bars[Cfg::kSFull + 1]);
+                }
+                if (j + 1 < nmax) mma_commit(&bars[Cfg::kKEmpty + ks]);
+            }
+        }
+        __syncwarp();
+      }   // warps 10-11 idle: they complete the third warpgroup
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        // ------------------------------------------------------------ softmax + epilogue
+        const int t = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;
+        const int tile = pair * 2 + t;
+        const int i = tile * kBlockM + r;                    // global query row
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tS = tmem + (uint32_t)t * 128u + lane_off;
+        const uint32_t tO = tmem + 256u + (uint32_t)t * 128u + lane_off;
+        const uint32_t bh = (uint32_t)(b * a.H + h);
+        const int n = nblk[t];
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+
+        for (int j = 0; j < n; ++j) {
+            ok = mbar_wait(&bars[Cfg::kSFull + t], (uint32_t)j & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);      // the TMEM accesses below are warp-collective
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t sr[4][32];                    // the row's 128 scores, then its 128 probabilities
+#define SF(c) __uint_as_float(sr[(c) >> 5][(c) & 31])
+#define SSET(c, x) sr[(c) >> 5][(c) & 31] = __float_as_uint(x)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + c * 32, sr[c]);
+            tmem_wait_ld();
+
+            const int col0 = j * kBlockN;
+            const bool need_mask = (a.causal && col0 + kBlockN - 1 > tile * kBlockM) || (col0 + kBlockN > a.Nk);
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < 128; ++c) {
+                    const int col = col0 + c;
+                    if (col >= a.Nk || (a.causal && col > i)) SSET(c, -INFINITY);
+                }
+            }
+            float mx0 = SF(0), mx1 = SF(1), mx2 = SF(2), mx3 = SF(3);
+#pragma unroll
+            for (int c = 4; c < 128; c += 4) {
+                mx0 = fmaxf(mx0, SF(c)); mx1 = fmaxf(mx1, SF(c + 1));
+                mx2 = fmaxf(mx2, SF(c + 2)); mx3 = fmaxf(mx3, SF(c + 3));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2;
+            const float m_new = fmaxf(m, mx);
+            const bool grow = (m_new - m) > kRescaleThreshold;   // first block: inf > 8
+            if (__any_sync(0xffffffffu, grow)) {
+                const float alpha = ex2(m - m_new);               // 0 on the first block
+                m = m_new;
+                l *= alpha;
+                if (j > 0) {
+                    // S_t(j) complete implies PV_t(j-1) complete (same issuing thread, in order)
+#pragma unroll
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t orr[32];
+                        tmem_ld_32x32(tO + c0, orr);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) orr[c] = __float_as_uint(__uint_as_float(orr[c]) * alpha);
+                        tmem_st_32x32(tO + c0, orr);
+                    }
+                }
+            }
+            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+            const float neg_m = -m;
+#pragma unroll
+            for (int c = 0; c < 128; c += 4) {
+                const float p0 = ex2(fmaf(SF(c), a.scale_log2, neg_m));
+                const float p1 = ex2(fmaf(SF(c + 1), a.scale_log2, neg_m));
+                const float p2 = ex2(fmaf(SF(c + 2), a.scale_log2, neg_m));
+                const float p3 = ex2(fmaf(SF(c + 3), a.scale_log2, neg_m));
+                l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+                SSET(c, p0); SSET(c + 1, p1); SSET(c + 2, p2); SSET(c + 3, p3);
+            }
+            l += (l0 + l1) + (l2 + l3);
+            if (a.drop_thr) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const uint32_t bits = dropout_keep_bits(a.key, bh, (uint32_t)i, (uint32_t)(j * 8 + g), a.drop_thr);
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)
+                        if (!((bits >> c) & 1u)) SSET(g * 16 + c, 0.f);
+                }
+            }
+#pragma unroll
+            for (int c0 = 0; c0 < 2; ++c0) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int c = 0; c < 32; ++c) pk[c] = pack2<P_BF16>(SF(c0 * 64 + 2 * c), SF(c0 * 64 + 2 * c + 1));
+                tmem_st_32x32(tS + c0 * 32, pk);
+            }
+#undef SF
+#undef SSET
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&bars[Cfg::kPFull + t]);
+        }
+
+        if (n > 0) {
+            if (ok) ok = mbar_wait(&bars[Cfg::kODone + t], 0u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                tc_fence_after_sync();
+                const float inv = a.inv_keep / l;
+                uint8_t* stage = sQ + t * TILE;     // Q_t is dead once its last S MMA completed
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t orr[32];
+                    tmem_ld_32x32(tO + c0, orr);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 v4;
+                        v4.x = pack2<BF16>(__uint_as_float(orr[g * 8 + 0]) * inv, __uint_as_float(orr[g * 8 + 1]) * inv);
+                        v4.y = pack2<BF16>(__uint_as_float(orr[g * 8 + 2]) * inv, __uint_as_float(orr[g * 8 + 3]) * inv);
+                        v4.z = pack2<BF16>(__uint_as_float(orr[g * 8 + 4]) * inv, __uint_as_float(orr[g * 8 + 5]) * inv);
+                        v4.w = pack2<BF16>(__uint_as_float(orr[g * 8 + 6]) * inv, __uint_as_float(orr[g * 8 + 7]) * inv);
+                        const int col = c0 + g * 8;                 // first of 8 columns (16 bytes)
+                        const int chunk = (col & 63) >> 3;          // 16-byte chunk within the 128-byte row
+                        uint8_t* dst = stage + (col >> 6) * kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
+                        *reinterpret_cast<uint4*>(dst) = v4;
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(&bars[Cfg::kEpi + t]);
+                if (r == 0 && mbar_wait(&bars[Cfg::kEpi + t], 0u, abort_flag)) {
+                    // all 128 rows of the tile are staged (a bounded wait: rows of an
+                    // unwinding warp never arrive and the store is skipped)
+#pragma unroll
+                    for (int bx = 0; bx < Cfg::kNBox; ++bx)
+                        tma_store_4d(&map_o, stage + bx * kBoxBytes, bx * 64, h, tile * kBlockM, b);
+                    tma_store_commit();
+                    tma_store_wait_all<0>();
+                }
+                if (i < a.Nq) a.lse[((int64_t)b * a.H + h) * a.Nq + i] = kLn2 * (m + log2f(l));
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 8) tmem_dealloc(tmem, 512);
+    if (threadIdx.x == 0 && *abort_flag && a.status) atomicExch(a.status, 1);
 }
+
+template <int D, bool BF16>
+int launch(const fa_b200_params& p) {
+    using Cfg = FwdCfg<D>;
+    const CUtensorMapDataType dt = BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap mq, mk, mv, mo;
+    int r;
+    if ((r = make_tmap_bnhd(&mq, p.q.ptr, dt, 2, p.B, p.Nq, p.H, D, p.q.stride_b, p.q.stride_n, p.q.stride_h, 128, 64, true)) ||
+        (r = make_tmap_bnhd(&mk, p.k.ptr, dt, 2, p.B, p.Nk, p.Hkv, D, p.k.stride_b, p.k.stride_n, p.k.stride_h, 128, 64, true)) ||
+        (r = make_tmap_bnhd(&mv, p.v.ptr, dt, 2, p.B, p.Nk, p.Hkv, D, p.v.stride_b, p.v.stride_n, p.v.stride_h, 128, 64, true)) ||
+        (r = make_tmap_bnhd(&mo, p.o.ptr, dt, 2, p.B, p.Nq, p.H, D, p.o.stride_b, p.o.stride_n, p.o.stride_h, 128, 64, true))) {
+        set_error("cuTensorMapEncodeTiled failed (%d)", r);
+        return FA_ECUDA;
+    }
+    FwdArgs a;
+    a.lse = p.lse;
+    a.status = p.status_word;
+    a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv;
+    a.causal = p.causal;
+    a.scale_log2 = p.scale * kLog2e;
+    a.drop_thr = dropout_threshold(p.dropout_p);
+    a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
+    a.key = philox_make_key(p.seed, p.offset);
+    auto kernel = fwd_sm100_kernel<D, BF16>;
+    FA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    dim3 grid((p.Nq + 2 * kBlockM - 1) / (2 * kBlockM), p.H, p.B);
+    kernel<<<grid, kThreads, Cfg::kSmemBytes, (cudaStream_t)p.stream>>>(mq, mk, mv, mo, a);
+    FA_CUDA_CHECK(cudaGetLastError());
+    return FA_OK;
+}
+
+bool tensor_ok(const fa_b200_tensor& t, int64_t B, int64_t N, int64_t H) {
+    if (((uintptr_t)t.ptr & 15u) != 0) return false;
+    if (H > 1 && (t.stride_h % 8) != 0) return false;
+    if (N > 1 && (t.stride_n % 8) != 0) return false;
+    if (B > 1 && (t.stride_b % 8) != 0) return false;
+    return true;
+}
+
+}  // namespace
+
+// Which calls the tensor-core family covers.  `why` names the first reason it does not.
+bool sm100_supports(const fa_b200_params& p, bool backward, const char** why) {
+    if (p.dtype != FA_B200_F16 && p.dtype != FA_B200_BF16) { *why = "dtype must be fp16 or bf16"; return false; }
+    if (p.D != 64 && p.D != 128) { *why = "head_dim must be 64 or 128"; return false; }
+    if (!(p.scale > 0.f) || !(p.scale < 1e30f)) { *why = "scale must be positive and finite"; return false; }
+    if (p.B > 65535 || p.H > 65535) { *why = "batch and heads must be below 65536"; return false; }
+    if (backward) { *why = "backward on tensor cores is not built"; return false; }
+    if (!tensor_ok(p.q, p.B, p.Nq, p.H) || !tensor_ok(p.k, p.B, p.Nk, p.Hkv) ||
+        !tensor_ok(p.v, p.B, p.Nk, p.Hkv) || !tensor_ok(p.o, p.B, p.Nq, p.H)) {
+        *why = "tensors must be 16-byte aligned with strides that are multiples of 8 elements";
+        return false;
+    }
+    *why = "";
+    return true;
+}
+
+int sm100_fwd(const fa_b200_params& p) {
+    if (p.dtype == FA_B200_BF16) return p.D == 128 ? launch<128, true>(p) : launch<64, true>(p);
+    return p.D == 128 ? launch<128, false>(p) : launch<64, false>(p);
+}
+
+}  // namespace fa

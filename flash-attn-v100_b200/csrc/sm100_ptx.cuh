@@ -179,8 +179,10 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 //   bits 4-5 D format (1 = f32) | 7-9 A format | 10-12 B format (0 = f16, 1 = bf16)
 //   bit 15 A major | bit 16 B major (0 = K-major, 1 = MN-major)
 //   bits 17-22 N >> 3 | bits 24-28 M >> 4
-__host__ __device__ constexpr uint32_t make_idesc_f16(bool bf16, int M, int N, bool a_mn_major, bool b_mn_major) {
-    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) |
+// A and B carry their own format fields: an fp16 A may meet a bf16 B.
+__host__ __device__ constexpr uint32_t make_idesc_f16(bool a_bf16, bool b_bf16, int M, int N, bool a_mn_major,
+                                                      bool b_mn_major) {
+    return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) |
            ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
            ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
