@@ -1,4 +1,575 @@
+// Attention backward for sm_100a: TMA -> shared memory -> tcgen05.mma with
+// accumulators in tensor memory, warp-specialised.
+//
+// Replaces the reference's Triton backward kernel
+// (kernels/backward_kernel.py:17-205) and its launcher (:208-318).
+//
+// Three launches:
+//   1. preprocess  delta = rowsum(dO o O) and lse*log2(e), both fp32, written
+//                  to the workspace in rows padded to whole 128-row tiles
+//                  (padding: delta = 0, lse = +inf, so padded queries get P = 0)
+//   2. MODE 0      one CTA per 128-row key tile (stationary K, V), streams the
+//                  query tiles: writes dK and dV
+//   3. MODE 1      one CTA per 128-row query tile (stationary Q, dO), streams
+//                  the key tiles: writes dQ
+// Every output element is owned by one CTA and accumulated in a fixed order, so
+// results are bit-reproducible (the reference accumulates dQ across CTAs with
+// an unordered read-modify-write, kernels/backward_kernel.py:179-194).
+//
+// Both modes run the same pipeline on a stationary pair (X, Y) and a streamed
+// pair (U, W):
+//                         MODE 0 (dK, dV)          MODE 1 (dQ)
+//   X, Y                  K_j, V_j                 Q_i, dO_i
+//   U, W                  Q_i, dO_i                K_j, V_j
+//   T1 = X U^T            S^T                      S
+//   T2 = Y W^T            dP^T                     dP
+//   phase A (T1 -> P)     P^T = exp2(S^T c - lse)  P = exp2(S c - lse)
+//   phase B (T2 -> dS)    dS^T = P^T o (dP^T o Z - delta)
+//   ACC2 += P  W          dV += (P o Z)^T dO       (not computed)
+//   ACC1 += dS U          dK += dS^T Q             dQ += dS K
+// T1/T2 are SS MMAs (both operands K-major in shared memory); the accumulating
+// MMAs take P / dS from TMEM (written over T1 / T2 by the threads that read
+// them) and U / W from the same shared-memory tiles read MN-major.
+//
+//   warps 0-3, 4-7   one thread per TMEM lane (row); warpgroup g owns columns
+//                    [64g, 64g+64) of T1/T2
+//   warp 8           MMA issuer; order  T1(0) T2(0) | ACC2(i) T1(i+1) ACC1(i) T2(i+1) ...
+//   warp 9           TMA producer (tiles, and the lse/delta rows in MODE 0)
+//   warps 10-11      idle (complete the third warpgroup for setmaxnreg)
+//
+// TMEM columns: T1 [0,128)  T2 [128,256)  ACC1 [256,256+D)  ACC2 [384,384+D).
+// Every mbarrier wait is bounded; see sm100_ptx.cuh.
 #include "fa_common.cuh"
+#include "sm100_ptx.cuh"
+#include "tma_host.cuh"
+#include <type_traits>
+
 namespace fa {
-int sm100_bwd(const fa_b200_params& p, const BwdWorkspace& ws) { return FA_EUNSUPPORTED; }
+namespace {
+
+using namespace ptx;
+
+constexpr int kTile = 128;
+constexpr int kThreads = 384;
+constexpr int kBoxBytes = 128 * 128;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D>
+struct BwdCfg {
+    static constexpr int kNBox = D / 64;
+    static constexpr int kTileBytes = kNBox * kBoxBytes;
+    static constexpr int kStages = 2;
+    static constexpr int kStageBytes = 2 * kTileBytes + 1024;   // U, W, lse[128], delta[128]
+    static constexpr int kMaskBytes = 2 * 128 * 8 * 2;          // two buffers of 128 x 8 uint16 keep masks
+    static constexpr int kXYFull = 0;
+    static constexpr int kUWFull = 1;                            // [kStages]
+    static constexpr int kUWEmpty = kUWFull + kStages;           // [kStages]
+    static constexpr int kT1Full = kUWEmpty + kStages;
+    static constexpr int kT2Full = kT1Full + 1;
+    static constexpr int kPReady = kT2Full + 1;                  // count 256
+    static constexpr int kDsReady = kPReady + 1;                 // count 256
+    static constexpr int kAccDone = kDsReady + 1;
+    static constexpr int kMask = kAccDone + 1;                   // count 256
+    static constexpr int kEpi = kMask + 1;                       // count 256
+    static constexpr int kNumBars = kEpi + 1;
+    static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kStageBytes + kMaskBytes + kNumBars * 8 + 64 + 1024;
+};
+
+struct BwdArgs {
+    const float* lse2;     // [B*H][nq_pad]  lse * log2(e), +inf in the padding
+    const float* delta;    // [B*H][nq_pad]  0 in the padding
+    int32_t* status;
+    int B, Nq, Nk, H, Hkv, nq_pad;
+    int causal;
+    float scale, scale_log2;
+    uint32_t drop_thr;
+    float inv_keep;
+    PhiloxKey key;
+};
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
 }
+
+// MODE 0: dK, dV (key-stationary).  MODE 1: dQ (query-stationary).
+template <int D, bool BF16, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                 const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
+                 const __grid_constant__ CUtensorMap map_out1, const __grid_constant__ CUtensorMap map_out2,
+                 const BwdArgs a) {
+    using Cfg = BwdCfg<D>;
+    constexpr int ST = Cfg::kStages;
+    constexpr int TILE = Cfg::kTileBytes;
+    constexpr uint32_t kStageTx = (MODE == 0) ? (2 * TILE + 1024) : (2 * TILE);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sX = smem;
+    uint8_t* sY = sX + TILE;
+    uint8_t* sRing = sY + TILE;                     // stage s: U | W | lse[128] | delta[128]
+    uint16_t* sMask = (uint16_t*)(sRing + ST * Cfg::kStageBytes);
+    uint64_t* bars = (uint64_t*)((uint8_t*)sMask + Cfg::kMaskBytes);
+    uint32_t* tmem_slot = (uint32_t*)(bars + Cfg::kNumBars);
+    volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z;
+    const int group = a.H / a.Hkv;
+    const int nq_tiles = (a.Nq + kTile - 1) / kTile;
+
+    // iteration space (uniform over the CTA)
+    int tile, head_x, it0, n_per_head, n_iter;
+    if (MODE == 0) {
+        tile = blockIdx.x;                          // key tile
+        head_x = blockIdx.y;                        // kv head
+        it0 = a.causal ? tile : 0;                  // first query tile that sees this key tile
+        n_per_head = nq_tiles > it0 ? nq_tiles - it0 : 0;
+        n_iter = n_per_head * group;
+    } else {
+        tile = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;   // query tile, heavy first
+        head_x = blockIdx.y;                        // query head
+        it0 = 0;
+        int kv_end = a.Nk;
+        if (a.causal && tile * kTile + kTile < kv_end) kv_end = tile * kTile + kTile;
+        n_per_head = (kv_end + kTile - 1) / kTile;
+        n_iter = n_per_head;
+    }
+    const int head_kv = (MODE == 0) ? head_x : head_x / group;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < Cfg::kNumBars; ++i) {
+            const bool wide = (i == Cfg::kPReady || i == Cfg::kDsReady || i == Cfg::kMask || i == Cfg::kEpi);
+            mbar_init(&bars[i], wide ? 256u : 1u);
+        }
+        *abort_flag = 0u;
+        fence_mbar_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    if (warp == 9 && lane == 0) {
+        prefetch_tensormap(&map_x); prefetch_tensormap(&map_y);
+        prefetch_tensormap(&map_u); prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_out1);
+        if (MODE == 0) prefetch_tensormap(&map_out2);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tT1 = tmem, tT2 = tmem + 128u, tAcc1 = tmem + 256u, tAcc2 = tmem + 384u;
+
+    if (warp >= 8) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      if (warp == 9) {
+        // ---------------------------------------------------------------- TMA producer
+        if (elect_one()) {
+            int issued = 0;
+            bool ok = true;
+            if (n_iter > 0) {
+                mbar_expect_tx(&bars[Cfg::kXYFull], 2 * TILE);
+#pragma unroll
+                for (int bx = 0; bx < Cfg::kNBox; ++bx) {
+                    tma_load_4d(sX + bx * kBoxBytes, &map_x, &bars[Cfg::kXYFull], bx * 64, head_x, tile * kTile, b);
+                    tma_load_4d(sY + bx * kBoxBytes, &map_y, &bars[Cfg::kXYFull], bx * 64, head_x, tile * kTile, b);
+                }
+            }
+            for (int it = 0; it < n_iter; ++it) {
+                const int s = it % ST;
+                const uint32_t ph = (uint32_t)(it / ST) & 1u;
+                ok = mbar_wait(&bars[Cfg::kUWEmpty + s], ph ^ 1u, abort_flag);
+                if (!ok) break;
+                uint8_t* stage = sRing + s * Cfg::kStageBytes;
+                int head_u, row_u;
+                if (MODE == 0) { head_u = head_x * group + it / n_per_head; row_u = (it0 + it % n_per_head) * kTile; }
+                else           { head_u = head_kv; row_u = it * kTile; }
+                mbar_expect_tx(&bars[Cfg::kUWFull + s], kStageTx);
+#pragma unroll
+                for (int bx = 0; bx < Cfg::kNBox; ++bx) {
+                    tma_load_4d(stage + bx * kBoxBytes, &map_u, &bars[Cfg::kUWFull + s], bx * 64, head_u, row_u, b);
+                    tma_load_4d(stage + TILE + bx * kBoxBytes, &map_w, &bars[Cfg::kUWFull + s], bx * 64, head_u, row_u, b);
+                }
+                if (MODE == 0) {
+                    const int64_t off = ((int64_t)b * a.H + head_u) * a.nq_pad + row_u;
+                    bulk_load_1d(stage + 2 * TILE, a.lse2 + off, 512, &bars[Cfg::kUWFull + s]);
+                    bulk_load_1d(stage + 2 * TILE + 512, a.delta + off, 512, &bars[Cfg::kUWFull + s]);
+                }
+                ++issued;
+            }
+            if (!ok) {
+                // unwinding: let copies already issued land before shared memory is given up
+                for (int s = 0; s < ST; ++s) {
+                    const int nf = (issued + ST - 1 - s) / ST;
+                    for (int spin = 0; spin < 4096 && nf > 0 &&
+                         !mbar_try_wait(&bars[Cfg::kUWFull + s], (uint32_t)(nf - 1) & 1u); ++spin) {}
+                }
+                for (int spin = 0; spin < 4096 && n_iter > 0 && !mbar_try_wait(&bars[Cfg::kXYFull], 0u); ++spin) {}
+            }
+        }
+        __syncwarp();
+      } else if (warp == 8) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (elect_one() && n_iter > 0) {
+            constexpr uint32_t idesc_t = make_idesc_f16(BF16, BF16, kTile, kTile, false, false);
+            constexpr uint32_t idesc_acc = make_idesc_f16(BF16, BF16, kTile, D, false, true);
+            const uint32_t sX_u = smem_u32(sX), sY_u = smem_u32(sY), sRing_u = smem_u32(sRing);
+
+            auto issue_t = [&](uint32_t d_tmem, uint32_t stat_u, uint32_t strm_u) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (uint32_t)(kk >> 2) * kBoxBytes + (uint32_t)(kk & 3) * 32u;
+                    mma_ss_f16(d_tmem, make_smem_desc_sw128(stat_u + off, 0, 1024),
+                               make_smem_desc_sw128(strm_u + off, 0, 1024), idesc_t, kk > 0);
+                }
+            };
+            // acc (+)= A[TMEM: 16-bit pairs at a_tmem, second half of K at +64 columns] * B[smem tile, MN-major]
+            auto issue_acc = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t strm_u, bool acc) {
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk) {
+                    const uint32_t a_col = (kk < 4) ? (uint32_t)kk * 8u : 64u + (uint32_t)(kk - 4) * 8u;
+                    mma_ts_f16(d_tmem, a_tmem + a_col, make_smem_desc_sw128(strm_u + kk * 2048, kBoxBytes, 1024),
+                               idesc_acc, (acc || kk > 0) ? 1u : 0u);
+                }
+            };
+
+            bool ok = mbar_wait(&bars[Cfg::kXYFull], 0u, abort_flag);
+            if (ok) ok = mbar_wait(&bars[Cfg::kUWFull + 0], 0u, abort_flag);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_t(tT1, sX_u, sRing_u);
+                mma_commit(&bars[Cfg::kT1Full]);
+                issue_t(tT2, sY_u, sRing_u + TILE);
+                mma_commit(&bars[Cfg::kT2Full]);
+            }
+            for (int it = 0; it < n_iter && ok; ++it) {
+                const int s = it % ST, ns = (it + 1) % ST;
+                const uint32_t nph = (uint32_t)((it + 1) / ST) & 1u;
+                const uint32_t cur_u = sRing_u + s * Cfg::kStageBytes, nxt_u = sRing_u + ns * Cfg::kStageBytes;
+                const bool more = it + 1 < n_iter;
+                if (more) { ok = mbar_wait(&bars[Cfg::kUWFull + ns], nph, abort_flag); if (!ok) break; }
+                ok = mbar_wait(&bars[Cfg::kPReady], (uint32_t)it & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (MODE == 0) issue_acc(tAcc2, tT1, cur_u + TILE, it > 0);      // dV += (P o Z)^T dO
+                if (more) { issue_t(tT1, sX_u, nxt_u); mma_commit(&bars[Cfg::kT1Full]); }
+                ok = mbar_wait(&bars[Cfg::kDsReady], (uint32_t)it & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_acc(tAcc1, tT2, cur_u, it > 0);                            // dK += dS^T Q  /  dQ += dS K
+                mma_commit(&bars[Cfg::kUWEmpty + s]);
+                if (more) { issue_t(tT2, sY_u, nxt_u + TILE); mma_commit(&bars[Cfg::kT2Full]); }
+            }
+            if (ok) mma_commit(&bars[Cfg::kAccDone]);
+        }
+        __syncwarp();
+      }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        // ---------------------------------------------------------------- P / dS and epilogue
+        const int hf = warp >> 2;                              // column half
+        const int r = (warp & 3) * 32 + lane;                  // TMEM lane = row of T1/T2
+        const int cb = hf * 64;
+        const int tid = hf * 128 + r;                          // 0..255
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const int row_g = tile * kTile + r;                    // MODE 0: key index; MODE 1: query index
+        float my_lse2 = 0.f, my_delta = 0.f;
+        if (MODE == 1) {
+            const int64_t off = ((int64_t)b * a.H + head_x) * a.nq_pad + row_g;
+            my_lse2 = a.lse2[off];
+            my_delta = a.delta[off];
+        }
+        bool ok = true;
+
+        for (int it = 0; it < n_iter; ++it) {
+            const int s = it % ST;
+            const uint8_t* stage = sRing + s * Cfg::kStageBytes;
+            const float* lse_s = reinterpret_cast<const float*>(stage + 2 * TILE);
+            const float* del_s = lse_s + 128;
+            const int strm_tile = (MODE == 0) ? it0 + it % n_per_head : it;     // query tile (0) / key tile (1)
+            const int col_g0 = strm_tile * kTile + cb;                          // global index of my first column
+            const int head_q = (MODE == 0) ? head_x * group + it / n_per_head : head_x;
+            const uint32_t bh = (uint32_t)(b * a.H + head_q);
+
+            // ---- dropout keep bits of my 64 columns
+            uint32_t kb0 = 0xFFFFFFFFu, kb1 = 0xFFFFFFFFu;
+            if (a.drop_thr) {
+                if (MODE == 1) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int g = 0; g < 4; ++g)
+                        w[g] = dropout_keep_bits(a.key, bh, (uint32_t)row_g, (uint32_t)((col_g0 >> 4) + g), a.drop_thr);
+                    kb0 = w[0] | (w[1] << 16);
+                    kb1 = w[2] | (w[3] << 16);
+                } else {
+                    // keys are rows here: build the tile's masks cooperatively, query-major, then read
+                    // one bit per (query column, my key row)
+                    uint16_t* mbuf = sMask + (it & 1) * (128 * 8);
+                    const int ql = tid & 127, jb0 = (tid >> 7) * 4;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g)
+                        mbuf[ql * 8 + jb0 + g] = (uint16_t)dropout_keep_bits(
+                            a.key, bh, (uint32_t)(strm_tile * kTile + ql), (uint32_t)(tile * 8 + jb0 + g), a.drop_thr);
+                    mbar_arrive(&bars[Cfg::kMask]);
+                    ok = mbar_wait(&bars[Cfg::kMask], (uint32_t)it & 1u, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    kb0 = 0u; kb1 = 0u;
+                    const int jw = r >> 4, jbit = r & 15;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        kb0 |= (((uint32_t)mbuf[(cb + c) * 8 + jw] >> jbit) & 1u) << c;
+                        kb1 |= (((uint32_t)mbuf[(cb + 32 + c) * 8 + jw] >> jbit) & 1u) << c;
+                    }
+                }
+            }
+
+            // ---- phase A: P from T1
+            ok = mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t pr[2][32];        // P of my 64 columns (fp32 bits), kept for phase B
+#define PF(c) __uint_as_float(pr[(c) >> 5][(c) & 31])
+#define PSET(c, x) pr[(c) >> 5][(c) & 31] = __float_as_uint(x)
+            tmem_ld_32x32(tT1 + lane_off + cb, pr[0]);
+            tmem_ld_32x32(tT1 + lane_off + cb + 32, pr[1]);
+            tmem_wait_ld();
+            if (MODE == 0) {
+                const float4* l4 = reinterpret_cast<const float4*>(lse_s + cb);
+#pragma unroll
+                for (int c4 = 0; c4 < 16; ++c4) {
+                    const float4 L = l4[c4];
+                    PSET(c4 * 4 + 0, ex2(fmaf(PF(c4 * 4 + 0), a.scale_log2, -L.x)));
+                    PSET(c4 * 4 + 1, ex2(fmaf(PF(c4 * 4 + 1), a.scale_log2, -L.y)));
+                    PSET(c4 * 4 + 2, ex2(fmaf(PF(c4 * 4 + 2), a.scale_log2, -L.z)));
+                    PSET(c4 * 4 + 3, ex2(fmaf(PF(c4 * 4 + 3), a.scale_log2, -L.w)));
+                }
+                if (a.causal && strm_tile == tile) {       // diagonal tile: key row > query column is hidden
+#pragma unroll
+                    for (int c = 0; c < 64; ++c)
+                        if (row_g > col_g0 + c) PSET(c, 0.f);
+                }
+            } else {
+                const float neg = -my_lse2;
+#pragma unroll
+                for (int c = 0; c < 64; ++c) PSET(c, ex2(fmaf(PF(c), a.scale_log2, neg)));
+                const bool diag = a.causal && strm_tile == tile;
+                if (diag || strm_tile * kTile + kTile > a.Nk) {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {
+                        const int col = col_g0 + c;
+                        if (col >= a.Nk || (diag && col > row_g)) PSET(c, 0.f);
+                    }
+                }
+            }
+            if (MODE == 0) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    float x0 = PF(2 * c), x1 = PF(2 * c + 1);
+                    const uint32_t kbits = (c < 16) ? kb0 : kb1;
+                    if (!((kbits >> ((2 * c) & 31)) & 1u)) x0 = 0.f;
+                    if (!((kbits >> ((2 * c + 1) & 31)) & 1u)) x1 = 0.f;
+                    pk[c] = pack2<BF16>(x0, x1);
+                }
+                tmem_st_32x32(tT1 + lane_off + cb, pk);
+                tmem_wait_st();
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&bars[Cfg::kPReady]);
+
+            // ---- phase B: dS from T2
+            ok = mbar_wait(&bars[Cfg::kT2Full], (uint32_t)it & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            {
+                uint32_t dr[2][32];
+                tmem_ld_32x32(tT2 + lane_off + cb, dr[0]);
+                tmem_ld_32x32(tT2 + lane_off + cb + 32, dr[1]);
+                tmem_wait_ld();
+                uint32_t pk[32];
+                const float4* d4 = reinterpret_cast<const float4*>(del_s + cb);
+#pragma unroll
+                for (int c4 = 0; c4 < 16; ++c4) {
+                    float4 dl;
+                    if (MODE == 0) dl = d4[c4];
+                    else dl = make_float4(my_delta, my_delta, my_delta, my_delta);
+                    const float dlt[4] = {dl.x, dl.y, dl.z, dl.w};
+                    float ds[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = c4 * 4 + e;
+                        const uint32_t kbits = (c < 32) ? kb0 : kb1;
+                        const float z = ((kbits >> (c & 31)) & 1u) ? a.inv_keep : 0.f;
+                        const float dp = __uint_as_float(dr[c >> 5][c & 31]);
+                        ds[e] = PF(c) * fmaf(dp, z, -dlt[e]);
+                    }
+                    pk[c4 * 2 + 0] = pack2<BF16>(ds[0], ds[1]);
+                    pk[c4 * 2 + 1] = pack2<BF16>(ds[2], ds[3]);
+                }
+                tmem_st_32x32(tT2 + lane_off + cb, pk);
+                tmem_wait_st();
+            }
+#undef PF
+#undef PSET
+            tc_fence_before_sync();
+            mbar_arrive(&bars[Cfg::kDsReady]);
+        }
+
+        // ---- epilogue: accumulators -> 16-bit -> swizzled staging -> TMA store
+        if (n_iter > 0 && ok) ok = mbar_wait(&bars[Cfg::kAccDone], 0u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after_sync();
+            constexpr int kColsPerThread = D / 2;              // my share of the D accumulator columns
+            constexpr int kOuts = (MODE == 0) ? 2 : 1;
+#pragma unroll
+            for (int o = 0; o < kOuts; ++o) {
+                const uint32_t tacc = (o == 0 ? tAcc1 : tAcc2) + lane_off + (uint32_t)(hf * kColsPerThread);
+                const float mul = (o == 0) ? a.scale : a.inv_keep;
+                uint8_t* stage = sRing + o * TILE;             // ring stage 0 is idle once all MMAs completed
+#pragma unroll
+                for (int c0 = 0; c0 < kColsPerThread; c0 += 32) {
+                    uint32_t acc[32];
+                    if (n_iter > 0) {
+                        tmem_ld_32x32(tacc + c0, acc);
+                        tmem_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) acc[c] = 0u;    // no query sees this key tile
+                    }
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 v4;
+                        v4.x = pack2<BF16>(__uint_as_float(acc[g * 8 + 0]) * mul, __uint_as_float(acc[g * 8 + 1]) * mul);
+                        v4.y = pack2<BF16>(__uint_as_float(acc[g * 8 + 2]) * mul, __uint_as_float(acc[g * 8 + 3]) * mul);
+                        v4.z = pack2<BF16>(__uint_as_float(acc[g * 8 + 4]) * mul, __uint_as_float(acc[g * 8 + 5]) * mul);
+                        v4.w = pack2<BF16>(__uint_as_float(acc[g * 8 + 6]) * mul, __uint_as_float(acc[g * 8 + 7]) * mul);
+                        const int col = hf * kColsPerThread + c0 + g * 8;
+                        const int chunk = (col & 63) >> 3;
+                        uint8_t* dst = stage + (col >> 6) * kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
+                        *reinterpret_cast<uint4*>(dst) = v4;
+                    }
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(&bars[Cfg::kEpi]);
+            if (tid == 0 && mbar_wait(&bars[Cfg::kEpi], 0u, abort_flag)) {
+#pragma unroll
+                for (int bx = 0; bx < Cfg::kNBox; ++bx) {
+                    tma_store_4d(&map_out1, sRing + bx * kBoxBytes, bx * 64, head_x, tile * kTile, b);
+                    if (MODE == 0)
+                        tma_store_4d(&map_out2, sRing + TILE + bx * kBoxBytes, bx * 64, head_x, tile * kTile, b);
+                }
+                tma_store_commit();
+                tma_store_wait_all<0>();
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 8) tmem_dealloc(tmem, 512);
+    if (threadIdx.x == 0 && *abort_flag && a.status) atomicExch(a.status, 2 + MODE);
+}
+
+// delta and scaled lse, one warp per (b, h, padded query row)
+template <typename T>
+__global__ void __launch_bounds__(256)
+bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
+                      float* __restrict__ lse2, float* __restrict__ delta, int B, int Nq, int H, int D, int nq_pad,
+                      int64_t o_sb, int64_t o_sn, int64_t o_sh, int64_t g_sb, int64_t g_sn, int64_t g_sh) {
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= (int64_t)B * H * nq_pad) return;
+    const int i = (int)(row % nq_pad);
+    const int64_t bh = row / nq_pad;
+    const int h = (int)(bh % H), b = (int)(bh / H);
+    if (i >= Nq) {
+        if (lane == 0) { lse2[row] = INFINITY; delta[row] = 0.f; }
+        return;
+    }
+    const T* po = o + b * o_sb + i * o_sn + h * o_sh;
+    const T* pg = d_o + b * g_sb + i * g_sn + h * g_sh;
+    float s = 0.f;
+    if (lane * 8 < D) {        // 16-byte vectors: 8 elements per lane
+        const uint4 vo = *reinterpret_cast<const uint4*>(po + lane * 8);
+        const uint4 vg = *reinterpret_cast<const uint4*>(pg + lane * 8);
+        const T* eo = reinterpret_cast<const T*>(&vo);
+        const T* eg = reinterpret_cast<const T*>(&vg);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(eo[e]), to_f32<T>(eg[e]), s);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (lane == 0) {
+        delta[row] = s;
+        lse2[row] = lse[bh * Nq + i] * kLog2e;
+    }
+}
+
+template <int D, bool BF16>
+int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
+    using Cfg = BwdCfg<D>;
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    const CUtensorMapDataType dt = BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    cudaStream_t st = (cudaStream_t)p.stream;
+    const int nq_pad = (int)align_up((size_t)p.Nq, 128);
+    float* delta = (float*)((char*)p.workspace + ws.delta_off);
+    float* lse2 = (float*)((char*)p.workspace + ws.lse2_off);
+
+    const int64_t rows = (int64_t)p.B * p.H * nq_pad;
+    bwd_preprocess_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+        (const T*)p.o.ptr, (const T*)p.d_o.ptr, p.lse, lse2, delta, p.B, p.Nq, p.H, D, nq_pad,
+        p.o.stride_b, p.o.stride_n, p.o.stride_h, p.d_o.stride_b, p.d_o.stride_n, p.d_o.stride_h);
+    FA_CUDA_CHECK(cudaGetLastError());
+
+    CUtensorMap mq, mk, mv, mg, mdq, mdk, mdv;
+    int r;
+    auto mk_map = [&](CUtensorMap* m, const fa_b200_tensor& t, int N, int H) {
+        return make_tmap_bnhd(m, t.ptr, dt, 2, p.B, N, H, D, t.stride_b, t.stride_n, t.stride_h, 128, 64, true);
+    };
+    if ((r = mk_map(&mq, p.q, p.Nq, p.H)) || (r = mk_map(&mk, p.k, p.Nk, p.Hkv)) ||
+        (r = mk_map(&mv, p.v, p.Nk, p.Hkv)) || (r = mk_map(&mg, p.d_o, p.Nq, p.H)) ||
+        (r = mk_map(&mdq, p.dq, p.Nq, p.H)) || (r = mk_map(&mdk, p.dk, p.Nk, p.Hkv)) ||
+        (r = mk_map(&mdv, p.dv, p.Nk, p.Hkv))) {
+        set_error("cuTensorMapEncodeTiled failed (%d)", r);
+        return FA_ECUDA;
+    }
+    BwdArgs a;
+    a.lse2 = lse2; a.delta = delta; a.status = p.status_word;
+    a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv; a.nq_pad = nq_pad;
+    a.causal = p.causal;
+    a.scale = p.scale;
+    a.scale_log2 = p.scale * kLog2e;
+    a.drop_thr = dropout_threshold(p.dropout_p);
+    a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
+    a.key = philox_make_key(p.seed, p.offset);
+
+    auto k0 = bwd_sm100_kernel<D, BF16, 0>;
+    auto k1 = bwd_sm100_kernel<D, BF16, 1>;
+    FA_CUDA_CHECK(cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    FA_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    dim3 grid_kv((p.Nk + kTile - 1) / kTile, p.Hkv, p.B);
+    k0<<<grid_kv, kThreads, Cfg::kSmemBytes, st>>>(mk, mv, mq, mg, mdk, mdv, a);
+    FA_CUDA_CHECK(cudaGetLastError());
+    dim3 grid_q((p.Nq + kTile - 1) / kTile, p.H, p.B);
+    k1<<<grid_q, kThreads, Cfg::kSmemBytes, st>>>(mq, mg, mk, mv, mdq, mdq, a);
+    FA_CUDA_CHECK(cudaGetLastError());
+    return FA_OK;
+}
+
+}  // namespace
+
+int sm100_bwd(const fa_b200_params& p, const BwdWorkspace& ws) {
+    if (p.dtype == FA_B200_BF16) return p.D == 128 ? launch<128, true>(p, ws) : launch<64, true>(p, ws);
+    return p.D == 128 ? launch<128, false>(p, ws) : launch<64, false>(p, ws);
+}
+
+}  // namespace fa

@@ -39,10 +39,11 @@ static inline size_t dtype_bytes(int dtype) { return dtype == FA_B200_F32 ? 4 : 
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // ---- workspace layout (backward) -------------------------------------------
-// [ delta : B*H*Nq fp32 | pad to 256 | dq_accum : B*Nq*H*D fp32 (tcgen05 only) ]
+// [ delta : B*H*nq_pad fp32 | pad to 256 | lse*log2(e) : B*H*nq_pad fp32 (tensor-core family only) ]
+// nq_pad = Nq rounded up to 128; the CUDA-core family indexes delta unpadded.
 struct BwdWorkspace {
     size_t delta_off, delta_bytes;
-    size_t dq_accum_off, dq_accum_bytes;
+    size_t lse2_off, lse2_bytes;
     size_t total;
 };
 BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant);

@@ -461,9 +461,10 @@ bool sm100_supports(const fa_b200_params& p, bool backward, const char** why) {
     if (p.D != 64 && p.D != 128) { *why = "head_dim must be 64 or 128"; return false; }
     if (!(p.scale > 0.f) || !(p.scale < 1e30f)) { *why = "scale must be positive and finite"; return false; }
     if (p.B > 65535 || p.H > 65535) { *why = "batch and heads must be below 65536"; return false; }
-    if (backward) { *why = "backward on tensor cores is not built"; return false; }
     if (!tensor_ok(p.q, p.B, p.Nq, p.H) || !tensor_ok(p.k, p.B, p.Nk, p.Hkv) ||
-        !tensor_ok(p.v, p.B, p.Nk, p.Hkv) || !tensor_ok(p.o, p.B, p.Nq, p.H)) {
+        !tensor_ok(p.v, p.B, p.Nk, p.Hkv) || !tensor_ok(p.o, p.B, p.Nq, p.H) ||
+        (backward && (!tensor_ok(p.d_o, p.B, p.Nq, p.H) || !tensor_ok(p.dq, p.B, p.Nq, p.H) ||
+                      !tensor_ok(p.dk, p.B, p.Nk, p.Hkv) || !tensor_ok(p.dv, p.B, p.Nk, p.Hkv)))) {
         *why = "tensors must be 16-byte aligned with strides that are multiples of 8 elements";
         return false;
     }

@@ -20,16 +20,12 @@ void set_error(const char* fmt, ...) {
 
 BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant) {
     BwdWorkspace w;
+    const size_t nq_pad = align_up((size_t)p.Nq, 128);
     w.delta_off = 0;
-    w.delta_bytes = (size_t)p.B * p.H * p.Nq * sizeof(float);
-    w.dq_accum_off = align_up(w.delta_bytes, 256);
-    w.dq_accum_bytes = 0;
-    if (variant == FA_B200_VARIANT_TCGEN05) {
-        // fp32 dQ accumulator, rows padded to whole 128-row tiles per (b, h)
-        size_t nq_pad = align_up((size_t)p.Nq, 128);
-        w.dq_accum_bytes = (size_t)p.B * p.H * nq_pad * p.D * sizeof(float);
-    }
-    w.total = w.dq_accum_off + w.dq_accum_bytes;
+    w.delta_bytes = (size_t)p.B * p.H * nq_pad * sizeof(float);
+    w.lse2_off = align_up(w.delta_bytes, 256);
+    w.lse2_bytes = (variant == FA_B200_VARIANT_TCGEN05) ? w.delta_bytes : 0;
+    w.total = w.lse2_off + w.lse2_bytes;
     if (w.total == 0) w.total = 256;
     return w;
 }
