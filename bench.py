@@ -1,0 +1,367 @@
+"""Benchmark of the attention hot path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3]
+
+N > 1 is launched with torch.distributed.run (one rank per GPU); the (batch x
+heads) grid has no exchange step, so every rank runs an independent shard of
+the same shape (weak scaling) and NCCL is used only for the barrier and the
+max-over-ranks reduction of the timings.  Rank 0 prints ONE JSON line.
+
+A step is one forward + backward pass of the workload (default: B4 N4096 H32
+D128 bf16 causal, the Llama-7B-like layer) through the public API.  `value` is
+device-resident throughput in TFLOP/s (4*B*H*N^2*D forward, 2.5x that backward,
+halved when causal); `e2e` repeats the measurement with the step's inputs
+copied from pinned host memory and its results copied back inside the timed
+region.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "flash-attn-v100_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+METRIC = "attention_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+# ----------------------------------------------------------------------------- helpers
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.12)
+            self.proc.terminate()          # the exact child started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        return False
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), "measured (cuBLAS bf16 burst, MEASURED_PEAKS.json)", d
+    except (OSError, KeyError, ValueError):
+        return FALLBACK_BF16_TFLOPS, "fallback (earlier measurement on this pool)", {}
+
+
+def ncu_traffic(kernel: str):
+    """DRAM bytes per launch of a kernel from the committed ncu summary, if any."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            return json.load(f).get(kernel)
+    except (OSError, ValueError):
+        return None
+
+
+def time_steps(fn, steps: int, device, world: int):
+    """ms per step of `fn`, CUDA events on the current stream, max over ranks."""
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+# ----------------------------------------------------------------------------- CPU side
+def cpu_reference_throughput(w, budget_s: float = 12.0, max_heads: int = 64):
+    """The reference's PyTorch math attention path (restated in oracle/) timed on
+    this box's host cores, forward + backward through autograd, on a bounded
+    sample of (batch, head) columns of the workload.  Returns (TFLOP/s, cores, sample)."""
+    from flash_attention_v100.testing import make_inputs
+    from oracle import attention_oracle as ao
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    one = w.shrink(B=1, H=1)
+    t = make_inputs(one)
+    args = [t[n].float() for n in ("q", "k", "v", "d_o")]
+    ao.attention_forward_backward(*args, causal=w.causal, scale=w.scale)       # warm-up
+    done, t0 = 0, time.perf_counter()
+    while done < max_heads and (time.perf_counter() - t0 < budget_s or done == 0):
+        ao.attention_forward_backward(*args, causal=w.causal, scale=w.scale)
+        done += 1
+    elapsed = time.perf_counter() - t0
+    flops = (one.fwd_flops() + one.bwd_flops()) * done
+    sample = (f"{done} of {w.B * w.H} (batch, head) columns of {w.name}, fp32 math path "
+              f"(dense N x N scores), {elapsed:.1f} s")
+    return flops / elapsed / 1e12, cores, sample, elapsed / done
+
+
+def run_reference(args, w):
+    """--impl reference: the reference's own CPU implementation of the path.  The
+    reference is pure Python (nothing to compile into oracle/_ref) and its tree is
+    not present on the GPU box, so the oracle port stands in (kind "port")."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ms = []
+    value = cores = sample = None
+    for _ in range(max(1, min(args.steps, 3))):
+        value, cores, sample, per_col = cpu_reference_throughput(w, budget_s=8.0, max_heads=48)
+        ms.append(per_col * 1e3 * w.B * w.H)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": statistics.median(ms),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": w.name, "parallelism": "host cores only",
+                   "note": "ms_per_step extrapolated from the sampled columns to the whole workload"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- GPU side
+def run_ours(args, w):
+    import flash_attention_v100 as fa
+    from flash_attention_v100.kernels import _cabi
+    from flash_attention_v100.ops import attention as ops
+    from flash_attention_v100.testing import make_inputs, DROPOUT_SEED, DROPOUT_OFFSET
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    _cabi.load()
+
+    host = make_inputs(w, seed=w.seed + rank, pin=True)              # pinned host copies
+    dev = {n: t.to(device, non_blocking=True) for n, t in host.items()}
+    torch.cuda.synchronize(device)
+    stream = (DROPOUT_SEED, DROPOUT_OFFSET)
+
+    q, k, v = (dev[n].requires_grad_(True) for n in ("q", "k", "v"))
+
+    def step():
+        if w.dropout_p > 0:
+            fa.set_dropout_seed(*stream)
+        o = fa.flash_attention_v100(q, k, v, causal=w.causal, scale=w.scale, dropout_p=w.dropout_p,
+                                    enable_multi_gpu=False)
+        o.backward(dev["d_o"])
+        q.grad = k.grad = v.grad = None
+        return o
+
+    # e2e: host -> device copies of the step's inputs and device -> host reads of its results
+    stage = {n: torch.empty_like(dev[n]) for n in ("q", "k", "v", "d_o")}
+    back = {n: torch.empty(host["q"].shape, dtype=w.dtype).pin_memory() for n in ("o", "dq", "dk", "dv")}
+
+    def step_e2e():
+        for n in ("q", "k", "v", "d_o"):
+            stage[n].copy_(host[n], non_blocking=True)
+        qq, kk, vv = (stage[n].detach().requires_grad_(True) for n in ("q", "k", "v"))
+        if w.dropout_p > 0:
+            fa.set_dropout_seed(*stream)
+        o = fa.flash_attention_v100(qq, kk, vv, causal=w.causal, scale=w.scale, dropout_p=w.dropout_p,
+                                    enable_multi_gpu=False)
+        o.backward(stage["d_o"])
+        back["o"].copy_(o.detach(), non_blocking=True)
+        back["dq"].copy_(qq.grad, non_blocking=True)
+        back["dk"].copy_(kk.grad, non_blocking=True)
+        back["dv"].copy_(vv.grad, non_blocking=True)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    with ClockSampler(local) as clocks:
+        ms_step = time_steps(step, args.steps, device, world)
+    clock_info = clocks.summary()
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = time_steps(step_e2e, max(3, args.steps // 2), device, world)
+
+    # per-kernel timing, each launch alone (live CUDA events), for the roofline
+    with torch.no_grad():
+        o, lse = ops.launch_forward(dev["q"], dev["k"], dev["v"], w.scale, w.causal, w.dropout_p, *stream)
+    p = ops._base_params(dev["q"].detach(), dev["k"].detach(), dev["v"].detach(), o, lse, w.scale, w.causal,
+                         w.dropout_p, *stream)
+    grads = [torch.empty_like(dev[n]) for n in ("q", "k", "v")]
+    p.d_o = ops._tensor4(dev["d_o"])
+    p.dq, p.dk, p.dv = (ops._tensor4(g) for g in grads)
+    lib = _cabi.load()
+    nbytes = int(lib.fa_b200_bwd_workspace_bytes(ctypes.byref(p)))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), nbytes
+
+    def call(fn, phases):
+        def run():
+            p.bwd_phases = phases
+            rc = fn(ctypes.byref(p))
+            if rc != 0:
+                _cabi.raise_for_status(rc, "bench")
+        return run
+
+    call(lib.fa_b200_bwd, 0)()
+    ksteps = max(5, args.steps)
+    kern_ms = {
+        "fwd": time_steps(call(lib.fa_b200_fwd, 0), ksteps, device, world),
+        "bwd_preprocess": time_steps(call(lib.fa_b200_bwd, 1), ksteps, device, world),
+        "bwd_dkdv": time_steps(call(lib.fa_b200_bwd, 2), ksteps, device, world),
+        "bwd_dq": time_steps(call(lib.fa_b200_bwd, 4), ksteps, device, world),
+    }
+    p.bwd_phases = 0
+    status = ops._status_word(device)
+
+    unit_gemm = w.fwd_flops() / 2.0            # one N x N x D GEMM over the workload (causal-halved)
+    kernels = {
+        # name: (ms, GEMMs counted by the metric's FLOP formula, GEMMs the kernel executes)
+        "fwd": (kern_ms["fwd"], 2, 2),
+        "bwd_dkdv": (kern_ms["bwd_dkdv"], 4, 4),
+        "bwd_dq": (kern_ms["bwd_dq"], 1, 3),    # S and dP are recomputed here: executed, not counted
+    }
+    peak, peak_kind, peaks_file = measured_peak()
+    dom = max(kernels, key=lambda n: kernels[n][0])
+    dom_ms, dom_alg, dom_exec = kernels[dom]
+    achieved = dom_alg * unit_gemm / (dom_ms * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+        "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS,
+        "executed_tflops": dom_exec * unit_gemm / (dom_ms * 1e-3) / 1e12,
+        "traffic": ncu_traffic(dom),
+        "per_kernel_ms": kern_ms,
+        "per_kernel_tflops_counted": {n: a * unit_gemm / (ms * 1e-3) / 1e12 for n, (ms, a, _) in kernels.items()},
+    }
+
+    total_flops = (w.fwd_flops() + w.bwd_flops()) * world
+    value = total_flops / (ms_step * 1e-3) / 1e12
+    e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
+    tb = w.tensor_bytes()
+    fwd_tf = w.fwd_flops() / (kern_ms["fwd"] * 1e-3) / 1e12
+    bwd_ms = kern_ms["bwd_preprocess"] + kern_ms["bwd_dkdv"] + kern_ms["bwd_dq"]
+    bwd_tf = w.bwd_flops() / (bwd_ms * 1e-3) / 1e12
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        v_cpu, cores, sample, _ = cpu_reference_throughput(w)
+        cpu = {"value": v_cpu, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": {torch.bfloat16: "bf16", torch.float16: "f16", torch.float32: "f32"}[w.dtype],
+            "data": "synthetic",
+            "config": {
+                "workload": w.name, "B": w.B, "N": w.N, "H": w.H, "D": w.D, "causal": w.causal,
+                "dropout_p": w.dropout_p, "per_gpu": "every rank runs this shape (its own seeded shard)",
+                "parallelism": f"(batch x heads) shards, {world} rank(s), no data-path collective",
+                "l2": "not flushed: q, k, v, o, dO, dQ, dK, dV are %.0f MB each, larger than the 126 MB L2" % (tb / 1e6),
+            },
+            "per_gpu_tflops": value / world,
+            "frac_of_nominal_bf16_peak": value / world / NOMINAL_BF16_TFLOPS,
+            "frac_of_measured_bf16_peak": value / world / peak,
+            "fwd_tflops": fwd_tf, "bwd_tflops": bwd_tf,
+            "roofline": roofline,
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": 4 * tb, "d2h_bytes_per_step": 4 * tb},
+            "gpu_launches": 4 * args.steps,     # per step: 1 forward + 3 backward kernels of this library
+            "clocks": clock_info,
+            "status_word": int(status.item()),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", default="cfg3")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=None, help="override the workload's batch (small profiling cases)")
+    ap.add_argument("--heads", type=int, default=None, help="override the workload's head count")
+    args = ap.parse_args()
+    from flash_attention_v100.testing import WORKLOADS
+    w = WORKLOADS[args.workload]
+    if args.batch is not None or args.heads is not None:
+        b, h = args.batch or w.B, args.heads or w.H
+        w = w.shrink(B=b, H=h, name=f"{w.name} [reduced to B{b} H{h}: not the benchmark size]")
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

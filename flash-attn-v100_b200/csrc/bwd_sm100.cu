@@ -524,11 +524,14 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     float* delta = (float*)((char*)p.workspace + ws.delta_off);
     float* lse2 = (float*)((char*)p.workspace + ws.lse2_off);
 
-    const int64_t rows = (int64_t)p.B * p.H * nq_pad;
-    bwd_preprocess_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
-        (const T*)p.o.ptr, (const T*)p.d_o.ptr, p.lse, lse2, delta, p.B, p.Nq, p.H, D, nq_pad,
-        p.o.stride_b, p.o.stride_n, p.o.stride_h, p.d_o.stride_b, p.d_o.stride_n, p.d_o.stride_h);
-    FA_CUDA_CHECK(cudaGetLastError());
+    const int phases = p.bwd_phases ? p.bwd_phases : 7;
+    if (phases & 1) {
+        const int64_t rows = (int64_t)p.B * p.H * nq_pad;
+        bwd_preprocess_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+            (const T*)p.o.ptr, (const T*)p.d_o.ptr, p.lse, lse2, delta, p.B, p.Nq, p.H, D, nq_pad,
+            p.o.stride_b, p.o.stride_n, p.o.stride_h, p.d_o.stride_b, p.d_o.stride_n, p.d_o.stride_h);
+        FA_CUDA_CHECK(cudaGetLastError());
+    }
 
     CUtensorMap mq, mk, mv, mg, mdq, mdk, mdv;
     int r;
@@ -556,12 +559,16 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     auto k1 = bwd_sm100_kernel<D, BF16, 1>;
     FA_CUDA_CHECK(cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     FA_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    dim3 grid_kv((p.Nk + kTile - 1) / kTile, p.Hkv, p.B);
-    k0<<<grid_kv, kThreads, Cfg::kSmemBytes, st>>>(mk, mv, mq, mg, mdk, mdv, a);
-    FA_CUDA_CHECK(cudaGetLastError());
-    dim3 grid_q((p.Nq + kTile - 1) / kTile, p.H, p.B);
-    k1<<<grid_q, kThreads, Cfg::kSmemBytes, st>>>(mq, mg, mk, mv, mdq, mdq, a);
-    FA_CUDA_CHECK(cudaGetLastError());
+    if (phases & 2) {
+        dim3 grid_kv((p.Nk + kTile - 1) / kTile, p.Hkv, p.B);
+        k0<<<grid_kv, kThreads, Cfg::kSmemBytes, st>>>(mk, mv, mq, mg, mdk, mdv, a);
+        FA_CUDA_CHECK(cudaGetLastError());
+    }
+    if (phases & 4) {
+        dim3 grid_q((p.Nq + kTile - 1) / kTile, p.H, p.B);
+        k1<<<grid_q, kThreads, Cfg::kSmemBytes, st>>>(mq, mg, mk, mv, mdq, mdq, a);
+        FA_CUDA_CHECK(cudaGetLastError());
+    }
     return FA_OK;
 }
 

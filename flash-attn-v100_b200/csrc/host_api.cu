@@ -82,6 +82,7 @@ int validate_common(const fa_b200_params* p, bool backward) {
         return FA_EINVAL;
     }
     if (!(p->scale == p->scale)) { set_error("scale is NaN"); return FA_EINVAL; }
+    if (p->bwd_phases < 0 || p->bwd_phases > 7) { set_error("bwd_phases must be a mask in [0, 7]"); return FA_EINVAL; }
     if (p->B == 0 || p->Nq == 0) return FA_OK;   // empty problem: nothing else to check
     int rc;
     if ((rc = check_tensor(p->q, "q", true))) return rc;

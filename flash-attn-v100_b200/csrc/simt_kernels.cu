@@ -463,19 +463,26 @@ int launch_bwd(const fa_b200_params& p, const BwdWorkspace& ws) {
     SimtArgs a = make_args(p, delta);
     cudaStream_t st = (cudaStream_t)p.stream;
     int64_t rows = (int64_t)p.B * p.H * p.Nq;
-    simt_delta_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(a);
-    FA_CUDA_CHECK(cudaGetLastError());
+    const int phases = p.bwd_phases ? p.bwd_phases : 7;
+    if (phases & 1) {
+        simt_delta_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(a);
+        FA_CUDA_CHECK(cudaGetLastError());
+    }
     size_t smem = ((size_t)(2 * BM + 2 * BN) * (p.D + 1) + (size_t)2 * BM * SLD + 2 * BM) * sizeof(float);
     int rc = set_smem(simt_bwd_kernel<T, 0>, smem);
     if (rc) return rc;
     rc = set_smem(simt_bwd_kernel<T, 1>, smem);
     if (rc) return rc;
-    dim3 grid_kv((p.Nk + BN - 1) / BN, p.Hkv, p.B);
-    simt_bwd_kernel<T, 0><<<grid_kv, NT, smem, st>>>(a);
-    FA_CUDA_CHECK(cudaGetLastError());
-    dim3 grid_q((p.Nq + BM - 1) / BM, p.H, p.B);
-    simt_bwd_kernel<T, 1><<<grid_q, NT, smem, st>>>(a);
-    FA_CUDA_CHECK(cudaGetLastError());
+    if (phases & 2) {
+        dim3 grid_kv((p.Nk + BN - 1) / BN, p.Hkv, p.B);
+        simt_bwd_kernel<T, 0><<<grid_kv, NT, smem, st>>>(a);
+        FA_CUDA_CHECK(cudaGetLastError());
+    }
+    if (phases & 4) {
+        dim3 grid_q((p.Nq + BM - 1) / BM, p.H, p.B);
+        simt_bwd_kernel<T, 1><<<grid_q, NT, smem, st>>>(a);
+        FA_CUDA_CHECK(cudaGetLastError());
+    }
     return FA_OK;
 }
 

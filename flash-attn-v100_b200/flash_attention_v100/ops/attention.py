@@ -59,6 +59,30 @@ def kernel_variant(name: str):
         _variant_override.value = old
 
 
+# One int32 per device that kernels set non-zero when a bounded device-side
+# wait gives up (a protocol error, never expected).  Reading it synchronises,
+# so it is only read on request.
+_status_words: Dict[int, torch.Tensor] = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status_words:
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[idx]
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel on `device` reported a timed-out wait."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status_word(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"flash_attention_v100: a device-side wait timed out (status {code}); "
+                           "results of the affected call are invalid")
+
+
 def _tensor4(t: Optional[torch.Tensor]) -> _cabi.Tensor4:
     r = _cabi.Tensor4()
     if t is None or t.numel() == 0:
@@ -87,6 +111,7 @@ def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset) -> _ca
     p.dropout_p = float(dropout_p)
     p.seed, p.offset = int(seed), int(offset)
     p.stream = torch.cuda.current_stream(q.device).cuda_stream or None
+    p.status_word = _status_word(q.device).data_ptr()
     return p
 
 
@@ -248,5 +273,5 @@ __all__ = [
     "flash_attention_backward_enhanced", "compare_with_pytorch_attention_enhanced",
     "gradient_checkpointing_mode", "mixed_precision_mode", "FlashAttentionV100Function",
     "flash_attention_forward", "flash_attention_backward", "compare_with_pytorch_attention",
-    "set_dropout_seed", "kernel_variant", "launch_forward", "launch_backward",
+    "set_dropout_seed", "kernel_variant", "launch_forward", "launch_backward", "check_status",
 ]

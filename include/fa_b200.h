@@ -95,6 +95,12 @@ typedef struct fa_b200_params {
     int32_t        device;         /* CUDA ordinal the pointers live on            */
     float          scale;          /* scores = scale * q.k                         */
     float          dropout_p;      /* [0, 1)                                       */
+    int32_t        bwd_phases;     /* 0 = whole backward.  Otherwise a bit mask of the
+                                      backward's launches to run, for timing one kernel
+                                      alone: 1 = preprocess (delta, scaled lse),
+                                      2 = dK/dV kernel, 4 = dQ kernel.  Bits 2 and 4 need
+                                      a workspace that an earlier call with bit 1 filled. */
+    int32_t        reserved;
 } fa_b200_params;
 
 /* Static tile choice for a (D, dtype, causal) key; replaces the reference's

@@ -41,6 +41,13 @@ def test_workload_shapes_reduced_vs_oracle(device, name, shrink):
     o, lse = launch_forward(d["q"], d["k"], d["v"], w.scale, w.causal, w.dropout_p, *stream)
     dq, dk, dv = launch_backward(d["d_o"], d["q"], d["k"], d["v"], o, lse, w.scale, w.causal, w.dropout_p, *stream)
     tol = tolerance(w.dtype, "auto", w.D)
+    if w.outlier_rows > 0:
+        # peaked rows amplify the rounding of the saved O in dQ/dK (see
+        # test_softmax_range_stress_rows): gradients are checked against the closed
+        # form on the O and LSE the backward was given
+        cf = ao.attention_backward_closed_form(*(t[n].float() for n in ("q", "k", "v")), o.float().cpu(), lse.cpu(),
+                                               t["d_o"].float(), causal=w.causal, scale=w.scale)
+        ref = ref[:2] + cf
     for nm, got, r in zip(("o", "lse", "dq", "dk", "dv"), (o, lse, dq, dk, dv), ref):
         err = rel_l2(got, r)
         assert err <= tol, f"{name}:{nm} rel-L2 {err:.3e}"
