@@ -6,6 +6,7 @@
 #include "fa_common.cuh"
 #include <stdarg.h>
 #include <string.h>
+#include <mutex>
 
 namespace fa {
 
@@ -204,6 +205,67 @@ int fa_b200_bwd(const fa_b200_params* p) {
         return FA_OK;
     }
     return variant == FA_B200_VARIANT_TCGEN05 ? sm100_bwd(*p, ws) : simt_bwd(*p, ws);
+}
+
+// ---------------------------------------------------------------------------
+// Backward without a caller-supplied workspace.
+//
+// Some hosts of this library cannot hand it scratch memory: a runtime that owns
+// all device memory itself and exposes no allocator to plugins, or a caller on a
+// path where cudaMalloc is forbidden (inside a latency-critical loop, under a
+// memory budget fixed at start-up).  For them the backward's scratch (delta and
+// the scaled log-sum-exp, 8 bytes per padded query row) lives in a fixed array
+// in the library's own device image.  Every GPU that loads the library holds
+// these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;          // 8 MiB: B*H*ceil128(Nq) <= 1 Mi rows
+static __device__ __align__(256) unsigned char g_bwd_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_ptr[kMaxDevices] = {};
+
+// Device address of the array on the CURRENT device.  In host code the array's
+// name is only a handle; the address kernels can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int static_scratch_address(int device, void** out) {
+    if (device < 0 || device >= kMaxDevices) { set_error("device %d out of range", device); return FA_EINVAL; }
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_ptr[device]) {
+        void* ptr = nullptr;
+        FA_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_bwd_static_scratch));
+        g_scratch_ptr[device] = ptr;
+    }
+    *out = g_scratch_ptr[device];
+    return FA_OK;
+}
+}  // namespace
+
+int fa_b200_bwd_static(const fa_b200_params* p) {
+    int rc = validate_common(p, true);
+    if (rc) return rc;
+    if (p->B == 0 || (p->Nq == 0 && p->Nk == 0)) return FA_OK;
+    if (p->Nk == 0) { set_error("Nk = 0: softmax over an empty key set is undefined"); return FA_EINVAL; }
+    if (p->Nq == 0) { set_error("fa_b200_bwd_static needs at least one query row"); return FA_EINVAL; }
+    int variant;
+    if ((rc = choose_variant(*p, true, &variant))) return rc;
+    BwdWorkspace ws = bwd_workspace_layout(*p, variant);
+    if (ws.total > kStaticScratchBytes) {
+        set_error("fa_b200_bwd_static: this problem needs %zu bytes of scratch, the built-in array holds %zu "
+                  "(B*H*Nq rounded up to 128 must stay within 1048576 rows); use fa_b200_bwd with a workspace",
+                  ws.total, kStaticScratchBytes);
+        return FA_EWORKSPACE;
+    }
+    GuardDevice g(p->device);
+    if (!g.ok) { set_error("cudaSetDevice(%d) failed", p->device); return FA_ECUDA; }
+    void* scratch = nullptr;
+    if ((rc = static_scratch_address(p->device, &scratch))) return rc;
+    fa_b200_params q = *p;
+    q.workspace = scratch;
+    q.workspace_bytes = kStaticScratchBytes;
+    // Nothing in the scratch has to start at zero: the preprocess launch writes
+    // every delta / lse entry (padding included) before the main kernels read them.
+    return variant == FA_B200_VARIANT_TCGEN05 ? sm100_bwd(q, ws) : simt_bwd(q, ws);
 }
 
 // Static tile table.  Tensor-core rows hold the tile shapes the sm_100a

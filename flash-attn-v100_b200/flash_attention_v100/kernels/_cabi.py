@@ -21,7 +21,7 @@ VARIANT_NAMES = {VARIANT_AUTO: "auto", VARIANT_SIMT: "simt", VARIANT_TCGEN05: "t
 FA_OK, FA_EINVAL, FA_EUNSUPPORTED, FA_EALIGN, FA_EWORKSPACE, FA_ECUDA, FA_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 
 EXPORTS = (
-    "fa_b200_fwd", "fa_b200_bwd", "fa_b200_bwd_workspace_bytes", "fa_b200_tile_config",
+    "fa_b200_fwd", "fa_b200_bwd", "fa_b200_bwd_static", "fa_b200_bwd_workspace_bytes", "fa_b200_tile_config",
     "fa_b200_dropout_mask_host", "fa_b200_dropout_mask_device", "fa_b200_dropout_effective_p",
     "fa_b200_philox4x32_10", "fa_b200_strerror", "fa_b200_last_error", "fa_b200_version",
 )
@@ -87,6 +87,8 @@ def load():
         lib.fa_b200_fwd.restype = ctypes.c_int
         lib.fa_b200_bwd.argtypes = [pp]
         lib.fa_b200_bwd.restype = ctypes.c_int
+        lib.fa_b200_bwd_static.argtypes = [pp]
+        lib.fa_b200_bwd_static.restype = ctypes.c_int
         lib.fa_b200_bwd_workspace_bytes.argtypes = [pp]
         lib.fa_b200_bwd_workspace_bytes.restype = ctypes.c_size_t
         lib.fa_b200_tile_config.argtypes = [ctypes.c_int] * 4 + [ctypes.POINTER(Tile)]

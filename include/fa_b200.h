@@ -123,6 +123,29 @@ int fa_b200_fwd(const fa_b200_params* p);
  * dq is reduced in a fixed order: two runs give bit-identical results. */
 int fa_b200_bwd(const fa_b200_params* p);
 
+/*
+ * Backward that takes no workspace and allocates nothing.  It has no
+ * counterpart in the reference.
+ *
+ * For callers that cannot give the library scratch memory: hosts that own all
+ * device memory and offer plugins no allocator, and paths on which cudaMalloc is
+ * not allowed.  Same arguments and results as fa_b200_bwd, except that
+ * `workspace` and `workspace_bytes` are ignored: the scratch (delta and the
+ * scaled log-sum-exp) is an 8 MiB array built into the library's device image,
+ * which every GPU that loads the library keeps until the process exits.
+ *
+ *  - Limit: B * H * (Nq rounded up to 128) <= 1048576 rows; larger problems
+ *    return FA_EWORKSPACE and must use fa_b200_bwd.
+ *  - The first call on each device looks the array's device address up
+ *    (cudaGetSymbolAddress, with that device current).  Make that first call
+ *    outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's
+ *    contents.  The kernels overwrite every entry they later read, so nothing
+ *    needs clearing, but two calls whose kernels overlap on the GPU (different
+ *    streams, no dependency between them) race on it: serialise them.
+ */
+int fa_b200_bwd_static(const fa_b200_params* p);
+
 /* Bytes of scratch fa_b200_bwd needs for these sizes (delta, fp32 dQ
  * accumulator, ...).  Counterpart of the 'delta' entry of
  * ops/memory.py:653-760 allocate_attention_workspace_enhanced. */
