@@ -89,7 +89,7 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
 
-// 4-D tiled load global -> shared, completion counted on `bar` (no multicast).
+// 4-D tiled load global -> shared, completion counted on `bar`; a plain per-CTA load.
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
                                             int c0, int c1, int c2, int c3) {
     asm volatile(

@@ -1,0 +1,96 @@
+"""Multi-GPU paths on real devices (skipped with fewer than two GPUs).
+
+Per-(batch, head) work is identical whichever GPU runs it, so a sharded run must
+equal the single-GPU run bit for bit."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import flash_attention_v100 as fa
+from flash_attention_v100.interface import FlashAttentionV100Manager, plan_shards, _slice
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_gpus(n):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _inputs(B, N, H, D, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(B, N, H, D, generator=g).to(dtype) for _ in range(4)]
+
+
+@pytest.mark.parametrize("B,H", [(2, 8), (4, 3)], ids=["heads", "batch"])
+def test_single_process_sharding_equals_single_gpu(B, H):
+    _need_gpus(2)
+    dev = torch.device("cuda:0")
+    qc, kc, vc, gc = _inputs(B, 384, H, 128, torch.bfloat16)
+    q1, k1, v1 = (t.to(dev).requires_grad_(True) for t in (qc, kc, vc))
+    o1, lse1 = fa.flash_attention_v100(q1, k1, v1, causal=True, return_softmax_lse=True, enable_multi_gpu=False)
+    o1.backward(gc.to(dev))
+    with FlashAttentionV100Manager(enable_multi_gpu=True) as mgr:
+        assert len(mgr.devices) >= 2
+        q2, k2, v2 = (t.to(dev).requires_grad_(True) for t in (qc, kc, vc))
+        o2, lse2 = fa.flash_attention_v100(q2, k2, v2, causal=True, return_softmax_lse=True, enable_multi_gpu=True)
+        o2.backward(gc.to(dev))
+    torch.cuda.synchronize()
+    assert o2.device == dev and torch.equal(o1, o2) and torch.equal(lse1, lse2)
+    assert torch.equal(q1.grad, q2.grad) and torch.equal(k1.grad, k2.grad) and torch.equal(v1.grad, v2.grad)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _rank_main(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        B, N, H, D = 2, 512, 8, 64
+        qc, kc, vc, gc = _inputs(B, N, H, D, torch.float16, seed=3)
+        _, shards = plan_shards(B, H, world)
+        like = torch.empty(B, N, H, D, dtype=torch.float16, device=dev)
+        full = [t.to(dev) if rank == 0 else None for t in (qc, kc, vc, gc)]
+        ql, kl, vl, gl = (FlashAttentionV100Manager.scatter_shards(t, shards, like) for t in full)
+        ql, kl, vl = (t.requires_grad_(True) for t in (ql, kl, vl))
+        o = fa.flash_attention_v100(ql, kl, vl, causal=True, enable_multi_gpu=False)
+        o.backward(gl)
+        outs = [FlashAttentionV100Manager.gather_shards(t, shards, (B, N, H, D)) for t in
+                (o.detach(), ql.grad, kl.grad, vl.grad)]
+        if rank == 0:
+            q1, k1, v1 = (t.to(dev).requires_grad_(True) for t in (qc, kc, vc))
+            o1 = fa.flash_attention_v100(q1, k1, v1, causal=True, enable_multi_gpu=False)
+            o1.backward(gc.to(dev))
+            same = all(torch.equal(a, b) for a, b in zip(outs, (o1.detach(), q1.grad, k1.grad, v1.grad)))
+            ret[0] = "ok" if same else "mismatch"
+        torch.cuda.synchronize()
+    except Exception as e:   # noqa: BLE001
+        ret[rank] = f"error: {e}"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_nccl_scatter_compute_gather_equals_single_gpu():
+    _need_gpus(2)
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert not p.is_alive()
+    assert dict(ret).get(0) == "ok", dict(ret)
