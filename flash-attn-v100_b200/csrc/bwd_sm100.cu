@@ -31,11 +31,11 @@
 // MMAs take P / dS from TMEM (written over T1 / T2 by the threads that read
 // them) and U / W from the same shared-memory tiles read MN-major.
 //
-//   warps 0-3, 4-7   one thread per TMEM lane (row); warpgroup g owns columns
-//                    [64g, 64g+64) of T1/T2
-//   warp 8           MMA issuer; order  T1(0) T2(0) | ACC2(i) T1(i+1) ACC1(i) T2(i+1) ...
-//   warp 9           TMA producer (tiles, and the lse/delta rows in MODE 0)
-//   warps 10-11      idle (complete the third warpgroup for setmaxnreg)
+//   warps 0-15       four elementwise warpgroups; a thread owns one TMEM lane (row)
+//                    and warpgroup g owns columns [32g, 32g+32) of T1/T2
+//   warp 16          MMA issuer; order  T1(0) T2(0) | ACC2(i) T1(i+1) ACC1(i) T2(i+1) ...
+//   warp 17          TMA producer (tiles, and the lse/delta rows in MODE 0)
+//   warps 18-19      idle (complete the fifth warpgroup for setmaxnreg)
 //
 // TMEM columns: T1 [0,128)  T2 [128,256)  ACC1 [256,256+D)  ACC2 [384,384+D).
 // Every mbarrier wait is bounded; see sm100_ptx.cuh.
@@ -50,8 +50,8 @@ namespace {
 using namespace ptx;
 
 constexpr int kTile = 128;
-constexpr int kThreads = 384;
 constexpr int kBoxBytes = 128 * 128;
+constexpr int kNWG = 4;                  // elementwise warpgroups per CTA (each owns 128 / kNWG columns)
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>
@@ -66,11 +66,11 @@ struct BwdCfg {
     static constexpr int kUWEmpty = kUWFull + kStages;           // [kStages]
     static constexpr int kT1Full = kUWEmpty + kStages;
     static constexpr int kT2Full = kT1Full + 1;
-    static constexpr int kPReady = kT2Full + 1;                  // count 256
-    static constexpr int kDsReady = kPReady + 1;                 // count 256
+    static constexpr int kPReady = kT2Full + 1;                  // one arrival per elementwise warp
+    static constexpr int kDsReady = kPReady + 1;                 // one arrival per elementwise warp
     static constexpr int kAccDone = kDsReady + 1;
-    static constexpr int kMask = kAccDone + 1;                   // count 256
-    static constexpr int kEpi = kMask + 1;                       // count 256
+    static constexpr int kMask = kAccDone + 1;                   // one arrival per elementwise warp
+    static constexpr int kEpi = kMask + 1;                       // one arrival per elementwise warp
     static constexpr int kNumBars = kEpi + 1;
     static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kStageBytes + kMaskBytes + kNumBars * 8 + 64 + 1024;
 };
@@ -95,8 +95,8 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
 }
 
 // MODE 0: dK, dV (key-stationary).  MODE 1: dQ (query-stationary).
-template <int D, bool BF16, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int D, bool BF16, int MODE, int NWG>
+__global__ void __launch_bounds__(128 * (NWG + 1), 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                  const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_out1, const __grid_constant__ CUtensorMap map_out2,
@@ -143,16 +143,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kNumBars; ++i) {
             const bool wide = (i == Cfg::kPReady || i == Cfg::kDsReady || i == Cfg::kMask || i == Cfg::kEpi);
-            mbar_init(&bars[i], wide ? 256u : 1u);
+            mbar_init(&bars[i], wide ? 4u * NWG : 1u);    // one arrival per elementwise warp
         }
         *abort_flag = 0u;
         fence_mbar_init();
     }
-    if (warp == 8) {
+    constexpr int kMmaWarp = 4 * NWG, kTmaWarp = 4 * NWG + 1;
+    constexpr int CPT = kTile / NWG;                    // columns of T1/T2 one elementwise thread owns
+    if (warp == kMmaWarp) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
-    if (warp == 9 && lane == 0) {
+    if (warp == kTmaWarp && lane == 0) {
         prefetch_tensormap(&map_x); prefetch_tensormap(&map_y);
         prefetch_tensormap(&map_u); prefetch_tensormap(&map_w);
         prefetch_tensormap(&map_out1);
@@ -164,9 +166,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t tmem = *tmem_slot;
     const uint32_t tT1 = tmem, tT2 = tmem + 128u, tAcc1 = tmem + 256u, tAcc2 = tmem + 384u;
 
-    if (warp >= 8) {
+    if (warp >= kMmaWarp) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-      if (warp == 9) {
+      if (warp == kTmaWarp) {
         // ---------------------------------------------------------------- TMA producer
         if (elect_one()) {
             int issued = 0;
@@ -212,7 +214,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
         }
         __syncwarp();
-      } else if (warp == 8) {
+      } else if (warp == kMmaWarp) {
         // ---------------------------------------------------------------- MMA issuer
         if (elect_one() && n_iter > 0) {
             constexpr uint32_t idesc_t = make_idesc_f16(BF16, BF16, kTile, kTile, false, false);
@@ -227,11 +229,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                                make_smem_desc_sw128(strm_u + off, 0, 1024), idesc_t, kk > 0);
                 }
             };
-            // acc (+)= A[TMEM: 16-bit pairs at a_tmem, second half of K at +64 columns] * B[smem tile, MN-major]
+            // acc (+)= A[TMEM] * B[smem tile, MN-major].  A holds 16-bit pairs: the thread group that owns
+            // columns [g*CPT, (g+1)*CPT) of T wrote its CPT values packed into columns [g*CPT, g*CPT + CPT/2).
             auto issue_acc = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t strm_u, bool acc) {
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk) {
-                    const uint32_t a_col = (kk < 4) ? (uint32_t)kk * 8u : 64u + (uint32_t)(kk - 4) * 8u;
+                    const uint32_t a_col = (uint32_t)((16 * kk) / CPT) * CPT + (uint32_t)((16 * kk) % CPT) / 2u;
                     mma_ts_f16(d_tmem, a_tmem + a_col, make_smem_desc_sw128(strm_u + kk * 2048, kBoxBytes, 1024),
                                idesc_acc, (acc || kk > 0) ? 1u : 0u);
                 }
@@ -269,14 +272,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         __syncwarp();
       }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        if (NWG == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        else          asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
         // ---------------------------------------------------------------- P / dS and epilogue
-        const int hf = warp >> 2;                              // column half
+        constexpr int NLD = CPT / 32;                          // 32-column TMEM loads per thread and phase
+        const int wg = warp >> 2;                              // which CPT-column slice
         const int r = (warp & 3) * 32 + lane;                  // TMEM lane = row of T1/T2
-        const int cb = hf * 64;
-        const int tid = hf * 128 + r;                          // 0..255
+        const int cb = wg * CPT;
+        const int tid = wg * 128 + r;                          // 0 .. 128*NWG-1
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const int row_g = tile * kTile + r;                    // MODE 0: key index; MODE 1: query index
+        const bool drop = a.drop_thr != 0u;
         float my_lse2 = 0.f, my_delta = 0.f;
         if (MODE == 1) {
             const int64_t off = ((int64_t)b * a.H + head_x) * a.nq_pad + row_g;
@@ -295,36 +301,35 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const int head_q = (MODE == 0) ? head_x * group + it / n_per_head : head_x;
             const uint32_t bh = (uint32_t)(b * a.H + head_q);
 
-            // ---- dropout keep bits of my 64 columns
-            uint32_t kb0 = 0xFFFFFFFFu, kb1 = 0xFFFFFFFFu;
-            if (a.drop_thr) {
+            // ---- dropout keep bits of my CPT columns (bit c of kb[c / 32])
+            uint32_t kb[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};
+            if (drop) {
+                kb[0] = 0u; kb[1] = 0u;
                 if (MODE == 1) {
-                    uint32_t w[4];
 #pragma unroll
-                    for (int g = 0; g < 4; ++g)
-                        w[g] = dropout_keep_bits(a.key, bh, (uint32_t)row_g, (uint32_t)((col_g0 >> 4) + g), a.drop_thr);
-                    kb0 = w[0] | (w[1] << 16);
-                    kb1 = w[2] | (w[3] << 16);
+                    for (int g = 0; g < CPT / 16; ++g) {
+                        const uint32_t w = dropout_keep_bits(a.key, bh, (uint32_t)row_g, (uint32_t)((col_g0 >> 4) + g),
+                                                             a.drop_thr);
+                        kb[g >> 1] |= w << (16 * (g & 1));
+                    }
                 } else {
                     // keys are rows here: build the tile's masks cooperatively, query-major, then read
                     // one bit per (query column, my key row)
+                    constexpr int PER = 8 / NWG;               // 16-key blocks each thread generates
                     uint16_t* mbuf = sMask + (it & 1) * (128 * 8);
-                    const int ql = tid & 127, jb0 = (tid >> 7) * 4;
+                    const int ql = tid & 127, jb0 = (tid >> 7) * PER;
 #pragma unroll
-                    for (int g = 0; g < 4; ++g)
+                    for (int g = 0; g < PER; ++g)
                         mbuf[ql * 8 + jb0 + g] = (uint16_t)dropout_keep_bits(
                             a.key, bh, (uint32_t)(strm_tile * kTile + ql), (uint32_t)(tile * 8 + jb0 + g), a.drop_thr);
-                    mbar_arrive(&bars[Cfg::kMask]);
+                    mbar_arrive_warp(&bars[Cfg::kMask]);
                     ok = mbar_wait(&bars[Cfg::kMask], (uint32_t)it & 1u, abort_flag);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
-                    kb0 = 0u; kb1 = 0u;
                     const int jw = r >> 4, jbit = r & 15;
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        kb0 |= (((uint32_t)mbuf[(cb + c) * 8 + jw] >> jbit) & 1u) << c;
-                        kb1 |= (((uint32_t)mbuf[(cb + 32 + c) * 8 + jw] >> jbit) & 1u) << c;
-                    }
+                    for (int c = 0; c < CPT; ++c)
+                        kb[c >> 5] |= (((uint32_t)mbuf[(cb + c) * 8 + jw] >> jbit) & 1u) << (c & 31);
                 }
             }
 
@@ -333,16 +338,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            uint32_t pr[2][32];        // P of my 64 columns (fp32 bits), kept for phase B
+            uint32_t pr[NLD][32];      // P of my columns (fp32 bits), kept for phase B
 #define PF(c) __uint_as_float(pr[(c) >> 5][(c) & 31])
 #define PSET(c, x) pr[(c) >> 5][(c) & 31] = __float_as_uint(x)
-            tmem_ld_32x32(tT1 + lane_off + cb, pr[0]);
-            tmem_ld_32x32(tT1 + lane_off + cb + 32, pr[1]);
+#pragma unroll
+            for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tT1 + lane_off + cb + q * 32, pr[q]);
             tmem_wait_ld();
             if (MODE == 0) {
                 const float4* l4 = reinterpret_cast<const float4*>(lse_s + cb);
 #pragma unroll
-                for (int c4 = 0; c4 < 16; ++c4) {
+                for (int c4 = 0; c4 < CPT / 4; ++c4) {
                     const float4 L = l4[c4];
                     PSET(c4 * 4 + 0, ex2(fmaf(PF(c4 * 4 + 0), a.scale_log2, -L.x)));
                     PSET(c4 * 4 + 1, ex2(fmaf(PF(c4 * 4 + 1), a.scale_log2, -L.y)));
@@ -351,37 +356,41 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
                 if (a.causal && strm_tile == tile) {       // diagonal tile: key row > query column is hidden
 #pragma unroll
-                    for (int c = 0; c < 64; ++c)
+                    for (int c = 0; c < CPT; ++c)
                         if (row_g > col_g0 + c) PSET(c, 0.f);
                 }
             } else {
                 const float neg = -my_lse2;
 #pragma unroll
-                for (int c = 0; c < 64; ++c) PSET(c, ex2(fmaf(PF(c), a.scale_log2, neg)));
+                for (int c = 0; c < CPT; ++c) PSET(c, ex2(fmaf(PF(c), a.scale_log2, neg)));
                 const bool diag = a.causal && strm_tile == tile;
                 if (diag || strm_tile * kTile + kTile > a.Nk) {
 #pragma unroll
-                    for (int c = 0; c < 64; ++c) {
+                    for (int c = 0; c < CPT; ++c) {
                         const int col = col_g0 + c;
                         if (col >= a.Nk || (diag && col > row_g)) PSET(c, 0.f);
                     }
                 }
             }
             if (MODE == 0) {
-                uint32_t pk[32];
+                uint32_t pk[CPT / 2];
+                if (drop) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    float x0 = PF(2 * c), x1 = PF(2 * c + 1);
-                    const uint32_t kbits = (c < 16) ? kb0 : kb1;
-                    if (!((kbits >> ((2 * c) & 31)) & 1u)) x0 = 0.f;
-                    if (!((kbits >> ((2 * c + 1) & 31)) & 1u)) x1 = 0.f;
-                    pk[c] = pack2<BF16>(x0, x1);
+                    for (int c = 0; c < CPT / 2; ++c) {
+                        const float x0 = ((kb[(2 * c) >> 5] >> ((2 * c) & 31)) & 1u) ? PF(2 * c) : 0.f;
+                        const float x1 = ((kb[(2 * c + 1) >> 5] >> ((2 * c + 1) & 31)) & 1u) ? PF(2 * c + 1) : 0.f;
+                        pk[c] = pack2<BF16>(x0, x1);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < CPT / 2; ++c) pk[c] = pack2<BF16>(PF(2 * c), PF(2 * c + 1));
                 }
-                tmem_st_32x32(tT1 + lane_off + cb, pk);
+                if constexpr (CPT == 64) tmem_st_32x32(tT1 + lane_off + cb, pk);
+                else                     tmem_st_32x16(tT1 + lane_off + cb, pk);
                 tmem_wait_st();
             }
             tc_fence_before_sync();
-            mbar_arrive(&bars[Cfg::kPReady]);
+            mbar_arrive_warp(&bars[Cfg::kPReady]);
 
             // ---- phase B: dS from T2
             ok = mbar_wait(&bars[Cfg::kT2Full], (uint32_t)it & 1u, abort_flag);
@@ -389,14 +398,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             if (!ok) break;
             tc_fence_after_sync();
             {
-                uint32_t dr[2][32];
-                tmem_ld_32x32(tT2 + lane_off + cb, dr[0]);
-                tmem_ld_32x32(tT2 + lane_off + cb + 32, dr[1]);
+                uint32_t dr[NLD][32];
+#pragma unroll
+                for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tT2 + lane_off + cb + q * 32, dr[q]);
                 tmem_wait_ld();
-                uint32_t pk[32];
+                uint32_t pk[CPT / 2];
                 const float4* d4 = reinterpret_cast<const float4*>(del_s + cb);
 #pragma unroll
-                for (int c4 = 0; c4 < 16; ++c4) {
+                for (int c4 = 0; c4 < CPT / 4; ++c4) {
                     float4 dl;
                     if (MODE == 0) dl = d4[c4];
                     else dl = make_float4(my_delta, my_delta, my_delta, my_delta);
@@ -405,21 +414,25 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int c = c4 * 4 + e;
-                        const uint32_t kbits = (c < 32) ? kb0 : kb1;
-                        const float z = ((kbits >> (c & 31)) & 1u) ? a.inv_keep : 0.f;
                         const float dp = __uint_as_float(dr[c >> 5][c & 31]);
-                        ds[e] = PF(c) * fmaf(dp, z, -dlt[e]);
+                        if (drop) {
+                            const float z = ((kb[c >> 5] >> (c & 31)) & 1u) ? a.inv_keep : 0.f;
+                            ds[e] = PF(c) * fmaf(dp, z, -dlt[e]);
+                        } else {
+                            ds[e] = PF(c) * (dp - dlt[e]);
+                        }
                     }
                     pk[c4 * 2 + 0] = pack2<BF16>(ds[0], ds[1]);
                     pk[c4 * 2 + 1] = pack2<BF16>(ds[2], ds[3]);
                 }
-                tmem_st_32x32(tT2 + lane_off + cb, pk);
+                if constexpr (CPT == 64) tmem_st_32x32(tT2 + lane_off + cb, pk);
+                else                     tmem_st_32x16(tT2 + lane_off + cb, pk);
                 tmem_wait_st();
             }
 #undef PF
 #undef PSET
             tc_fence_before_sync();
-            mbar_arrive(&bars[Cfg::kDsReady]);
+            mbar_arrive_warp(&bars[Cfg::kDsReady]);
         }
 
         // ---- epilogue: accumulators -> 16-bit -> swizzled staging -> TMA store
@@ -427,31 +440,33 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after_sync();
-            constexpr int kColsPerThread = D / 2;              // my share of the D accumulator columns
+            constexpr int kCols = D / NWG;                     // my share of the D accumulator columns: 16..64
             constexpr int kOuts = (MODE == 0) ? 2 : 1;
 #pragma unroll
             for (int o = 0; o < kOuts; ++o) {
-                const uint32_t tacc = (o == 0 ? tAcc1 : tAcc2) + lane_off + (uint32_t)(hf * kColsPerThread);
+                const uint32_t tacc = (o == 0 ? tAcc1 : tAcc2) + lane_off + (uint32_t)(wg * kCols);
                 const float mul = (o == 0) ? a.scale : a.inv_keep;
                 uint8_t* stage = sRing + o * TILE;             // ring stage 0 is idle once all MMAs completed
 #pragma unroll
-                for (int c0 = 0; c0 < kColsPerThread; c0 += 32) {
-                    uint32_t acc[32];
+                for (int c0 = 0; c0 < kCols; c0 += 32) {
+                    constexpr int kN = kCols < 32 ? kCols : 32;
+                    uint32_t acc[kN];
                     if (n_iter > 0) {
-                        tmem_ld_32x32(tacc + c0, acc);
+                        if constexpr (kN == 32) tmem_ld_32x32(tacc + c0, acc);
+                        else                    tmem_ld_32x16(tacc + c0, acc);
                         tmem_wait_ld();
                     } else {
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) acc[c] = 0u;    // no query sees this key tile
+                        for (int c = 0; c < kN; ++c) acc[c] = 0u;    // no query sees this key tile
                     }
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
+                    for (int g = 0; g < kN / 8; ++g) {
                         uint4 v4;
                         v4.x = pack2<BF16>(__uint_as_float(acc[g * 8 + 0]) * mul, __uint_as_float(acc[g * 8 + 1]) * mul);
                         v4.y = pack2<BF16>(__uint_as_float(acc[g * 8 + 2]) * mul, __uint_as_float(acc[g * 8 + 3]) * mul);
                         v4.z = pack2<BF16>(__uint_as_float(acc[g * 8 + 4]) * mul, __uint_as_float(acc[g * 8 + 5]) * mul);
                         v4.w = pack2<BF16>(__uint_as_float(acc[g * 8 + 6]) * mul, __uint_as_float(acc[g * 8 + 7]) * mul);
-                        const int col = hf * kColsPerThread + c0 + g * 8;
+                        const int col = wg * kCols + c0 + g * 8;
                         const int chunk = (col & 63) >> 3;
                         uint8_t* dst = stage + (col >> 6) * kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
                         *reinterpret_cast<uint4*>(dst) = v4;
@@ -459,7 +474,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
             }
             fence_proxy_async_smem();
-            mbar_arrive(&bars[Cfg::kEpi]);
+            mbar_arrive_warp(&bars[Cfg::kEpi]);
             if (tid == 0 && mbar_wait(&bars[Cfg::kEpi], 0u, abort_flag)) {
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kNBox; ++bx) {
@@ -468,14 +483,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         tma_store_4d(&map_out2, sRing + TILE + bx * kBoxBytes, bx * 64, head_x, tile * kTile, b);
                 }
                 tma_store_commit();
-                tma_store_wait_all<0>();
+                tma_store_wait_read<0>();   // the staging tile has been read; the writes complete on their own
             }
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 8) tmem_dealloc(tmem, 512);
+    if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
     if (threadIdx.x == 0 && *abort_flag && a.status) atomicExch(a.status, 2 + MODE);
 }
 
@@ -555,8 +570,9 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
     a.key = philox_make_key(p.seed, p.offset);
 
-    auto k0 = bwd_sm100_kernel<D, BF16, 0>;
-    auto k1 = bwd_sm100_kernel<D, BF16, 1>;
+    constexpr int kThreads = 128 * (kNWG + 1);
+    auto k0 = bwd_sm100_kernel<D, BF16, 0, kNWG>;
+    auto k1 = bwd_sm100_kernel<D, BF16, 1, kNWG>;
     FA_CUDA_CHECK(cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     FA_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     if (phases & 2) {

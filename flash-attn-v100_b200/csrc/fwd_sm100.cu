@@ -116,7 +116,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kNumBars; ++i) {
             const bool wg_bar = (i >= Cfg::kPFull && i < Cfg::kPFull + 2) || (i >= Cfg::kEpi);
-            mbar_init(&bars[i], wg_bar ? 128u : 1u);
+            mbar_init(&bars[i], wg_bar ? 4u : 1u);       // one arrival per warp of the warpgroup
         }
         *abort_flag = 0u;
         fence_mbar_init();
@@ -365,7 +365,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #undef SSET
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&bars[Cfg::kPFull + t]);
+            mbar_arrive_warp(&bars[Cfg::kPFull + t]);
         }
 
         if (n > 0) {
@@ -394,7 +394,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     }
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(&bars[Cfg::kEpi + t]);
+                mbar_arrive_warp(&bars[Cfg::kEpi + t]);
                 if (r == 0 && mbar_wait(&bars[Cfg::kEpi + t], 0u, abort_flag)) {
                     // all 128 rows of the tile are staged (a bounded wait: rows of an
                     // unwinding warp never arrive and the store is skipped)
@@ -402,7 +402,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     for (int bx = 0; bx < Cfg::kNBox; ++bx)
                         tma_store_4d(&map_o, stage + bx * kBoxBytes, bx * 64, h, tile * kBlockM, b);
                     tma_store_commit();
-                    tma_store_wait_all<0>();
+                    tma_store_wait_read<0>();   // the staging tile has been read; the writes complete on their own
                 }
                 if (i < a.Nq) a.lse[((int64_t)b * a.H + h) * a.Nq + i] = kLn2 * (m + log2f(l));
             }

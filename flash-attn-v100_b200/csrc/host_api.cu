@@ -281,7 +281,7 @@ int fa_b200_tile_config(int D, int dtype, int causal, int backward, fa_b200_tile
         out->block_n = 128;
         out->q_tiles_per_cta = backward ? 1 : 2;
         out->kv_stages = backward ? 1 : (D == 64 ? 3 : 2);
-        out->num_warps = backward ? 10 : 10;
+        out->num_warps = backward ? 20 : 12;
     } else {
         out->variant = FA_B200_VARIANT_SIMT;
         out->block_m = 64;
