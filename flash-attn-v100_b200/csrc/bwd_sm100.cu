@@ -344,15 +344,23 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
             for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tT1 + lane_off + cb + q * 32, pr[q]);
             tmem_wait_ld();
+            const uint64_t sc2 = f2_pack(a.scale_log2, a.scale_log2);
             if (MODE == 0) {
                 const float4* l4 = reinterpret_cast<const float4*>(lse_s + cb);
 #pragma unroll
                 for (int c4 = 0; c4 < CPT / 4; ++c4) {
+                    // P = 2^(S*c - lse): of every four, two on the special-function unit and
+                    // two by the polynomial on the FMA pipes (the unit's 16 lanes/clk would
+                    // otherwise bound this phase)
                     const float4 L = l4[c4];
-                    PSET(c4 * 4 + 0, ex2(fmaf(PF(c4 * 4 + 0), a.scale_log2, -L.x)));
-                    PSET(c4 * 4 + 1, ex2(fmaf(PF(c4 * 4 + 1), a.scale_log2, -L.y)));
-                    PSET(c4 * 4 + 2, ex2(fmaf(PF(c4 * 4 + 2), a.scale_log2, -L.z)));
-                    PSET(c4 * 4 + 3, ex2(fmaf(PF(c4 * 4 + 3), a.scale_log2, -L.w)));
+                    float x0, x1, x2, x3, p2, p3;
+                    f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 0), PF(c4 * 4 + 1)), sc2, f2_pack(-L.x, -L.y)), x0, x1);
+                    f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 2), PF(c4 * 4 + 3)), sc2, f2_pack(-L.z, -L.w)), x2, x3);
+                    ex2_poly2(x2, x3, p2, p3);
+                    PSET(c4 * 4 + 0, ex2(x0));
+                    PSET(c4 * 4 + 1, ex2(x1));
+                    PSET(c4 * 4 + 2, p2);
+                    PSET(c4 * 4 + 3, p3);
                 }
                 if (a.causal && strm_tile == tile) {       // diagonal tile: key row > query column is hidden
 #pragma unroll
@@ -360,9 +368,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         if (row_g > col_g0 + c) PSET(c, 0.f);
                 }
             } else {
-                const float neg = -my_lse2;
+                const uint64_t neg2 = f2_pack(-my_lse2, -my_lse2);
 #pragma unroll
-                for (int c = 0; c < CPT; ++c) PSET(c, ex2(fmaf(PF(c), a.scale_log2, neg)));
+                for (int c = 0; c < CPT; c += 4) {
+                    float x0, x1, x2, x3, p2, p3;
+                    f2_unpack(f2_fma(f2_pack(PF(c), PF(c + 1)), sc2, neg2), x0, x1);
+                    f2_unpack(f2_fma(f2_pack(PF(c + 2), PF(c + 3)), sc2, neg2), x2, x3);
+                    ex2_poly2(x2, x3, p2, p3);
+                    PSET(c, ex2(x0));
+                    PSET(c + 1, ex2(x1));
+                    PSET(c + 2, p2);
+                    PSET(c + 3, p3);
+                }
                 const bool diag = a.causal && strm_tile == tile;
                 if (diag || strm_tile * kTile + kTile > a.Nk) {
 #pragma unroll

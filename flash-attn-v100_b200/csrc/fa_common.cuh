@@ -59,6 +59,9 @@ int sm100_fwd(const fa_b200_params& p);
 int sm100_bwd(const fa_b200_params& p, const BwdWorkspace& ws);
 bool sm100_supports(const fa_b200_params& p, bool backward, const char** why);
 
+// Number of SMs of a device (cached per device; 0 on failure).
+int sm_count(int device);
+
 int launch_dropout_mask(uint64_t seed, uint64_t offset, float p, int B, int H, int Nq, int Nk,
                         uint8_t* out, cudaStream_t stream);
 

@@ -1,21 +1,28 @@
 // Attention forward for sm_100a: TMA -> shared memory -> tcgen05.mma with
-// accumulators in tensor memory, warp-specialised.
+// accumulators in tensor memory, warp-specialised, persistent.
 //
 // Replaces the reference's Triton forward kernel
 // (kernels/forward_kernel.py:18-243) and its launcher (:246-387).
 //
-// One CTA owns two consecutive 128-row query tiles of one (batch, head) and
-// walks the key/value sequence in 128-row blocks:
+// Work: a "pair" is two consecutive 128-row query tiles of one (batch, head);
+// it walks the key/value sequence in 128-row blocks.  The grid is one CTA per
+// SM; CTA c processes work items c, c + grid, c + 2 grid, ...  Under a causal
+// mask an item is a pair together with its mirror (pair p and pair P-1-p), so
+// that every item costs the same number of key blocks and a static round-robin
+// is balanced; items of one head are adjacent, so the CTAs running at any time
+// share a few heads' K/V in L2.  Nothing is re-initialised between pairs: the
+// K/V ring, the barriers' phases and tensor memory carry on, and the next
+// pair's Q and first K/V blocks are loaded while the current pair drains.
 //
-//   warps 10-11 idle (they complete the third warpgroup for setmaxnreg)
-//   warp 9      TMA producer: Q tiles once, then K_j / V_j into two rings
+//   warp 9      TMA producer: Q tiles per pair, K_j / V_j into two rings
 //   warp 8      MMA issuer (one elected thread):
 //                   S_t = Q_t K_j^T          (SS MMA, both operands K-major)
 //                   O_t += P_t V_j           (TS MMA: P_t from TMEM, V_j MN-major)
 //               issue order  S0(0) S1(0) | PV0(j) S0(j+1) PV1(j) S1(j+1) ...
 //               so that the softmax of one tile overlaps the MMAs of the other
-//   warps 0-3   softmax of tile 0, one thread per query row (TMEM lane)
-//   warps 4-7   softmax of tile 1
+//   warps 0-3   softmax + epilogue of tile 0, one thread per query row (TMEM lane)
+//   warps 4-7   softmax + epilogue of tile 1
+//   warps 10-11 idle (they complete the third warpgroup for setmaxnreg)
 //
 // Online softmax in the log2 domain with scale*log2(e) folded into one FMA.
 // The running maximum is only refreshed when it grows by more than 2^8 (warp
@@ -25,12 +32,15 @@
 // factor is applied once to O), the row sum uses the undropped P.
 //
 // TMEM columns: S0/P0 [0,128)  S1/P1 [128,256)  O0 [256,256+D)  O1 [384,384+D).
+// O_t of the next pair is first written by a PV MMA that waits for P_t, which
+// the owning threads produce only after their epilogue has read O_t.
 //
 // Every mbarrier wait is bounded; on a time-out the CTA raises its abort flag,
 // every role unwinds, TMEM is freed and the status word is set.
 #include "fa_common.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
+#include <type_traits>
 
 namespace fa {
 namespace {
@@ -39,7 +49,7 @@ using namespace ptx;
 
 constexpr int kBlockM = 128;        // query rows per tile
 constexpr int kBlockN = 128;        // key rows per block
-constexpr int kThreads = 384;        // 2 softmax warpgroups + 1 warpgroup holding the MMA and TMA warps
+constexpr int kThreads = 384;       // 2 softmax warpgroups + 1 warpgroup holding the MMA and TMA warps
 constexpr int kBoxBytes = 128 * 128;   // one TMA box: 128 rows x 64 16-bit elements
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -52,34 +62,66 @@ struct FwdCfg {
     static constexpr int kStages = (D == 128) ? 2 : 4;
     // barrier slots
     static constexpr int kQFull = 0;                       // [2]
-    static constexpr int kKFull = 2;                       // [kStages]
+    static constexpr int kQEmpty = 2;                      // [2] last S MMA of the pair has read Q_t
+    static constexpr int kKFull = 4;                       // [kStages]
     static constexpr int kKEmpty = kKFull + kStages;
     static constexpr int kVFull = kKEmpty + kStages;
     static constexpr int kVEmpty = kVFull + kStages;
     static constexpr int kSFull = kVEmpty + kStages;       // [2]
-    static constexpr int kPFull = kSFull + 2;              // [2]
+    static constexpr int kPFull = kSFull + 2;              // [2] one arrival per warp of the warpgroup
     static constexpr int kODone = kPFull + 2;              // [2]
-    static constexpr int kEpi = kODone + 2;                // [2] epilogue rows staged
-    static constexpr int kNumBars = kEpi + 2;
+    static constexpr int kNumBars = kODone + 2;
     static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + kNumBars * 8 + 64 + 1024;
 };
 
 struct FwdArgs {
+    void* o;                       // (B, Nq, H, D) output, element strides below
+    int64_t o_sb, o_sn, o_sh;
     float* lse;
     int32_t* status;
     int B, Nq, Nk, H, Hkv;
     int causal;
-    float scale_log2;     // scale * log2(e)
+    int n_pairs;                   // ceil(Nq / 256)
+    int items_per_head;            // causal: ceil(n_pairs / 2) mirrored items; else n_pairs
+    int n_items;                   // items_per_head * B * H
+    float scale_log2;              // scale * log2(e)
     uint32_t drop_thr;
     float inv_keep;
     PhiloxKey key;
 };
 
+struct Pair { int pair, h, b; };
+
+// Sub-item u (0 or 1) of work item w; false if the item has no such sub-item.
+__device__ __forceinline__ bool decode_work(const FwdArgs& a, int w, int u, Pair& out) {
+    const int bh = w / a.items_per_head, slot = w - bh * a.items_per_head;
+    int pair;
+    if (a.causal) {
+        const int heavy = a.n_pairs - 1 - slot;           // more key blocks: first
+        if (u == 0) pair = heavy;
+        else { if (slot == heavy) return false; pair = slot; }
+    } else {
+        if (u == 1) return false;
+        pair = slot;
+    }
+    out.pair = pair;
+    out.h = bh % a.H;
+    out.b = bh / a.H;
+    return true;
+}
+
+// key blocks tile t of a pair visits
+__device__ __forceinline__ int num_blocks(const FwdArgs& a, int pair, int t) {
+    const int row0 = (pair * 2 + t) * kBlockM;
+    int kv_end = a.Nk;
+    if (a.causal && row0 + kBlockM < kv_end) kv_end = row0 + kBlockM;
+    return (row0 < a.Nq) ? (kv_end + kBlockN - 1) / kBlockN : 0;
+}
+
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                 const FwdArgs a) {
+                 const __grid_constant__ CUtensorMap map_v, const FwdArgs a) {
     using Cfg = FwdCfg<D>;
     constexpr int ST = Cfg::kStages;
     constexpr int TILE = Cfg::kTileBytes;
@@ -97,26 +139,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pair = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-    const int h = blockIdx.y, b = blockIdx.z;
-    const int hk = h / (a.H / a.Hkv);
-    const int q0 = pair * 2 * kBlockM;
-
-    // key blocks each tile visits (uniform over the CTA)
-    int nblk[2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        const int row0 = q0 + t * kBlockM;
-        int kv_end = a.Nk;
-        if (a.causal && row0 + kBlockM < kv_end) kv_end = row0 + kBlockM;
-        nblk[t] = (row0 < a.Nq) ? (kv_end + kBlockN - 1) / kBlockN : 0;
-    }
-    const int nmax = nblk[0] > nblk[1] ? nblk[0] : nblk[1];
+    const int group = a.H / a.Hkv;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kNumBars; ++i) {
-            const bool wg_bar = (i >= Cfg::kPFull && i < Cfg::kPFull + 2) || (i >= Cfg::kEpi);
-            mbar_init(&bars[i], wg_bar ? 4u : 1u);       // one arrival per warp of the warpgroup
+            const bool wg_bar = (i >= Cfg::kPFull && i < Cfg::kPFull + 2);
+            mbar_init(&bars[i], wg_bar ? 4u : 1u);
         }
         *abort_flag = 0u;
         fence_mbar_init();
@@ -129,64 +157,78 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         prefetch_tensormap(&map_q);
         prefetch_tensormap(&map_k);
         prefetch_tensormap(&map_v);
-        prefetch_tensormap(&map_o);
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    // Register re-partition: the softmax warpgroups take the registers the
-    // MMA/TMA warpgroup does not need (168 * 384 = 232 * 256 + 40 * 128).
     if (warp >= 8) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
       if (warp == 9) {
         // ------------------------------------------------------------ TMA producer
         if (elect_one()) {
-            int k_issued = 0, v_issued = 0;     // fills armed so far (stage = index % ST)
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                if (nblk[t] > 0) {
-                    mbar_expect_tx(&bars[Cfg::kQFull + t], TILE);
-#pragma unroll
-                    for (int bx = 0; bx < Cfg::kNBox; ++bx)
-                        tma_load_4d(sQ + t * TILE + bx * kBoxBytes, &map_q, &bars[Cfg::kQFull + t],
-                                    bx * 64, h, q0 + t * kBlockM, b);
-                }
-            }
+            int kvc = 0;                    // K/V blocks loaded so far (ring index = count % ST)
+            int q_loads[2] = {0, 0};
             bool ok = true;
-            for (int j = 0; j < nmax && ok; ++j) {
-                const int s = j % ST;
-                const uint32_t ph = (uint32_t)(j / ST) & 1u;
-                ok = mbar_wait(&bars[Cfg::kKEmpty + s], ph ^ 1u, abort_flag);
-                if (!ok) break;
-                mbar_expect_tx(&bars[Cfg::kKFull + s], TILE);
+            for (int w = blockIdx.x; w < a.n_items && ok; w += gridDim.x) {
+                for (int u = 0; u < 2 && ok; ++u) {
+                    Pair pr;
+                    if (!decode_work(a, w, u, pr)) continue;
+                    const int hk = pr.h / group;
+                    const int q0 = pr.pair * 2 * kBlockM;
+                    const int n0 = num_blocks(a, pr.pair, 0), n1 = num_blocks(a, pr.pair, 1);
+                    const int nmax = n0 > n1 ? n0 : n1;
 #pragma unroll
-                for (int bx = 0; bx < Cfg::kNBox; ++bx)
-                    tma_load_4d(sK + s * TILE + bx * kBoxBytes, &map_k, &bars[Cfg::kKFull + s],
-                                bx * 64, hk, j * kBlockN, b);
-                ++k_issued;
-                ok = mbar_wait(&bars[Cfg::kVEmpty + s], ph ^ 1u, abort_flag);
-                if (!ok) break;
-                mbar_expect_tx(&bars[Cfg::kVFull + s], TILE);
+                    for (int t = 0; t < 2; ++t) {
+                        if ((t == 0 ? n0 : n1) == 0) continue;
+                        // Q_t of the previous pair must have been read by its last S MMA
+                        ok = mbar_wait(&bars[Cfg::kQEmpty + t], ((uint32_t)q_loads[t] & 1u) ^ 1u, abort_flag);
+                        if (!ok) break;
+                        mbar_expect_tx(&bars[Cfg::kQFull + t], TILE);
 #pragma unroll
-                for (int bx = 0; bx < Cfg::kNBox; ++bx)
-                    tma_load_4d(sV + s * TILE + bx * kBoxBytes, &map_v, &bars[Cfg::kVFull + s],
-                                bx * 64, hk, j * kBlockN, b);
-                ++v_issued;
+                        for (int bx = 0; bx < Cfg::kNBox; ++bx)
+                            tma_load_4d(sQ + t * TILE + bx * kBoxBytes, &map_q, &bars[Cfg::kQFull + t],
+                                        bx * 64, pr.h, q0 + t * kBlockM, pr.b);
+                        ++q_loads[t];
+                    }
+                    for (int j = 0; j < nmax && ok; ++j, ++kvc) {
+                        const int s = kvc % ST;
+                        const uint32_t ph = (uint32_t)(kvc / ST) & 1u;
+                        ok = mbar_wait(&bars[Cfg::kKEmpty + s], ph ^ 1u, abort_flag);
+                        if (!ok) break;
+                        mbar_expect_tx(&bars[Cfg::kKFull + s], TILE);
+#pragma unroll
+                        for (int bx = 0; bx < Cfg::kNBox; ++bx)
+                            tma_load_4d(sK + s * TILE + bx * kBoxBytes, &map_k, &bars[Cfg::kKFull + s],
+                                        bx * 64, hk, j * kBlockN, pr.b);
+                        ok = mbar_wait(&bars[Cfg::kVEmpty + s], ph ^ 1u, abort_flag);
+                        if (!ok) {
+                            // K of this block is in flight: let it land before giving up shared memory
+                            for (int spin = 0; spin < 4096 && !mbar_try_wait(&bars[Cfg::kKFull + s], ph); ++spin) {}
+                            break;
+                        }
+                        mbar_expect_tx(&bars[Cfg::kVFull + s], TILE);
+#pragma unroll
+                        for (int bx = 0; bx < Cfg::kNBox; ++bx)
+                            tma_load_4d(sV + s * TILE + bx * kBoxBytes, &map_v, &bars[Cfg::kVFull + s],
+                                        bx * 64, hk, j * kBlockN, pr.b);
+                    }
+                }
             }
             if (!ok) {
                 // unwinding: let copies already issued land before the CTA gives up its
                 // shared memory (bounded: a copy that has not landed by now never will)
                 for (int s = 0; s < ST; ++s) {
-                    const int nk = (k_issued + ST - 1 - s) / ST, nv = (v_issued + ST - 1 - s) / ST;
-                    for (int spin = 0; spin < 4096 && nk > 0 &&
-                         !mbar_try_wait(&bars[Cfg::kKFull + s], (uint32_t)(nk - 1) & 1u); ++spin) {}
-                    for (int spin = 0; spin < 4096 && nv > 0 &&
-                         !mbar_try_wait(&bars[Cfg::kVFull + s], (uint32_t)(nv - 1) & 1u); ++spin) {}
+                    const int nf = (kvc + ST - 1 - s) / ST;       // completed K+V fills of stage s
+                    for (int spin = 0; spin < 4096 && nf > 0 &&
+                         !mbar_try_wait(&bars[Cfg::kKFull + s], (uint32_t)(nf - 1) & 1u); ++spin) {}
+                    for (int spin = 0; spin < 4096 && nf > 0 &&
+                         !mbar_try_wait(&bars[Cfg::kVFull + s], (uint32_t)(nf - 1) & 1u); ++spin) {}
                 }
                 for (int t = 0; t < 2; ++t)
-                    for (int spin = 0; spin < 4096 && nblk[t] > 0 && !mbar_try_wait(&bars[Cfg::kQFull + t], 0u); ++spin) {}
+                    for (int spin = 0; spin < 4096 && q_loads[t] > 0 &&
+                         !mbar_try_wait(&bars[Cfg::kQFull + t], (uint32_t)(q_loads[t] - 1) & 1u); ++spin) {}
             }
         }
         __syncwarp();
@@ -215,196 +257,218 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             };
 
+            int kvc = 0;                    // K/V blocks consumed so far
+            int q_uses[2] = {0, 0};         // pairs that used tile t (Q_full phase)
+            int p_waits[2] = {0, 0};        // P_t hand-offs so far (P_full phase)
             bool ok = true;
-            if (nblk[0] > 0) ok = mbar_wait(&bars[Cfg::kQFull + 0], 0u, abort_flag);
-            if (ok && nblk[1] > 0) ok = mbar_wait(&bars[Cfg::kQFull + 1], 0u, abort_flag);
-            if (ok && nmax > 0) ok = mbar_wait(&bars[Cfg::kKFull + 0], 0u, abort_flag);
-            if (ok && nmax > 0) {
-                tc_fence_after_sync();
-                if (nblk[0] > 0) { issue_s(0, 0); mma_commit(&bars[Cfg::kSFull + 0]); }
-                if (nblk[1] > 0) { issue_s(1, 0); mma_commit(&bars[Cfg::kSFull + 1]); }
-                mma_commit(&bars[Cfg::kKEmpty + 0]);
-            }
-            for (int j = 0; j < nmax && ok; ++j) {
-                const int vs = j % ST;
-                const uint32_t vph = (uint32_t)(j / ST) & 1u;
-                const int ks = (j + 1) % ST;
-                const uint32_t kph = (uint32_t)((j + 1) / ST) & 1u;
-                bool k_ready = false;
-                ok = mbar_wait(&bars[Cfg::kVFull + vs], vph, abort_flag);
-                if (!ok) break;
-                if (j < nblk[0]) {
-                    ok = mbar_wait(&bars[Cfg::kPFull + 0], (uint32_t)j & 1u, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_pv(0, vs, j > 0);
-                    if (j == nblk[0] - 1) mma_commit(&bars[Cfg::kODone + 0]);
-                }
-                if (j + 1 < nblk[0]) {
-                    ok = mbar_wait(&bars[Cfg::kKFull + ks], kph, abort_flag);
-                    if (!ok) break;
-                    k_ready = true;
-                    tc_fence_after_sync();
-                    issue_s(0, ks);
-                    mma_commit(&bars[Cfg::kSFull + 0]);
-                }
-                if (j < nblk[1]) {
-                    ok = mbar_wait(&bars[Cfg::kPFull + 1], (uint32_t)j & 1u, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_pv(1, vs, j > 0);
-                    if (j == nblk[1] - 1) mma_commit(&bars[Cfg::kODone + 1]);
-                }
-                mma_commit(&bars[Cfg::kVEmpty + vs]);
-                if (j + 1 < nblk[1]) {
-                    if (!k_ready) {
-                        ok = mbar_wait(&bars[Cfg::kKFull + ks], kph, abort_flag);
-                        if (!ok) break;
-                        k_ready = true;
-                        tc_fence_after_sync();
+            for (int w = blockIdx.x; w < a.n_items && ok; w += gridDim.x) {
+                for (int u = 0; u < 2 && ok; ++u) {
+                    Pair pr;
+                    if (!decode_work(a, w, u, pr)) continue;
+                    int nblk[2] = {num_blocks(a, pr.pair, 0), num_blocks(a, pr.pair, 1)};
+                    const int nmax = nblk[0] > nblk[1] ? nblk[0] : nblk[1];
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (nblk[t] == 0) continue;
+                        if (ok) ok = mbar_wait(&bars[Cfg::kQFull + t], (uint32_t)q_uses[t] & 1u, abort_flag);
+                        ++q_uses[t];
                     }
-                    issue_s(1, ks);
-                    mma_commit(&bars[Cfg::kSFull + 1]);
+                    if (ok) ok = mbar_wait(&bars[Cfg::kKFull + kvc % ST], (uint32_t)(kvc / ST) & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (nblk[t] == 0) continue;
+                        issue_s(t, kvc % ST);
+                        mma_commit(&bars[Cfg::kSFull + t]);
+                        if (nblk[t] == 1) mma_commit(&bars[Cfg::kQEmpty + t]);
+                    }
+                    mma_commit(&bars[Cfg::kKEmpty + kvc % ST]);
+
+                    for (int j = 0; j < nmax && ok; ++j) {
+                        const int vs = (kvc + j) % ST;
+                        const uint32_t vph = (uint32_t)((kvc + j) / ST) & 1u;
+                        const int ks = (kvc + j + 1) % ST;
+                        const uint32_t kph = (uint32_t)((kvc + j + 1) / ST) & 1u;
+                        bool k_ready = false;
+                        ok = mbar_wait(&bars[Cfg::kVFull + vs], vph, abort_flag);
+                        if (!ok) break;
+#pragma unroll
+                        for (int t = 0; t < 2; ++t) {
+                            if (j < nblk[t]) {
+                                ok = mbar_wait(&bars[Cfg::kPFull + t], (uint32_t)p_waits[t] & 1u, abort_flag);
+                                if (!ok) break;
+                                ++p_waits[t];
+                                tc_fence_after_sync();
+                                issue_pv(t, vs, j > 0);
+                                if (j == nblk[t] - 1) mma_commit(&bars[Cfg::kODone + t]);
+                            }
+                            if (t == 1) mma_commit(&bars[Cfg::kVEmpty + vs]);
+                            if (j + 1 < nblk[t]) {
+                                if (!k_ready) {
+                                    ok = mbar_wait(&bars[Cfg::kKFull + ks], kph, abort_flag);
+                                    if (!ok) break;
+                                    k_ready = true;
+                                    tc_fence_after_sync();
+                                }
+                                issue_s(t, ks);
+                                mma_commit(&bars[Cfg::kSFull + t]);
+                                if (j + 2 == nblk[t]) mma_commit(&bars[Cfg::kQEmpty + t]);   // last S of tile t
+                            }
+                        }
+                        if (ok && j + 1 < nmax) mma_commit(&bars[Cfg::kKEmpty + ks]);
+                    }
+                    kvc += nmax;
                 }
-                if (j + 1 < nmax) mma_commit(&bars[Cfg::kKEmpty + ks]);
             }
         }
         __syncwarp();
       }   // warps 10-11 idle: they complete the third warpgroup
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ------------------------------------------------------------ softmax + epilogue
+        using T16 = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
         const int t = warp >> 2;
         const int r = (warp & 3) * 32 + lane;
-        const int tile = pair * 2 + t;
-        const int i = tile * kBlockM + r;                    // global query row
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tS = tmem + (uint32_t)t * 128u + lane_off;
         const uint32_t tO = tmem + 256u + (uint32_t)t * 128u + lane_off;
-        const uint32_t bh = (uint32_t)(b * a.H + h);
-        const int n = nblk[t];
-        float m = -INFINITY, l = 0.f;
+        int s_waits = 0;                 // S_t hand-offs so far (S_full phase)
+        int o_waits = 0;                 // pairs finished so far (O_done phase)
         bool ok = true;
 
-        for (int j = 0; j < n; ++j) {
-            ok = mbar_wait(&bars[Cfg::kSFull + t], (uint32_t)j & 1u, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);      // the TMEM accesses below are warp-collective
-            if (!ok) break;
-            tc_fence_after_sync();
-            uint32_t sr[4][32];                    // the row's 128 scores, then its 128 probabilities
+        for (int w = blockIdx.x; w < a.n_items && ok; w += gridDim.x) {
+            for (int u = 0; u < 2 && ok; ++u) {
+                Pair pr;
+                if (!decode_work(a, w, u, pr)) continue;
+                const int n = num_blocks(a, pr.pair, t);
+                if (n == 0) continue;
+                const int tile = pr.pair * 2 + t;
+                const int i = tile * kBlockM + r;                    // global query row
+                const uint32_t bh = (uint32_t)(pr.b * a.H + pr.h);
+                float m = -INFINITY, l = 0.f;
+
+                for (int j = 0; j < n; ++j) {
+                    ok = mbar_wait(&bars[Cfg::kSFull + t], (uint32_t)s_waits & 1u, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);      // the TMEM accesses below are warp-collective
+                    if (!ok) break;
+                    ++s_waits;
+                    tc_fence_after_sync();
+                    uint32_t sr[4][32];                    // the row's 128 scores, then its 128 probabilities
 #define SF(c) __uint_as_float(sr[(c) >> 5][(c) & 31])
 #define SSET(c, x) sr[(c) >> 5][(c) & 31] = __float_as_uint(x)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + c * 32, sr[c]);
-            tmem_wait_ld();
+                    for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + c * 32, sr[c]);
+                    tmem_wait_ld();
 
-            const int col0 = j * kBlockN;
-            const bool need_mask = (a.causal && col0 + kBlockN - 1 > tile * kBlockM) || (col0 + kBlockN > a.Nk);
-            if (need_mask) {
+                    const int col0 = j * kBlockN;
+                    const bool need_mask = (a.causal && col0 + kBlockN - 1 > tile * kBlockM) || (col0 + kBlockN > a.Nk);
+                    if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < 128; ++c) {
-                    const int col = col0 + c;
-                    if (col >= a.Nk || (a.causal && col > i)) SSET(c, -INFINITY);
-                }
-            }
-            float mx0 = SF(0), mx1 = SF(1), mx2 = SF(2), mx3 = SF(3);
-#pragma unroll
-            for (int c = 4; c < 128; c += 4) {
-                mx0 = fmaxf(mx0, SF(c)); mx1 = fmaxf(mx1, SF(c + 1));
-                mx2 = fmaxf(mx2, SF(c + 2)); mx3 = fmaxf(mx3, SF(c + 3));
-            }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2;
-            const float m_new = fmaxf(m, mx);
-            const bool grow = (m_new - m) > kRescaleThreshold;   // first block: inf > 8
-            if (__any_sync(0xffffffffu, grow)) {
-                const float alpha = ex2(m - m_new);               // 0 on the first block
-                m = m_new;
-                l *= alpha;
-                if (j > 0) {
-                    // S_t(j) complete implies PV_t(j-1) complete (same issuing thread, in order)
-#pragma unroll
-                    for (int c0 = 0; c0 < D; c0 += 32) {
-                        uint32_t orr[32];
-                        tmem_ld_32x32(tO + c0, orr);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) orr[c] = __float_as_uint(__uint_as_float(orr[c]) * alpha);
-                        tmem_st_32x32(tO + c0, orr);
+                        for (int c = 0; c < 128; ++c) {
+                            const int col = col0 + c;
+                            if (col >= a.Nk || (a.causal && col > i)) SSET(c, -INFINITY);
+                        }
                     }
-                }
-            }
-            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-            const float neg_m = -m;
+                    float mx0 = SF(0), mx1 = SF(1), mx2 = SF(2), mx3 = SF(3);
 #pragma unroll
-            for (int c = 0; c < 128; c += 4) {
-                const float p0 = ex2(fmaf(SF(c), a.scale_log2, neg_m));
-                const float p1 = ex2(fmaf(SF(c + 1), a.scale_log2, neg_m));
-                const float p2 = ex2(fmaf(SF(c + 2), a.scale_log2, neg_m));
-                const float p3 = ex2(fmaf(SF(c + 3), a.scale_log2, neg_m));
-                l0 += p0; l1 += p1; l2 += p2; l3 += p3;
-                SSET(c, p0); SSET(c + 1, p1); SSET(c + 2, p2); SSET(c + 3, p3);
-            }
-            l += (l0 + l1) + (l2 + l3);
-            if (a.drop_thr) {
+                    for (int c = 4; c < 128; c += 8) {          // 3-input max: one instruction per two scores
+                        mx0 = max3(mx0, SF(c), SF(c + 1)); mx1 = max3(mx1, SF(c + 2), SF(c + 3));
+                        if (c + 4 < 128) { mx2 = max3(mx2, SF(c + 4), SF(c + 5)); mx3 = max3(mx3, SF(c + 6), SF(c + 7)); }
+                    }
+                    const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2;
+                    const float m_new = fmaxf(m, mx);
+                    const bool grow = (m_new - m) > kRescaleThreshold;   // first block: inf > 8
+                    if (__any_sync(0xffffffffu, grow)) {
+                        const float alpha = ex2(m - m_new);               // 0 on the first block
+                        m = m_new;
+                        l *= alpha;
+                        if (j > 0) {
+                            // S_t(j) complete implies PV_t(j-1) complete (same issuing thread, in order)
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const uint32_t bits = dropout_keep_bits(a.key, bh, (uint32_t)i, (uint32_t)(j * 8 + g), a.drop_thr);
+                            for (int c0 = 0; c0 < D; c0 += 32) {
+                                uint32_t orr[32];
+                                tmem_ld_32x32(tO + c0, orr);
+                                tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 16; ++c)
-                        if (!((bits >> c) & 1u)) SSET(g * 16 + c, 0.f);
-                }
-            }
+                                for (int c = 0; c < 32; ++c) orr[c] = __float_as_uint(__uint_as_float(orr[c]) * alpha);
+                                tmem_st_32x32(tO + c0, orr);
+                            }
+                        }
+                    }
+                    // P = 2^(S*c - m): packed FMAs; of every four probabilities two take the
+                    // special-function unit and two the polynomial on the FMA pipes
+                    const uint64_t c2 = f2_pack(a.scale_log2, a.scale_log2), nm2 = f2_pack(-m, -m);
+                    uint64_t la = 0ull, lb = 0ull;             // {0.f, 0.f}
 #pragma unroll
-            for (int c0 = 0; c0 < 2; ++c0) {
-                uint32_t pk[32];
+                    for (int c = 0; c < 128; c += 4) {
+                        float x0, x1, x2, x3, p0, p1, p2, p3;
+                        f2_unpack(f2_fma(f2_pack(SF(c), SF(c + 1)), c2, nm2), x0, x1);
+                        f2_unpack(f2_fma(f2_pack(SF(c + 2), SF(c + 3)), c2, nm2), x2, x3);
+                        p0 = ex2(x0); p1 = ex2(x1);
+                        ex2_poly2(x2, x3, p2, p3);
+                        la = f2_add(la, f2_pack(p0, p1));
+                        lb = f2_add(lb, f2_pack(p2, p3));
+                        SSET(c, p0); SSET(c + 1, p1); SSET(c + 2, p2); SSET(c + 3, p3);
+                    }
+                    {
+                        float s0, s1, s2, s3;
+                        f2_unpack(la, s0, s1); f2_unpack(lb, s2, s3);
+                        l += (s0 + s1) + (s2 + s3);
+                    }
+                    if (a.drop_thr) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) pk[c] = pack2<P_BF16>(SF(c0 * 64 + 2 * c), SF(c0 * 64 + 2 * c + 1));
-                tmem_st_32x32(tS + c0 * 32, pk);
-            }
+                        for (int g = 0; g < 8; ++g) {
+                            const uint32_t bits = dropout_keep_bits(a.key, bh, (uint32_t)i, (uint32_t)(j * 8 + g), a.drop_thr);
+#pragma unroll
+                            for (int c = 0; c < 16; ++c)
+                                if (!((bits >> c) & 1u)) SSET(g * 16 + c, 0.f);
+                        }
+                    }
+#pragma unroll
+                    for (int c0 = 0; c0 < 2; ++c0) {
+                        uint32_t pk[32];
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) pk[c] = pack2<P_BF16>(SF(c0 * 64 + 2 * c), SF(c0 * 64 + 2 * c + 1));
+                        tmem_st_32x32(tS + c0 * 32, pk);
+                    }
 #undef SF
 #undef SSET
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive_warp(&bars[Cfg::kPFull + t]);
-        }
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive_warp(&bars[Cfg::kPFull + t]);
+                }
+                if (!ok) break;
 
-        if (n > 0) {
-            if (ok) ok = mbar_wait(&bars[Cfg::kODone + t], 0u, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
+                // ---- epilogue: O_t / l -> 16 bit -> global, straight from registers
+                ok = mbar_wait(&bars[Cfg::kODone + t], (uint32_t)o_waits & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ++o_waits;
                 tc_fence_after_sync();
                 const float inv = a.inv_keep / l;
-                uint8_t* stage = sQ + t * TILE;     // Q_t is dead once its last S MMA completed
+                T16* orow = reinterpret_cast<T16*>(a.o) + (int64_t)pr.b * a.o_sb + (int64_t)i * a.o_sn +
+                            (int64_t)pr.h * a.o_sh;
 #pragma unroll
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t orr[32];
                     tmem_ld_32x32(tO + c0, orr);
                     tmem_wait_ld();
+                    if (i < a.Nq) {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint4 v4;
-                        v4.x = pack2<BF16>(__uint_as_float(orr[g * 8 + 0]) * inv, __uint_as_float(orr[g * 8 + 1]) * inv);
-                        v4.y = pack2<BF16>(__uint_as_float(orr[g * 8 + 2]) * inv, __uint_as_float(orr[g * 8 + 3]) * inv);
-                        v4.z = pack2<BF16>(__uint_as_float(orr[g * 8 + 4]) * inv, __uint_as_float(orr[g * 8 + 5]) * inv);
-                        v4.w = pack2<BF16>(__uint_as_float(orr[g * 8 + 6]) * inv, __uint_as_float(orr[g * 8 + 7]) * inv);
-                        const int col = c0 + g * 8;                 // first of 8 columns (16 bytes)
-                        const int chunk = (col & 63) >> 3;          // 16-byte chunk within the 128-byte row
-                        uint8_t* dst = stage + (col >> 6) * kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
-                        *reinterpret_cast<uint4*>(dst) = v4;
+                        for (int g = 0; g < 4; ++g) {
+                            uint4 v4;
+                            v4.x = pack2<BF16>(__uint_as_float(orr[g * 8 + 0]) * inv, __uint_as_float(orr[g * 8 + 1]) * inv);
+                            v4.y = pack2<BF16>(__uint_as_float(orr[g * 8 + 2]) * inv, __uint_as_float(orr[g * 8 + 3]) * inv);
+                            v4.z = pack2<BF16>(__uint_as_float(orr[g * 8 + 4]) * inv, __uint_as_float(orr[g * 8 + 5]) * inv);
+                            v4.w = pack2<BF16>(__uint_as_float(orr[g * 8 + 6]) * inv, __uint_as_float(orr[g * 8 + 7]) * inv);
+                            *reinterpret_cast<uint4*>(orow + c0 + g * 8) = v4;
+                        }
                     }
                 }
-                fence_proxy_async_smem();
-                mbar_arrive_warp(&bars[Cfg::kEpi + t]);
-                if (r == 0 && mbar_wait(&bars[Cfg::kEpi + t], 0u, abort_flag)) {
-                    // all 128 rows of the tile are staged (a bounded wait: rows of an
-                    // unwinding warp never arrive and the store is skipped)
-#pragma unroll
-                    for (int bx = 0; bx < Cfg::kNBox; ++bx)
-                        tma_store_4d(&map_o, stage + bx * kBoxBytes, bx * 64, h, tile * kBlockM, b);
-                    tma_store_commit();
-                    tma_store_wait_read<0>();   // the staging tile has been read; the writes complete on their own
-                }
-                if (i < a.Nq) a.lse[((int64_t)b * a.H + h) * a.Nq + i] = kLn2 * (m + log2f(l));
+                if (i < a.Nq) a.lse[((int64_t)pr.b * a.H + pr.h) * a.Nq + i] = kLn2 * (m + log2f(l));
+                // the O_t reads above are complete (wait::ld); the next pair's first PV_t MMA waits for
+                // this warpgroup's next P_t, so it cannot overwrite O_t earlier
             }
         }
     }
@@ -419,28 +483,36 @@ template <int D, bool BF16>
 int launch(const fa_b200_params& p) {
     using Cfg = FwdCfg<D>;
     const CUtensorMapDataType dt = BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap mq, mk, mv, mo;
+    CUtensorMap mq, mk, mv;
     int r;
     if ((r = make_tmap_bnhd(&mq, p.q.ptr, dt, 2, p.B, p.Nq, p.H, D, p.q.stride_b, p.q.stride_n, p.q.stride_h, 128, 64, true)) ||
         (r = make_tmap_bnhd(&mk, p.k.ptr, dt, 2, p.B, p.Nk, p.Hkv, D, p.k.stride_b, p.k.stride_n, p.k.stride_h, 128, 64, true)) ||
-        (r = make_tmap_bnhd(&mv, p.v.ptr, dt, 2, p.B, p.Nk, p.Hkv, D, p.v.stride_b, p.v.stride_n, p.v.stride_h, 128, 64, true)) ||
-        (r = make_tmap_bnhd(&mo, p.o.ptr, dt, 2, p.B, p.Nq, p.H, D, p.o.stride_b, p.o.stride_n, p.o.stride_h, 128, 64, true))) {
+        (r = make_tmap_bnhd(&mv, p.v.ptr, dt, 2, p.B, p.Nk, p.Hkv, D, p.v.stride_b, p.v.stride_n, p.v.stride_h, 128, 64, true))) {
         set_error("cuTensorMapEncodeTiled failed (%d)", r);
         return FA_ECUDA;
     }
     FwdArgs a;
+    a.o = p.o.ptr;
+    a.o_sb = p.o.stride_b; a.o_sn = p.o.stride_n; a.o_sh = p.o.stride_h;
     a.lse = p.lse;
     a.status = p.status_word;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv;
     a.causal = p.causal;
+    a.n_pairs = (p.Nq + 2 * kBlockM - 1) / (2 * kBlockM);
+    a.items_per_head = p.causal ? (a.n_pairs + 1) / 2 : a.n_pairs;
+    const int64_t n_items = (int64_t)a.items_per_head * p.B * p.H;
+    if (n_items > 0x7fffffff) { set_error("too many work items"); return FA_EUNSUPPORTED; }
+    a.n_items = (int)n_items;
     a.scale_log2 = p.scale * kLog2e;
     a.drop_thr = dropout_threshold(p.dropout_p);
     a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
     a.key = philox_make_key(p.seed, p.offset);
     auto kernel = fwd_sm100_kernel<D, BF16>;
     FA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    dim3 grid((p.Nq + 2 * kBlockM - 1) / (2 * kBlockM), p.H, p.B);
-    kernel<<<grid, kThreads, Cfg::kSmemBytes, (cudaStream_t)p.stream>>>(mq, mk, mv, mo, a);
+    const int sms = sm_count(p.device);
+    if (sms <= 0) { set_error("cannot read the SM count of device %d", p.device); return FA_ECUDA; }
+    const int grid = a.n_items < sms ? a.n_items : sms;     // one persistent CTA per SM
+    kernel<<<grid, kThreads, Cfg::kSmemBytes, (cudaStream_t)p.stream>>>(mq, mk, mv, a);
     FA_CUDA_CHECK(cudaGetLastError());
     return FA_OK;
 }

@@ -31,6 +31,19 @@ BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant) {
     return w;
 }
 
+int sm_count(int device) {
+    static std::mutex mu;
+    static int cache[64] = {};
+    if (device < 0 || device >= 64) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[device] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+        cache[device] = n;
+    }
+    return cache[device];
+}
+
 namespace {
 
 struct GuardDevice {

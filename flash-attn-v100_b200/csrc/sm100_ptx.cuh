@@ -267,6 +267,62 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// ---- packed fp32 pairs (sm_100: fma/add/mul on two floats per instruction) -------------
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 2^x for two values on the FMA pipes instead of the 16-lane/clk special-function
+// unit: n = round(x) through the 1.5*2^23 magic add, f = x - n in [-0.5, 0.5],
+// 2^f by a degree-3 minimax polynomial (relative error 7.5e-5, below the rounding
+// of a 16-bit P), and n added into the exponent field.  x is clamped at -126, so
+// -inf (masked) gives ~1e-38 instead of 0, which vanishes in every later sum.
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& p0, float& p1) {
+    const uint64_t kMagic = 0x4B4000004B400000ull;      // {12582912.f, 12582912.f}
+    const uint64_t kMinus1 = 0xBF800000BF800000ull;     // {-1.f, -1.f}
+    const uint64_t kC0 = 0x3F7FFB493F7FFB49ull;         // 0.99992806
+    const uint64_t kC1 = 0x3F31798D3F31798Dull;         // 0.69326097
+    const uint64_t kC2 = 0x3E786F0D3E786F0Dull;         // 0.24261113
+    const uint64_t kC3 = 0x3D61FBB03D61FBB0ull;         // 0.05517167
+    const uint64_t x = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+    const uint64_t t = f2_add(x, kMagic);
+    const uint64_t neg_n = f2_fma(t, kMinus1, kMagic);
+    const uint64_t f = f2_add(x, neg_n);
+    uint64_t r = f2_fma(f, kC3, kC2);
+    r = f2_fma(r, f, kC1);
+    r = f2_fma(r, f, kC0);
+    float r0, r1, t0, t1;
+    f2_unpack(r, r0, r1);
+    f2_unpack(t, t0, t1);
+    p0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
+    p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
+}
+
 // two floats -> packed 16-bit pair; `lo` lands in bits 0-15
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
