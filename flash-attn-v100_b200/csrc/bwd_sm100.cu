@@ -5,9 +5,9 @@
 // (kernels/backward_kernel.py:17-205) and its launcher (:208-318).
 //
 // Three launches:
-//   1. preprocess  delta = rowsum(dO o O) and lse*log2(e), both fp32, written
+//   1. preprocess  -delta = -rowsum(dO o O) and -lse*log2(e), both fp32, written
 //                  to the workspace in rows padded to whole 128-row tiles
-//                  (padding: delta = 0, lse = +inf, so padded queries get P = 0)
+//                  (padding: delta = 0, -lse = -inf, so padded queries get P = 0)
 //   2. MODE 0      one CTA per 128-row key tile (stationary K, V), streams the
 //                  query tiles: writes dK and dV
 //   3. MODE 1      one CTA per 128-row query tile (stationary Q, dO), streams
@@ -38,6 +38,8 @@
 //   warps 18-19      idle (complete the fifth warpgroup for setmaxnreg)
 //
 // TMEM columns: T1 [0,128)  T2 [128,256)  ACC1 [256,256+D)  ACC2 [384,384+D).
+// MODE 1 has no ACC2 and uses [384,512) as a second S buffer: S(i+1) is computed
+// while the threads still work on S(i).
 // Every mbarrier wait is bounded; see sm100_ptx.cuh.
 #include "fa_common.cuh"
 #include "sm100_ptx.cuh"
@@ -64,8 +66,8 @@ struct BwdCfg {
     static constexpr int kXYFull = 0;
     static constexpr int kUWFull = 1;                            // [kStages]
     static constexpr int kUWEmpty = kUWFull + kStages;           // [kStages]
-    static constexpr int kT1Full = kUWEmpty + kStages;
-    static constexpr int kT2Full = kT1Full + 1;
+    static constexpr int kT1Full = kUWEmpty + kStages;           // [2]: one per S buffer (MODE 0 uses the first)
+    static constexpr int kT2Full = kT1Full + 2;
     static constexpr int kPReady = kT2Full + 1;                  // one arrival per elementwise warp
     static constexpr int kDsReady = kPReady + 1;                 // one arrival per elementwise warp
     static constexpr int kAccDone = kDsReady + 1;
@@ -76,8 +78,8 @@ struct BwdCfg {
 };
 
 struct BwdArgs {
-    const float* lse2;     // [B*H][nq_pad]  lse * log2(e), +inf in the padding
-    const float* delta;    // [B*H][nq_pad]  0 in the padding
+    const float* lse2;     // [B*H][nq_pad]  -lse * log2(e), -inf in the padding
+    const float* delta;    // [B*H][nq_pad]  -delta, 0 in the padding
     int32_t* status;
     int B, Nq, Nk, H, Hkv, nq_pad;
     int causal;
@@ -255,11 +257,22 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 const uint32_t cur_u = sRing_u + s * Cfg::kStageBytes, nxt_u = sRing_u + ns * Cfg::kStageBytes;
                 const bool more = it + 1 < n_iter;
                 if (more) { ok = mbar_wait(&bars[Cfg::kUWFull + ns], nph, abort_flag); if (!ok) break; }
-                ok = mbar_wait(&bars[Cfg::kPReady], (uint32_t)it & 1u, abort_flag);
-                if (!ok) break;
-                tc_fence_after_sync();
-                if (MODE == 0) issue_acc(tAcc2, tT1, cur_u + TILE, it > 0);      // dV += (P o Z)^T dO
-                if (more) { issue_t(tT1, sX_u, nxt_u); mma_commit(&bars[Cfg::kT1Full]); }
+                if (MODE == 0) {
+                    ok = mbar_wait(&bars[Cfg::kPReady], (uint32_t)it & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_acc(tAcc2, tT1, cur_u + TILE, it > 0);                 // dV += (P o Z)^T dO
+                    if (more) { issue_t(tT1, sX_u, nxt_u); mma_commit(&bars[Cfg::kT1Full]); }
+                } else if (more) {
+                    // dQ needs no second accumulator, so S is double-buffered in its columns: S(it+1)
+                    // goes to the buffer S(it-1) left, which phase A(it-1) finished reading before the
+                    // dS(it-1) hand-off this thread waited for in the previous step
+                    tc_fence_after_sync();
+                    issue_t(((it + 1) & 1) ? tAcc2 : tT1, sX_u, nxt_u);
+                    // a barrier per buffer: its previous phase, S(it-1), was observed by every warp
+                    // before the dS(it-1) hand-off, so this completion cannot lap a waiter
+                    mma_commit(&bars[Cfg::kT1Full + ((it + 1) & 1)]);
+                }
                 ok = mbar_wait(&bars[Cfg::kDsReady], (uint32_t)it & 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -283,11 +296,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const int row_g = tile * kTile + r;                    // MODE 0: key index; MODE 1: query index
         const bool drop = a.drop_thr != 0u;
-        float my_lse2 = 0.f, my_delta = 0.f;
+        float my_nlse2 = 0.f, my_ndelta = 0.f;      // -lse*log2(e) and -delta of my query row (MODE 1)
         if (MODE == 1) {
             const int64_t off = ((int64_t)b * a.H + head_x) * a.nq_pad + row_g;
-            my_lse2 = a.lse2[off];
-            my_delta = a.delta[off];
+            my_nlse2 = a.lse2[off];
+            my_ndelta = a.delta[off];
         }
         bool ok = true;
 
@@ -334,33 +347,32 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
 
             // ---- phase A: P from T1
-            ok = mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag);
+            ok = (MODE == 0) ? mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag)
+                             : mbar_wait(&bars[Cfg::kT1Full + (it & 1)], (uint32_t)(it >> 1) & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
             uint32_t pr[NLD][32];      // P of my columns (fp32 bits), kept for phase B
 #define PF(c) __uint_as_float(pr[(c) >> 5][(c) & 31])
 #define PSET(c, x) pr[(c) >> 5][(c) & 31] = __float_as_uint(x)
+            const uint32_t tS = (MODE == 1 && (it & 1)) ? tAcc2 : tT1;      // MODE 1 double-buffers S
 #pragma unroll
-            for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tT1 + lane_off + cb + q * 32, pr[q]);
+            for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tS + lane_off + cb + q * 32, pr[q]);
             tmem_wait_ld();
             const uint64_t sc2 = f2_pack(a.scale_log2, a.scale_log2);
             if (MODE == 0) {
-                const float4* l4 = reinterpret_cast<const float4*>(lse_s + cb);
+                // P = 2^(S*c - lse): the staged vector holds -lse*log2(e), two columns per 64-bit word
+                const ulonglong2* l2 = reinterpret_cast<const ulonglong2*>(lse_s + cb);
 #pragma unroll
                 for (int c4 = 0; c4 < CPT / 4; ++c4) {
-                    // P = 2^(S*c - lse): of every four, two on the special-function unit and
-                    // two by the polynomial on the FMA pipes (the unit's 16 lanes/clk would
-                    // otherwise bound this phase)
-                    const float4 L = l4[c4];
-                    float x0, x1, x2, x3, p2, p3;
-                    f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 0), PF(c4 * 4 + 1)), sc2, f2_pack(-L.x, -L.y)), x0, x1);
-                    f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 2), PF(c4 * 4 + 3)), sc2, f2_pack(-L.z, -L.w)), x2, x3);
-                    ex2_poly2(x2, x3, p2, p3);
+                    const ulonglong2 L = l2[c4];
+                    float x0, x1, x2, x3;
+                    f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 0), PF(c4 * 4 + 1)), sc2, L.x), x0, x1);
+                    f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 2), PF(c4 * 4 + 3)), sc2, L.y), x2, x3);
                     PSET(c4 * 4 + 0, ex2(x0));
                     PSET(c4 * 4 + 1, ex2(x1));
-                    PSET(c4 * 4 + 2, p2);
-                    PSET(c4 * 4 + 3, p3);
+                    PSET(c4 * 4 + 2, ex2(x2));
+                    PSET(c4 * 4 + 3, ex2(x3));
                 }
                 if (a.causal && strm_tile == tile) {       // diagonal tile: key row > query column is hidden
 #pragma unroll
@@ -368,17 +380,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         if (row_g > col_g0 + c) PSET(c, 0.f);
                 }
             } else {
-                const uint64_t neg2 = f2_pack(-my_lse2, -my_lse2);
+                const uint64_t neg2 = f2_pack(my_nlse2, my_nlse2);
 #pragma unroll
-                for (int c = 0; c < CPT; c += 4) {
-                    float x0, x1, x2, x3, p2, p3;
+                for (int c = 0; c < CPT; c += 2) {
+                    float x0, x1;
                     f2_unpack(f2_fma(f2_pack(PF(c), PF(c + 1)), sc2, neg2), x0, x1);
-                    f2_unpack(f2_fma(f2_pack(PF(c + 2), PF(c + 3)), sc2, neg2), x2, x3);
-                    ex2_poly2(x2, x3, p2, p3);
                     PSET(c, ex2(x0));
                     PSET(c + 1, ex2(x1));
-                    PSET(c + 2, p2);
-                    PSET(c + 3, p3);
                 }
                 const bool diag = a.causal && strm_tile == tile;
                 if (diag || strm_tile * kTile + kTile > a.Nk) {
@@ -420,27 +428,33 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tT2 + lane_off + cb + q * 32, dr[q]);
                 tmem_wait_ld();
                 uint32_t pk[CPT / 2];
-                const float4* d4 = reinterpret_cast<const float4*>(del_s + cb);
+                // dS = P o (dP o Z - delta); the staged vector holds -delta
+                const ulonglong2* d2 = reinterpret_cast<const ulonglong2*>(del_s + cb);
+                const uint64_t my_nd2 = f2_pack(my_ndelta, my_ndelta);
 #pragma unroll
                 for (int c4 = 0; c4 < CPT / 4; ++c4) {
-                    float4 dl;
-                    if (MODE == 0) dl = d4[c4];
-                    else dl = make_float4(my_delta, my_delta, my_delta, my_delta);
-                    const float dlt[4] = {dl.x, dl.y, dl.z, dl.w};
-                    float ds[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int c = c4 * 4 + e;
-                        const float dp = __uint_as_float(dr[c >> 5][c & 31]);
-                        if (drop) {
-                            const float z = ((kb[c >> 5] >> (c & 31)) & 1u) ? a.inv_keep : 0.f;
-                            ds[e] = PF(c) * fmaf(dp, z, -dlt[e]);
-                        } else {
-                            ds[e] = PF(c) * (dp - dlt[e]);
-                        }
+                    ulonglong2 nd;
+                    if (MODE == 0) nd = d2[c4];
+                    else { nd.x = my_nd2; nd.y = my_nd2; }
+                    const int c = c4 * 4;
+                    uint64_t dpa = f2_pack(__uint_as_float(dr[c >> 5][c & 31]), __uint_as_float(dr[c >> 5][(c + 1) & 31]));
+                    uint64_t dpb = f2_pack(__uint_as_float(dr[c >> 5][(c + 2) & 31]), __uint_as_float(dr[c >> 5][(c + 3) & 31]));
+                    uint64_t ta, tb;
+                    if (drop) {
+                        const uint32_t kw = kb[c >> 5] >> (c & 31);
+                        const uint64_t za = f2_pack((kw & 1u) ? a.inv_keep : 0.f, (kw & 2u) ? a.inv_keep : 0.f);
+                        const uint64_t zb = f2_pack((kw & 4u) ? a.inv_keep : 0.f, (kw & 8u) ? a.inv_keep : 0.f);
+                        ta = f2_fma(dpa, za, nd.x);
+                        tb = f2_fma(dpb, zb, nd.y);
+                    } else {
+                        ta = f2_add(dpa, nd.x);
+                        tb = f2_add(dpb, nd.y);
                     }
-                    pk[c4 * 2 + 0] = pack2<BF16>(ds[0], ds[1]);
-                    pk[c4 * 2 + 1] = pack2<BF16>(ds[2], ds[3]);
+                    float d0, d1, d2v, d3;
+                    f2_unpack(f2_mul(f2_pack(PF(c), PF(c + 1)), ta), d0, d1);
+                    f2_unpack(f2_mul(f2_pack(PF(c + 2), PF(c + 3)), tb), d2v, d3);
+                    pk[c4 * 2 + 0] = pack2<BF16>(d0, d1);
+                    pk[c4 * 2 + 1] = pack2<BF16>(d2v, d3);
                 }
                 if constexpr (CPT == 64) tmem_st_32x32(tT2 + lane_off + cb, pk);
                 else                     tmem_st_32x16(tT2 + lane_off + cb, pk);
@@ -511,7 +525,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (threadIdx.x == 0 && *abort_flag && a.status) atomicExch(a.status, 2 + MODE);
 }
 
-// delta and scaled lse, one warp per (b, h, padded query row)
+// negated delta and negated scaled lse (the main kernels add them), one warp per (b, h, padded query row)
 template <typename T>
 __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
@@ -524,7 +538,7 @@ bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const 
     const int64_t bh = row / nq_pad;
     const int h = (int)(bh % H), b = (int)(bh / H);
     if (i >= Nq) {
-        if (lane == 0) { lse2[row] = INFINITY; delta[row] = 0.f; }
+        if (lane == 0) { lse2[row] = -INFINITY; delta[row] = 0.f; }
         return;
     }
     const T* po = o + b * o_sb + i * o_sn + h * o_sh;
@@ -541,8 +555,8 @@ bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const 
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
     if (lane == 0) {
-        delta[row] = s;
-        lse2[row] = lse[bh * Nq + i] * kLog2e;
+        delta[row] = -s;
+        lse2[row] = -lse[bh * Nq + i] * kLog2e;
     }
 }
 
