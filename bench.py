@@ -325,7 +325,9 @@ def run_ours(args, w):
                 "workload": w.name, "B": w.B, "N": w.N, "H": w.H, "D": w.D, "causal": w.causal,
                 "dropout_p": w.dropout_p, "per_gpu": "every rank runs this shape (its own seeded shard)",
                 "parallelism": f"(batch x heads) shards, {world} rank(s), no data-path collective",
-                "l2": "not flushed: q, k, v, o, dO, dQ, dK, dV are %.0f MB each, larger than the 126 MB L2" % (tb / 1e6),
+                "l2": ("not flushed: q, k, v, o, dO, dQ, dK, dV are %.0f MB each (working set %.0f MB), %s the 126 MB L2"
+                       % (tb / 1e6, 8 * tb / 1e6, "larger than" if tb > 126 * 2 ** 20 else
+                          ("working set larger than" if 8 * tb > 126 * 2 ** 20 else "SMALLER than: L2-resident run,"))),
             },
             "per_gpu_tflops": value / world,
             "frac_of_nominal_bf16_peak": value / world / NOMINAL_BF16_TFLOPS,
