@@ -322,3 +322,30 @@ def test_error_codes_on_device(device):
     # empty problems are legal and return empty tensors
     e = torch.zeros(0, 16, 2, 64, device=device, dtype=torch.float16)
     assert fa.flash_attention_v100(e, e, e, enable_multi_gpu=False).shape == (0, 16, 2, 64)
+
+
+def test_side_stream_and_status_word(device):
+    """Work is enqueued on the caller's current stream (no implicit default-stream use),
+    and the per-device status word stays clear."""
+    from flash_attention_v100.ops.attention import check_status
+    B, N, H, D = 2, 640, 4, 128
+    q, k, v, g = (_rand((B, N, H, D), torch.bfloat16, 40 + i).to(device) for i in range(4))
+    o_ref, lse_ref = launch_forward(q, k, v, D ** -0.5, True)
+    dq_ref, dk_ref, dv_ref = launch_backward(g, q, k, v, o_ref, lse_ref, D ** -0.5, True)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device=device)
+    with torch.cuda.stream(side):
+        o, lse = launch_forward(q, k, v, D ** -0.5, True)
+        dq, dk, dv = launch_backward(g, q, k, v, o, lse, D ** -0.5, True)
+    side.synchronize()
+    assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
+    assert torch.equal(dq, dq_ref) and torch.equal(dk, dk_ref) and torch.equal(dv, dv_ref)
+    check_status(device)        # raises if any kernel reported a timed-out wait
+
+
+def test_many_small_heads_and_long_sequence_shapes(device):
+    """Grid-shape extremes of the persistent forward: more work items than SMs with one
+    block each, and one head with many blocks."""
+    _run_case(device, "tcgen05", 3, 130, 130, 70, 70, 64, torch.float16, True, seed=77)
+    _run_case(device, "tcgen05", 1, 2304, 2304, 1, 1, 128, torch.float16, True, seed=78)
+    _run_case(device, "tcgen05", 1, 1100, 2500, 2, 1, 128, torch.bfloat16, False, seed=79)
