@@ -93,14 +93,22 @@ FA_HD uint32_t dropout_keep_bits(const PhiloxKey& key, uint32_t bh, uint32_t i, 
     uint32_t w[4];
     dropout_block(key, bh, i, jblk, w);
     uint32_t bits = 0;
+#if defined(__CUDA_ARCH__)
+    // four byte compares per instruction, then gather the four 0/1 results into a nibble
+    const uint32_t thr4 = threshold * 0x01010101u;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-#pragma unroll
+        const uint32_t ge = __vcmpgeu4(w[q], thr4) & 0x01010101u;
+        bits |= (((ge * 0x01020408u) >> 24) & 0xFu) << (4 * q);
+    }
+#else
+    for (int q = 0; q < 4; ++q) {
         for (int b = 0; b < 4; ++b) {
             uint32_t byte = (w[q] >> (8 * b)) & 0xFFu;
             bits |= (byte >= threshold ? 1u : 0u) << (4 * q + b);
         }
     }
+#endif
     return bits;
 }
 
