@@ -118,7 +118,7 @@ __device__ __forceinline__ int num_blocks(const FwdArgs& a, int pair, int t) {
     return (row0 < a.Nq) ? (kv_end + kBlockN - 1) / kBlockN : 0;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool DROP>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const FwdArgs a) {
@@ -397,26 +397,40 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         }
                     }
                     // P = 2^(S*c - m): packed FMAs; of every four probabilities two take the
-                    // special-function unit and two the polynomial on the FMA pipes
+                    // special-function unit and two the polynomial on the FMA pipes.  Without
+                    // dropout P is packed to 16 bits as it is produced and each 64-key half is
+                    // stored to TMEM as soon as it is complete, so conversion and store latency
+                    // overlap the exponentials of the other half.
                     const uint64_t c2 = f2_pack(a.scale_log2, a.scale_log2), nm2 = f2_pack(-m, -m);
                     uint64_t la = 0ull, lb = 0ull;             // {0.f, 0.f}
 #pragma unroll
-                    for (int c = 0; c < 128; c += 4) {
-                        float x0, x1, x2, x3, p0, p1, p2, p3;
-                        f2_unpack(f2_fma(f2_pack(SF(c), SF(c + 1)), c2, nm2), x0, x1);
-                        f2_unpack(f2_fma(f2_pack(SF(c + 2), SF(c + 3)), c2, nm2), x2, x3);
-                        p0 = ex2(x0); p1 = ex2(x1);
-                        ex2_poly2(x2, x3, p2, p3);
-                        la = f2_add(la, f2_pack(p0, p1));
-                        lb = f2_add(lb, f2_pack(p2, p3));
-                        SSET(c, p0); SSET(c + 1, p1); SSET(c + 2, p2); SSET(c + 3, p3);
+                    for (int c0 = 0; c0 < 2; ++c0) {
+                        uint32_t pk[32];
+#pragma unroll
+                        for (int cc = 0; cc < 64; cc += 4) {
+                            const int c = c0 * 64 + cc;
+                            float x0, x1, x2, x3, p0, p1, p2, p3;
+                            f2_unpack(f2_fma(f2_pack(SF(c), SF(c + 1)), c2, nm2), x0, x1);
+                            f2_unpack(f2_fma(f2_pack(SF(c + 2), SF(c + 3)), c2, nm2), x2, x3);
+                            p0 = ex2(x0); p1 = ex2(x1);
+                            ex2_poly2(x2, x3, p2, p3);
+                            la = f2_add(la, f2_pack(p0, p1));
+                            lb = f2_add(lb, f2_pack(p2, p3));
+                            if constexpr (DROP) {
+                                SSET(c, p0); SSET(c + 1, p1); SSET(c + 2, p2); SSET(c + 3, p3);
+                            } else {
+                                pk[cc / 2] = pack2<P_BF16>(p0, p1);
+                                pk[cc / 2 + 1] = pack2<P_BF16>(p2, p3);
+                            }
+                        }
+                        if constexpr (!DROP) tmem_st_32x32(tS + c0 * 32, pk);
                     }
                     {
                         float s0, s1, s2, s3;
                         f2_unpack(la, s0, s1); f2_unpack(lb, s2, s3);
                         l += (s0 + s1) + (s2 + s3);
                     }
-                    if (a.drop_thr) {
+                    if constexpr (DROP) {
 #pragma unroll
                         for (int g = 0; g < 8; ++g) {
                             const uint32_t bits = dropout_keep_bits(a.key, bh, (uint32_t)i, (uint32_t)(j * 8 + g), a.drop_thr);
@@ -424,13 +438,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             for (int c = 0; c < 16; ++c)
                                 if (!((bits >> c) & 1u)) SSET(g * 16 + c, 0.f);
                         }
-                    }
 #pragma unroll
-                    for (int c0 = 0; c0 < 2; ++c0) {
-                        uint32_t pk[32];
+                        for (int c0 = 0; c0 < 2; ++c0) {
+                            uint32_t pk[32];
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) pk[c] = pack2<P_BF16>(SF(c0 * 64 + 2 * c), SF(c0 * 64 + 2 * c + 1));
-                        tmem_st_32x32(tS + c0 * 32, pk);
+                            for (int c = 0; c < 32; ++c) pk[c] = pack2<P_BF16>(SF(c0 * 64 + 2 * c), SF(c0 * 64 + 2 * c + 1));
+                            tmem_st_32x32(tS + c0 * 32, pk);
+                        }
                     }
 #undef SF
 #undef SSET
@@ -507,7 +521,7 @@ int launch(const fa_b200_params& p) {
     a.drop_thr = dropout_threshold(p.dropout_p);
     a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
     a.key = philox_make_key(p.seed, p.offset);
-    auto kernel = fwd_sm100_kernel<D, BF16>;
+    auto kernel = a.drop_thr ? fwd_sm100_kernel<D, BF16, true> : fwd_sm100_kernel<D, BF16, false>;
     FA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     const int sms = sm_count(p.device);
     if (sms <= 0) { set_error("cannot read the SM count of device %d", p.device); return FA_ECUDA; }
