@@ -223,22 +223,28 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             constexpr uint32_t idesc_acc = make_idesc_f16(BF16, BF16, kTile, D, false, true);
             const uint32_t sX_u = smem_u32(sX), sY_u = smem_u32(sY), sRing_u = smem_u32(sRing);
 
+            // Descriptors differ only in the 16-byte-granular start address held in their low
+            // bits: build the two kinds once and add offsets in the issue loops, which keeps the
+            // single issuing thread's instruction count per MMA small.
+            const uint64_t dk_major = make_smem_desc_sw128(0, 0, 1024);            // K-major operand
+            const uint64_t dmn_major = make_smem_desc_sw128(0, kBoxBytes, 1024);   // MN-major operand
             auto issue_t = [&](uint32_t d_tmem, uint32_t stat_u, uint32_t strm_u) {
+                const uint64_t a0 = dk_major + (uint64_t)(stat_u >> 4), b0 = dk_major + (uint64_t)(strm_u >> 4);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (uint32_t)(kk >> 2) * kBoxBytes + (uint32_t)(kk & 3) * 32u;
-                    mma_ss_f16(d_tmem, make_smem_desc_sw128(stat_u + off, 0, 1024),
-                               make_smem_desc_sw128(strm_u + off, 0, 1024), idesc_t, kk > 0);
+                    const uint32_t off = ((uint32_t)(kk >> 2) * kBoxBytes + (uint32_t)(kk & 3) * 32u) >> 4;
+                    mma_ss_f16(d_tmem, a0 + off, b0 + off, idesc_t, kk > 0);
                 }
             };
             // acc (+)= A[TMEM] * B[smem tile, MN-major].  A holds 16-bit pairs: the thread group that owns
             // columns [g*CPT, (g+1)*CPT) of T wrote its CPT values packed into columns [g*CPT, g*CPT + CPT/2).
             auto issue_acc = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t strm_u, bool acc) {
+                const uint64_t b0 = dmn_major + (uint64_t)(strm_u >> 4);
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk) {
                     const uint32_t a_col = (uint32_t)((16 * kk) / CPT) * CPT + (uint32_t)((16 * kk) % CPT) / 2u;
-                    mma_ts_f16(d_tmem, a_tmem + a_col, make_smem_desc_sw128(strm_u + kk * 2048, kBoxBytes, 1024),
-                               idesc_acc, (acc || kk > 0) ? 1u : 0u);
+                    mma_ts_f16(d_tmem, a_tmem + a_col, b0 + (uint64_t)((kk * 2048) >> 4), idesc_acc,
+                               (acc || kk > 0) ? 1u : 0u);
                 }
             };
 

@@ -243,22 +243,28 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             constexpr uint32_t idesc_pv = make_idesc_f16(P_BF16, BF16, kBlockM, D, false, true);
             const uint32_t sQ_u = smem_u32(sQ), sK_u = smem_u32(sK), sV_u = smem_u32(sV);
 
+            // Descriptors differ only in the 16-byte-granular start address held in their low
+            // bits: build one per buffer here and add offsets in the issue loops, which keeps the
+            // single issuing thread's instruction count per MMA small.
+            const uint64_t dQ = make_smem_desc_sw128(sQ_u, 0, 1024);
+            const uint64_t dK = make_smem_desc_sw128(sK_u, 0, 1024);
+            const uint64_t dV = make_smem_desc_sw128(sV_u, kBoxBytes, 1024);
             auto issue_s = [&](int t, int ks) {
+                const uint64_t a0 = dQ + (uint64_t)((t * TILE) >> 4), b0 = dK + (uint64_t)((ks * TILE) >> 4);
+                const uint32_t d = tmem + (uint32_t)t * 128u;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (uint32_t)(kk >> 2) * kBoxBytes + (uint32_t)(kk & 3) * 32u;
-                    mma_ss_f16(tmem + (uint32_t)t * 128u,
-                               make_smem_desc_sw128(sQ_u + t * TILE + off, 0, 1024),
-                               make_smem_desc_sw128(sK_u + ks * TILE + off, 0, 1024), idesc_s, kk > 0);
+                    const uint32_t off = ((uint32_t)(kk >> 2) * kBoxBytes + (uint32_t)(kk & 3) * 32u) >> 4;
+                    mma_ss_f16(d, a0 + off, b0 + off, idesc_s, kk > 0);
                 }
             };
             auto issue_pv = [&](int t, int vs, bool acc) {
+                const uint64_t b0 = dV + (uint64_t)((vs * TILE) >> 4);
+                const uint32_t d = tmem + 256u + (uint32_t)t * 128u, a0 = tmem + (uint32_t)t * 128u;
 #pragma unroll
-                for (int kk = 0; kk < kBlockN / 16; ++kk) {
-                    mma_ts_f16(tmem + 256u + (uint32_t)t * 128u, tmem + (uint32_t)t * 128u + (uint32_t)kk * 8u,
-                               make_smem_desc_sw128(sV_u + vs * TILE + kk * 2048, kBoxBytes, 1024), idesc_pv,
+                for (int kk = 0; kk < kBlockN / 16; ++kk)
+                    mma_ts_f16(d, a0 + (uint32_t)kk * 8u, b0 + (uint64_t)((kk * 2048) >> 4), idesc_pv,
                                (acc || kk > 0) ? 1u : 0u);
-                }
             };
 
             int kvc = 0;                    // K/V blocks consumed so far
