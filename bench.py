@@ -109,7 +109,7 @@ def measured_peak():
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
 # profiles/ncu_full_fwd_bwd_cfg3_batch1.md: measured at batch 1 of the default workload and scaled by
 # the batch (traffic is proportional to the number of independent (batch, head) columns).
-NCU_DRAM_BYTES_PER_BATCH = {"fwd": 113.2e6, "bwd_dkdv": 177.9e6, "bwd_dq": 155.4e6}
+NCU_DRAM_BYTES_PER_BATCH = {"fwd": 112.8e6, "bwd_dkdv": 178.2e6, "bwd_dq": 155.8e6}
 
 
 def ncu_traffic(kernel: str, w):
