@@ -20,6 +20,8 @@ from .memory import (
     backward_workspace_bytes,
 )
 
+from .host_pipeline import HostAttentionStep, chunk_bounds, chunk_dropout_offset
+
 __version__ = "0.1.0"
 
 __all__ = [
@@ -27,4 +29,5 @@ __all__ = [
     "compare_with_pytorch_attention", "set_dropout_seed", "kernel_variant",
     "allocate_attention_workspace", "free_attention_workspace", "estimate_peak_memory_usage",
     "get_memory_statistics", "backward_workspace_bytes",
+    "HostAttentionStep", "chunk_bounds", "chunk_dropout_offset",
 ]

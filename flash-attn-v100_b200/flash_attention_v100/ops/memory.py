@@ -22,6 +22,7 @@ def _sizes_params(batch_size, seq_len_q, seq_len_k, num_heads, head_dim, dtype, 
     p.B, p.Nq, p.Nk, p.H, p.D = batch_size, seq_len_q, seq_len_k, num_heads, head_dim
     p.Hkv = num_heads if num_heads_kv is None else num_heads_kv
     p.dtype = dtype_enum(dtype)
+    p.scale = 1.0          # any valid scale: the size does not depend on it, kernel selection checks it
     return p
 
 
