@@ -16,6 +16,15 @@
 // results are bit-reproducible (the reference accumulates dQ across CTAs with
 // an unordered read-modify-write, kernels/backward_kernel.py:179-194).
 //
+// D = 64 has a faster route (MODE 2) unless the two-pass variant is asked for:
+// the key-stationary kernel also forms the step's dQ tile, dS K_j, from the
+// dS^T tile its threads leave in shared memory, and adds it to an fp32 buffer in
+// global memory (red.global.add.v4.f32, order across CTAs not fixed); S and dP
+// are then computed once instead of twice.  Launches: memset of the buffer +
+// preprocess, MODE 2, and a conversion of the sums to dQ.  At D = 128 tensor
+// memory has no columns left for the dQ tile and the additions cost more than
+// the second kernel's recomputation, so that size keeps the two passes.
+//
 // Both modes run the same pipeline on a stationary pair (X, Y) and a streamed
 // pair (U, W):
 //                         MODE 0 (dK, dV)          MODE 1 (dQ)
@@ -39,7 +48,7 @@
 //
 // TMEM columns: T1 [0,128)  T2 [128,256)  ACC1 [256,256+D)  ACC2 [384,384+D).
 // MODE 1 has no ACC2 and uses [384,512) as a second S buffer: S(i+1) is computed
-// while the threads still work on S(i).
+// while the threads still work on S(i).  MODE 2 (D = 64) puts the dQ tile at [448,512).
 // Every mbarrier wait is bounded; see sm100_ptx.cuh.
 #include "fa_common.cuh"
 #include "sm100_ptx.cuh"
@@ -54,6 +63,8 @@ using namespace ptx;
 constexpr int kTile = 128;
 constexpr int kBoxBytes = 128 * 128;
 constexpr int kNWG = 4;                  // elementwise warpgroups per CTA (each owns 128 / kNWG columns)
+constexpr int kExtraThreads = 128;       // MMA warp + TMA warp + two idle warps: registers are granted per
+                                         // four warps, so dropping the idle pair would free none
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>
@@ -73,13 +84,26 @@ struct BwdCfg {
     static constexpr int kAccDone = kDsReady + 1;
     static constexpr int kMask = kAccDone + 1;                   // one arrival per elementwise warp
     static constexpr int kEpi = kMask + 1;                       // one arrival per elementwise warp
-    static constexpr int kNumBars = kEpi + 1;
-    static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kStageBytes + kMaskBytes + kNumBars * 8 + 64 + 1024;
+    static constexpr int kDqFull = kEpi + 1;                     // fused kernel: dQ tile of the step complete
+    static constexpr int kDqRead = kDqFull + 1;                  // ... and read out (one arrival per warp)
+    static constexpr int kNumBars = kDqRead + 1;
+    static constexpr int kDsBytes = 128 * 128 * 2;               // fused kernel: dS^T tile for the dQ MMA
+    // bytes used from the 1024-aligned base: tiles, ring, [dS], barriers, TMEM slot + flag, [masks]
+    __host__ __device__ static constexpr int used_bytes(bool fused, bool drop) {
+        return 2 * kTileBytes + kStages * kStageBytes + (fused ? kDsBytes : 0) + (drop ? kMaskBytes : 0) +
+               kNumBars * 8 + 64;
+    }
+    static constexpr int kMaxSmem = 232448;                      // 227 KB: the most one CTA can ask for
+    // what the launch asks for: room to align the base when it fits (the kernel checks what it got)
+    static constexpr int smem_bytes(bool fused, bool drop) {
+        return used_bytes(fused, drop) + 1024 <= kMaxSmem ? used_bytes(fused, drop) + 1024 : kMaxSmem;
+    }
 };
 
 struct BwdArgs {
     const float* lse2;     // [B*H][nq_pad]  -lse * log2(e), -inf in the padding
     const float* delta;    // [B*H][nq_pad]  -delta, 0 in the padding
+    float* dq_acc;         // fused kernel: fp32 dQ sums, [B*H][nq_pad/128] tiles of [D/4][128 rows][4]
     int32_t* status;
     int B, Nq, Nk, H, Hkv, nq_pad;
     int causal;
@@ -97,26 +121,38 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
 }
 
 // MODE 0: dK, dV (key-stationary).  MODE 1: dQ (query-stationary).
-template <int D, bool BF16, int MODE, int NWG>
-__global__ void __launch_bounds__(128 * (NWG + 1), 1)
+template <int D, bool BF16, int MODE, int NWG, bool DROP>
+__global__ void __launch_bounds__(128 * NWG + kExtraThreads, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                  const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_out1, const __grid_constant__ CUtensorMap map_out2,
                  const BwdArgs a) {
     using Cfg = BwdCfg<D>;
+    constexpr bool KS = (MODE != 1);        // key-stationary: K, V stay, query tiles stream
+    constexpr bool FUSED = (MODE == 2);     // key-stationary and dQ too
     constexpr int ST = Cfg::kStages;
     constexpr int TILE = Cfg::kTileBytes;
-    constexpr uint32_t kStageTx = (MODE == 0) ? (2 * TILE + 1024) : (2 * TILE);
+    constexpr uint32_t kStageTx = (KS) ? (2 * TILE + 1024) : (2 * TILE);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sX = smem;
     uint8_t* sY = sX + TILE;
     uint8_t* sRing = sY + TILE;                     // stage s: U | W | lse[128] | delta[128]
-    uint16_t* sMask = (uint16_t*)(sRing + ST * Cfg::kStageBytes);
-    uint64_t* bars = (uint64_t*)((uint8_t*)sMask + Cfg::kMaskBytes);
+    uint8_t* sDs = sRing + ST * Cfg::kStageBytes;   // fused kernel only
+    uint64_t* bars = (uint64_t*)(sDs + (FUSED ? Cfg::kDsBytes : 0));
     uint32_t* tmem_slot = (uint32_t*)(bars + Cfg::kNumBars);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
+    uint16_t* sMask = (uint16_t*)((uint8_t*)bars + Cfg::kNumBars * 8 + 64);    // present with dropout only
+    {
+        // the launch may have had no room for a full kilobyte of alignment slack
+        uint32_t dyn;
+        asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+        if ((uint32_t)(smem - smem_raw) + (uint32_t)Cfg::used_bytes(FUSED, DROP) > dyn) {
+            if (threadIdx.x == 0 && a.status) atomicExch(a.status, 8);
+            return;
+        }
+    }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z;
@@ -125,7 +161,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
     // iteration space (uniform over the CTA)
     int tile, head_x, it0, n_per_head, n_iter;
-    if (MODE == 0) {
+    if (KS) {
         tile = blockIdx.x;                          // key tile
         head_x = blockIdx.y;                        // kv head
         it0 = a.causal ? tile : 0;                  // first query tile that sees this key tile
@@ -140,11 +176,21 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         n_per_head = (kv_end + kTile - 1) / kTile;
         n_iter = n_per_head;
     }
-    const int head_kv = (MODE == 0) ? head_x : head_x / group;
+    const int head_kv = (KS) ? head_x : head_x / group;
+    // Key-stationary kernels: query tile of step `it`.  The fused kernel without a causal mask starts
+    // each key tile's walk at a different query tile, so that the CTAs of one head, which run at
+    // the same time, add to different dQ tiles (under a causal mask the walks are staggered already).
+    const int rot = (FUSED && !a.causal && n_per_head > 0) ? tile % n_per_head : 0;
+    auto q_tile_of = [&](int it) {
+        int t = it % n_per_head + rot;
+        if (t >= n_per_head) t -= n_per_head;
+        return it0 + t;
+    };
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kNumBars; ++i) {
-            const bool wide = (i == Cfg::kPReady || i == Cfg::kDsReady || i == Cfg::kMask || i == Cfg::kEpi);
+            const bool wide = (i == Cfg::kPReady || i == Cfg::kDsReady || i == Cfg::kMask || i == Cfg::kEpi ||
+                               i == Cfg::kDqRead);
             mbar_init(&bars[i], wide ? 4u * NWG : 1u);    // one arrival per elementwise warp
         }
         *abort_flag = 0u;
@@ -160,13 +206,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         prefetch_tensormap(&map_x); prefetch_tensormap(&map_y);
         prefetch_tensormap(&map_u); prefetch_tensormap(&map_w);
         prefetch_tensormap(&map_out1);
-        if (MODE == 0) prefetch_tensormap(&map_out2);
+        if (KS) prefetch_tensormap(&map_out2);
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tT1 = tmem, tT2 = tmem + 128u, tAcc1 = tmem + 256u, tAcc2 = tmem + 384u;
+    // fused kernel: the per-step dQ tile has columns of its own when D = 64 and shares T2's when D = 128
+    constexpr bool kDqAliasesT2 = (D > 64);
+    const uint32_t tDq = kDqAliasesT2 ? tT2 : tmem + 448u;
 
     if (warp >= kMmaWarp) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
@@ -190,7 +239,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 if (!ok) break;
                 uint8_t* stage = sRing + s * Cfg::kStageBytes;
                 int head_u, row_u;
-                if (MODE == 0) { head_u = head_x * group + it / n_per_head; row_u = (it0 + it % n_per_head) * kTile; }
+                if (KS) { head_u = head_x * group + it / n_per_head; row_u = q_tile_of(it) * kTile; }
                 else           { head_u = head_kv; row_u = it * kTile; }
                 mbar_expect_tx(&bars[Cfg::kUWFull + s], kStageTx);
 #pragma unroll
@@ -198,7 +247,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     tma_load_4d(stage + bx * kBoxBytes, &map_u, &bars[Cfg::kUWFull + s], bx * 64, head_u, row_u, b);
                     tma_load_4d(stage + TILE + bx * kBoxBytes, &map_w, &bars[Cfg::kUWFull + s], bx * 64, head_u, row_u, b);
                 }
-                if (MODE == 0) {
+                if (KS) {
                     const int64_t off = ((int64_t)b * a.H + head_u) * a.nq_pad + row_u;
                     bulk_load_1d(stage + 2 * TILE, a.lse2 + off, 512, &bars[Cfg::kUWFull + s]);
                     bulk_load_1d(stage + 2 * TILE + 512, a.delta + off, 512, &bars[Cfg::kUWFull + s]);
@@ -248,6 +297,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
             };
 
+            // fused kernel: the step's dQ tile (fresh accumulation) from two shared-memory operands
+            constexpr uint32_t idesc_dq = make_idesc_f16(BF16, BF16, kTile, D, true, true);
+            const uint32_t sDs_u = smem_u32(sDs);
+            auto issue_dq = [&]() {
+                const uint64_t a0 = dmn_major + (uint64_t)(sDs_u >> 4), b0 = dmn_major + (uint64_t)(sX_u >> 4);
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)
+                    mma_ss_f16(tDq, a0 + (uint64_t)((kk * 2048) >> 4), b0 + (uint64_t)((kk * 2048) >> 4), idesc_dq,
+                               kk > 0);
+            };
+
             bool ok = mbar_wait(&bars[Cfg::kXYFull], 0u, abort_flag);
             if (ok) ok = mbar_wait(&bars[Cfg::kUWFull + 0], 0u, abort_flag);
             if (ok) {
@@ -263,7 +323,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 const uint32_t cur_u = sRing_u + s * Cfg::kStageBytes, nxt_u = sRing_u + ns * Cfg::kStageBytes;
                 const bool more = it + 1 < n_iter;
                 if (more) { ok = mbar_wait(&bars[Cfg::kUWFull + ns], nph, abort_flag); if (!ok) break; }
-                if (MODE == 0) {
+                if (KS) {
                     ok = mbar_wait(&bars[Cfg::kPReady], (uint32_t)it & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after_sync();
@@ -284,6 +344,25 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 tc_fence_after_sync();
                 issue_acc(tAcc1, tT2, cur_u, it > 0);                            // dK += dS^T Q  /  dQ += dS K
                 mma_commit(&bars[Cfg::kUWEmpty + s]);
+                if (FUSED) {
+                    // dQ tile of this step = dS K_j: A is the dS^T tile the threads left in shared memory,
+                    // read MN-major (M = queries), B is the stationary K tile read MN-major (N = D)
+                    if (!kDqAliasesT2 && it > 0) {
+                        // own columns: only the previous tile's read-out has to precede (issuing
+                        // dP^T(it+1) ahead of this MMA measured slower)
+                        ok = mbar_wait(&bars[Cfg::kDqRead], (uint32_t)(it - 1) & 1u, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                    }
+                    issue_dq();
+                    mma_commit(&bars[Cfg::kDqFull]);
+                    if (more && kDqAliasesT2) {
+                        // the tile sits in T2's columns: dP^T(it+1) may only follow its read-out
+                        ok = mbar_wait(&bars[Cfg::kDqRead], (uint32_t)it & 1u, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                    }
+                }
                 if (more) { issue_t(tT2, sY_u, nxt_u + TILE); mma_commit(&bars[Cfg::kT2Full]); }
             }
             if (ok) mma_commit(&bars[Cfg::kAccDone]);
@@ -301,7 +380,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const int tid = wg * 128 + r;                          // 0 .. 128*NWG-1
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const int row_g = tile * kTile + r;                    // MODE 0: key index; MODE 1: query index
-        const bool drop = a.drop_thr != 0u;
+        constexpr bool drop = DROP;
         float my_nlse2 = 0.f, my_ndelta = 0.f;      // -lse*log2(e) and -delta of my query row (MODE 1)
         if (MODE == 1) {
             const int64_t off = ((int64_t)b * a.H + head_x) * a.nq_pad + row_g;
@@ -310,14 +389,39 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
         bool ok = true;
 
+        // fused kernel: add the dQ tile of step `jt` (queries on the TMEM lanes, my D / NWG columns)
+        // to the fp32 sums in global memory; the order of additions across CTAs is not fixed
+        auto drain_dq = [&](int jt) -> bool {
+            constexpr int DQC = D / NWG;
+            bool good = mbar_wait(&bars[Cfg::kDqFull], (uint32_t)jt & 1u, abort_flag);
+            good = __all_sync(0xffffffffu, good);
+            if (!good) return false;
+            tc_fence_after_sync();
+            uint32_t acc[DQC];
+            if constexpr (DQC == 32) tmem_ld_32x32(tDq + lane_off + (uint32_t)(wg * DQC), acc);
+            else                     tmem_ld_32x16(tDq + lane_off + (uint32_t)(wg * DQC), acc);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive_warp(&bars[Cfg::kDqRead]);
+            const int q_tile = q_tile_of(jt);
+            const int head_q = head_x * group + jt / n_per_head;
+            float* dst = a.dq_acc + (((int64_t)b * a.H + head_q) * (a.nq_pad / kTile) + q_tile) * (int64_t)(kTile * D) +
+                         ((int64_t)(wg * (DQC / 4)) * kTile + r) * 4;
+#pragma unroll
+            for (int v = 0; v < DQC / 4; ++v)
+                red_add_v4_f32(dst + (int64_t)v * kTile * 4, __uint_as_float(acc[4 * v]), __uint_as_float(acc[4 * v + 1]),
+                               __uint_as_float(acc[4 * v + 2]), __uint_as_float(acc[4 * v + 3]));
+            return true;
+        };
+
         for (int it = 0; it < n_iter; ++it) {
             const int s = it % ST;
             const uint8_t* stage = sRing + s * Cfg::kStageBytes;
             const float* lse_s = reinterpret_cast<const float*>(stage + 2 * TILE);
             const float* del_s = lse_s + 128;
-            const int strm_tile = (MODE == 0) ? it0 + it % n_per_head : it;     // query tile (0) / key tile (1)
+            const int strm_tile = (KS) ? q_tile_of(it) : it;     // query tile (0) / key tile (1)
             const int col_g0 = strm_tile * kTile + cb;                          // global index of my first column
-            const int head_q = (MODE == 0) ? head_x * group + it / n_per_head : head_x;
+            const int head_q = (KS) ? head_x * group + it / n_per_head : head_x;
             const uint32_t bh = (uint32_t)(b * a.H + head_q);
 
             // ---- dropout keep bits of my CPT columns (bit c of kb[c / 32])
@@ -353,7 +457,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
 
             // ---- phase A: P from T1
-            ok = (MODE == 0) ? mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag)
+            ok = (KS) ? mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag)
                              : mbar_wait(&bars[Cfg::kT1Full + (it & 1)], (uint32_t)(it >> 1) & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -366,7 +470,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tS + lane_off + cb + q * 32, pr[q]);
             tmem_wait_ld();
             const uint64_t sc2 = f2_pack(a.scale_log2, a.scale_log2);
-            if (MODE == 0) {
+            if (KS) {
                 // P = 2^(S*c - lse): the staged vector holds -lse*log2(e), two columns per 64-bit word
                 const ulonglong2* l2 = reinterpret_cast<const ulonglong2*>(lse_s + cb);
 #pragma unroll
@@ -403,7 +507,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     }
                 }
             }
-            if (MODE == 0) {
+            if (KS) {
                 uint32_t pk[CPT / 2];
                 if (drop) {
 #pragma unroll
@@ -423,6 +527,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tc_fence_before_sync();
             mbar_arrive_warp(&bars[Cfg::kPReady]);
 
+            if (FUSED && it > 0) {
+                // dQ of the previous step: its MMAs ran while phase A above did
+                ok = drain_dq(it - 1);
+                if (!ok) break;
+            }
+
             // ---- phase B: dS from T2
             ok = mbar_wait(&bars[Cfg::kT2Full], (uint32_t)it & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
@@ -440,7 +550,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                 for (int c4 = 0; c4 < CPT / 4; ++c4) {
                     ulonglong2 nd;
-                    if (MODE == 0) nd = d2[c4];
+                    if (KS) nd = d2[c4];
                     else { nd.x = my_nd2; nd.y = my_nd2; }
                     const int c = c4 * 4;
                     uint64_t dpa = f2_pack(__uint_as_float(dr[c >> 5][c & 31]), __uint_as_float(dr[c >> 5][(c + 1) & 31]));
@@ -464,6 +574,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
                 if constexpr (CPT == 64) tmem_st_32x32(tT2 + lane_off + cb, pk);
                 else                     tmem_st_32x16(tT2 + lane_off + cb, pk);
+                if (FUSED) {
+                    // the same dS^T values as a shared-memory tile [key row][query], 64-query boxes with
+                    // the 128-byte swizzle: the A operand (MN-major) of the dQ MMA.  The previous
+                    // step's dQ MMA has finished reading it: its completion was awaited in drain_dq.
+#pragma unroll
+                    for (int v = 0; v < CPT / 8; ++v) {
+                        const int q0 = cb + v * 8;                                  // first of 8 queries
+                        uint8_t* dst = sDs + (q0 >> 6) * kBoxBytes + r * 128 + ((((q0 & 63) >> 3) ^ (r & 7)) << 4);
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+                    }
+                    fence_proxy_async_smem();
+                }
                 tmem_wait_st();
             }
 #undef PF
@@ -472,13 +594,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             mbar_arrive_warp(&bars[Cfg::kDsReady]);
         }
 
+        if (FUSED && n_iter > 0 && ok) ok = drain_dq(n_iter - 1);
+
         // ---- epilogue: accumulators -> 16-bit -> swizzled staging -> TMA store
         if (n_iter > 0 && ok) ok = mbar_wait(&bars[Cfg::kAccDone], 0u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after_sync();
             constexpr int kCols = D / NWG;                     // my share of the D accumulator columns: 16..64
-            constexpr int kOuts = (MODE == 0) ? 2 : 1;
+            constexpr int kOuts = (KS) ? 2 : 1;
 #pragma unroll
             for (int o = 0; o < kOuts; ++o) {
                 const uint32_t tacc = (o == 0 ? tAcc1 : tAcc2) + lane_off + (uint32_t)(wg * kCols);
@@ -516,7 +640,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kNBox; ++bx) {
                     tma_store_4d(&map_out1, sRing + bx * kBoxBytes, bx * 64, head_x, tile * kTile, b);
-                    if (MODE == 0)
+                    if (KS)
                         tma_store_4d(&map_out2, sRing + TILE + bx * kBoxBytes, bx * 64, head_x, tile * kTile, b);
                 }
                 tma_store_commit();
@@ -566,6 +690,30 @@ bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const 
     }
 }
 
+// fused backward: fp32 dQ sums (tiles of [D/4][128 rows][4]) * scale -> dQ in the call's dtype and layout
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+bwd_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, int Nq, int H, int n_tiles, float scale,
+                      int64_t sb, int64_t sn, int64_t sh) {
+    const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const float* src = acc + (((int64_t)b * H + h) * n_tiles + tile) * (int64_t)(kTile * D);
+    const int row = threadIdx.x & 127;
+    const int i = tile * kTile + row;
+    if (i >= Nq) return;
+    T* out = dq + b * sb + (int64_t)i * sn + h * sh;
+#pragma unroll
+    for (int cg = threadIdx.x >> 7; cg < D / 8; cg += 2) {      // 8 columns = two 4-column groups
+        const float4 lo = *reinterpret_cast<const float4*>(src + ((int64_t)(2 * cg) * kTile + row) * 4);
+        const float4 hi = *reinterpret_cast<const float4*>(src + ((int64_t)(2 * cg + 1) * kTile + row) * 4);
+        uint4 v4;
+        v4.x = pack2<std::is_same<T, __nv_bfloat16>::value>(lo.x * scale, lo.y * scale);
+        v4.y = pack2<std::is_same<T, __nv_bfloat16>::value>(lo.z * scale, lo.w * scale);
+        v4.z = pack2<std::is_same<T, __nv_bfloat16>::value>(hi.x * scale, hi.y * scale);
+        v4.w = pack2<std::is_same<T, __nv_bfloat16>::value>(hi.z * scale, hi.w * scale);
+        *reinterpret_cast<uint4*>(out + cg * 8) = v4;
+    }
+}
+
 template <int D, bool BF16>
 int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     using Cfg = BwdCfg<D>;
@@ -576,8 +724,13 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     float* delta = (float*)((char*)p.workspace + ws.delta_off);
     float* lse2 = (float*)((char*)p.workspace + ws.lse2_off);
 
+    const bool fused = ws.dq_bytes > 0;
+    float* dq_acc = fused ? (float*)((char*)p.workspace + ws.dq_off) : nullptr;
+    const bool drop = dropout_threshold(p.dropout_p) != 0u;
+
     const int phases = p.bwd_phases ? p.bwd_phases : 7;
     if (phases & 1) {
+        if (fused) FA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, ws.dq_bytes, st));
         const int64_t rows = (int64_t)p.B * p.H * nq_pad;
         bwd_preprocess_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
             (const T*)p.o.ptr, (const T*)p.d_o.ptr, p.lse, lse2, delta, p.B, p.Nq, p.H, D, nq_pad,
@@ -598,7 +751,7 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
         return FA_ECUDA;
     }
     BwdArgs a;
-    a.lse2 = lse2; a.delta = delta; a.status = p.status_word;
+    a.lse2 = lse2; a.delta = delta; a.dq_acc = dq_acc; a.status = p.status_word;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv; a.nq_pad = nq_pad;
     a.causal = p.causal;
     a.scale = p.scale;
@@ -607,25 +760,50 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
     a.key = philox_make_key(p.seed, p.offset);
 
-    constexpr int kThreads = 128 * (kNWG + 1);
-    auto k0 = bwd_sm100_kernel<D, BF16, 0, kNWG>;
-    auto k1 = bwd_sm100_kernel<D, BF16, 1, kNWG>;
-    FA_CUDA_CHECK(cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    FA_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    constexpr int kThreads = 128 * kNWG + kExtraThreads;
+    const dim3 grid_kv((p.Nk + kTile - 1) / kTile, p.Hkv, p.B);
+    const dim3 grid_q((p.Nq + kTile - 1) / kTile, p.H, p.B);
+    if constexpr (D == 64) if (fused) {
+        // one key-stationary kernel for dK, dV and the fp32 dQ sums, then the conversion of dQ
+        auto k2 = drop ? bwd_sm100_kernel<D, BF16, 2, kNWG, true> : bwd_sm100_kernel<D, BF16, 2, kNWG, false>;
+        const int smem2 = Cfg::smem_bytes(true, drop);
+        FA_CUDA_CHECK(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
+        if (phases & 2) {
+            k2<<<grid_kv, kThreads, smem2, st>>>(mk, mv, mq, mg, mdk, mdv, a);
+            FA_CUDA_CHECK(cudaGetLastError());
+        }
+        if (phases & 4) {
+            bwd_dq_convert_kernel<T, D><<<grid_q, 256, 0, st>>>(dq_acc, (T*)p.dq.ptr, p.Nq, p.H, nq_pad / kTile, p.scale,
+                                                               p.dq.stride_b, p.dq.stride_n, p.dq.stride_h);
+            FA_CUDA_CHECK(cudaGetLastError());
+        }
+        return FA_OK;
+    }
+    auto k0 = drop ? bwd_sm100_kernel<D, BF16, 0, kNWG, true> : bwd_sm100_kernel<D, BF16, 0, kNWG, false>;
+    auto k1 = drop ? bwd_sm100_kernel<D, BF16, 1, kNWG, true> : bwd_sm100_kernel<D, BF16, 1, kNWG, false>;
+    const int smem01 = Cfg::smem_bytes(false, drop);
+    FA_CUDA_CHECK(cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, smem01));
+    FA_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem01));
     if (phases & 2) {
-        dim3 grid_kv((p.Nk + kTile - 1) / kTile, p.Hkv, p.B);
-        k0<<<grid_kv, kThreads, Cfg::kSmemBytes, st>>>(mk, mv, mq, mg, mdk, mdv, a);
+        k0<<<grid_kv, kThreads, smem01, st>>>(mk, mv, mq, mg, mdk, mdv, a);
         FA_CUDA_CHECK(cudaGetLastError());
     }
     if (phases & 4) {
-        dim3 grid_q((p.Nq + kTile - 1) / kTile, p.H, p.B);
-        k1<<<grid_q, kThreads, Cfg::kSmemBytes, st>>>(mq, mg, mk, mv, mdq, mdq, a);
+        k1<<<grid_q, kThreads, smem01, st>>>(mq, mg, mk, mv, mdq, mdq, a);
         FA_CUDA_CHECK(cudaGetLastError());
     }
     return FA_OK;
 }
 
 }  // namespace
+
+bool sm100_bwd_fused_supported(const fa_b200_params& p) {
+    // D = 64 only.  At D = 128 tensor memory is full (S^T, dP^T, dK, dV), the per-step dQ tile has
+    // to share dP^T's columns, which serialises the step, and the fp32 additions (64 KB per step)
+    // cost more than recomputing S and dP in a second kernel: measured on B200 (B4 N4096 H32
+    // causal) 2.12 ms against 1.95 ms for the two kernels.
+    return p.D == 64;
+}
 
 int sm100_bwd(const fa_b200_params& p, const BwdWorkspace& ws) {
     if (p.dtype == FA_B200_BF16) return p.D == 128 ? launch<128, true>(p, ws) : launch<64, true>(p, ws);

@@ -39,11 +39,13 @@ static inline size_t dtype_bytes(int dtype) { return dtype == FA_B200_F32 ? 4 : 
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // ---- workspace layout (backward) -------------------------------------------
-// [ delta : B*H*nq_pad fp32 | pad to 256 | lse*log2(e) : B*H*nq_pad fp32 (tensor-core family only) ]
+// [ delta : B*H*nq_pad fp32 | pad to 256 | lse*log2(e) : B*H*nq_pad fp32 (tensor-core family only)
+//   | pad to 256 | dQ sums : B*H*nq_pad*D fp32 (one-kernel tensor-core backward only) ]
 // nq_pad = Nq rounded up to 128; the CUDA-core family indexes delta unpadded.
 struct BwdWorkspace {
     size_t delta_off, delta_bytes;
     size_t lse2_off, lse2_bytes;
+    size_t dq_off, dq_bytes;
     size_t total;
 };
 BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant);
@@ -58,6 +60,8 @@ bool simt_supports(const fa_b200_params& p);
 int sm100_fwd(const fa_b200_params& p);
 int sm100_bwd(const fa_b200_params& p, const BwdWorkspace& ws);
 bool sm100_supports(const fa_b200_params& p, bool backward, const char** why);
+// Whether the one-kernel backward (dQ summed with global additions) covers a call the family supports.
+bool sm100_bwd_fused_supported(const fa_b200_params& p);
 
 // Number of SMs of a device (cached per device; 0 on failure).
 int sm_count(int device);

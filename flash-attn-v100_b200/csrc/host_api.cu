@@ -25,8 +25,12 @@ BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant) {
     w.delta_off = 0;
     w.delta_bytes = (size_t)p.B * p.H * nq_pad * sizeof(float);
     w.lse2_off = align_up(w.delta_bytes, 256);
-    w.lse2_bytes = (variant == FA_B200_VARIANT_TCGEN05) ? w.delta_bytes : 0;
-    w.total = w.lse2_off + w.lse2_bytes;
+    const bool tc = (variant == FA_B200_VARIANT_TCGEN05 || variant == FA_B200_VARIANT_TCGEN05_2PASS);
+    w.lse2_bytes = tc ? w.delta_bytes : 0;
+    w.dq_off = align_up(w.lse2_off + w.lse2_bytes, 256);
+    w.dq_bytes = (variant == FA_B200_VARIANT_TCGEN05 && sm100_bwd_fused_supported(p))
+                     ? (size_t)p.B * p.H * nq_pad * (size_t)p.D * sizeof(float) : 0;
+    w.total = w.dq_bytes ? w.dq_off + w.dq_bytes : w.lse2_off + w.lse2_bytes;
     if (w.total == 0) w.total = 256;
     return w;
 }
@@ -87,7 +91,7 @@ int validate_common(const fa_b200_params* p, bool backward) {
         set_error("unknown dtype %d", p->dtype);
         return FA_EINVAL;
     }
-    if (p->variant < FA_B200_VARIANT_AUTO || p->variant > FA_B200_VARIANT_TCGEN05) {
+    if (p->variant < FA_B200_VARIANT_AUTO || p->variant > FA_B200_VARIANT_TCGEN05_2PASS) {
         set_error("unknown variant %d", p->variant);
         return FA_EINVAL;
     }
@@ -123,9 +127,9 @@ int validate_common(const fa_b200_params* p, bool backward) {
 int choose_variant(const fa_b200_params& p, bool backward, int* variant) {
     const char* why = "";
     bool tc = sm100_supports(p, backward, &why);
-    if (p.variant == FA_B200_VARIANT_TCGEN05) {
+    if (p.variant == FA_B200_VARIANT_TCGEN05 || p.variant == FA_B200_VARIANT_TCGEN05_2PASS) {
         if (!tc) { set_error("tcgen05 kernels do not cover this call: %s", why); return FA_EUNSUPPORTED; }
-        *variant = FA_B200_VARIANT_TCGEN05;
+        *variant = p.variant;
         return FA_OK;
     }
     if (p.variant == FA_B200_VARIANT_AUTO && tc) { *variant = FA_B200_VARIANT_TCGEN05; return FA_OK; }
@@ -170,7 +174,7 @@ int fa_b200_fwd(const fa_b200_params* p) {
     if ((rc = choose_variant(*p, false, &variant))) return rc;
     GuardDevice g(p->device);
     if (!g.ok) { set_error("cudaSetDevice(%d) failed", p->device); return FA_ECUDA; }
-    return variant == FA_B200_VARIANT_TCGEN05 ? sm100_fwd(*p) : simt_fwd(*p);
+    return variant != FA_B200_VARIANT_SIMT ? sm100_fwd(*p) : simt_fwd(*p);
 }
 
 size_t fa_b200_bwd_workspace_bytes(const fa_b200_params* p) {
@@ -182,7 +186,8 @@ size_t fa_b200_bwd_workspace_bytes(const fa_b200_params* p) {
     // answer does not depend on pointer alignment (pointers may be null here).
     const char* why = "";
     q.variant = FA_B200_VARIANT_AUTO;
-    if (sm100_supports(q, true, &why)) variant = FA_B200_VARIANT_TCGEN05;
+    if (p->variant != FA_B200_VARIANT_SIMT && sm100_supports(q, true, &why))
+        variant = (p->variant == FA_B200_VARIANT_TCGEN05_2PASS) ? FA_B200_VARIANT_TCGEN05_2PASS : FA_B200_VARIANT_TCGEN05;
     return bwd_workspace_layout(*p, variant).total;
 }
 
@@ -217,7 +222,7 @@ int fa_b200_bwd(const fa_b200_params* p) {
             }
         return FA_OK;
     }
-    return variant == FA_B200_VARIANT_TCGEN05 ? sm100_bwd(*p, ws) : simt_bwd(*p, ws);
+    return variant != FA_B200_VARIANT_SIMT ? sm100_bwd(*p, ws) : simt_bwd(*p, ws);
 }
 
 // ---------------------------------------------------------------------------
@@ -262,6 +267,8 @@ int fa_b200_bwd_static(const fa_b200_params* p) {
     if (p->Nq == 0) { set_error("fa_b200_bwd_static needs at least one query row"); return FA_EINVAL; }
     int variant;
     if ((rc = choose_variant(*p, true, &variant))) return rc;
+    // the built-in array is sized for the per-row vectors only: tensor-core calls take the two-pass backward
+    if (variant == FA_B200_VARIANT_TCGEN05) variant = FA_B200_VARIANT_TCGEN05_2PASS;
     BwdWorkspace ws = bwd_workspace_layout(*p, variant);
     if (ws.total > kStaticScratchBytes) {
         set_error("fa_b200_bwd_static: this problem needs %zu bytes of scratch, the built-in array holds %zu "
@@ -278,7 +285,7 @@ int fa_b200_bwd_static(const fa_b200_params* p) {
     q.workspace_bytes = kStaticScratchBytes;
     // Nothing in the scratch has to start at zero: the preprocess launch writes
     // every delta / lse entry (padding included) before the main kernels read them.
-    return variant == FA_B200_VARIANT_TCGEN05 ? sm100_bwd(q, ws) : simt_bwd(q, ws);
+    return variant != FA_B200_VARIANT_SIMT ? sm100_bwd(q, ws) : simt_bwd(q, ws);
 }
 
 // Static tile table.  Tensor-core rows hold the tile shapes the sm_100a

@@ -91,6 +91,13 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ---- global reductions ---------------------------------------------------------
+// Four fp32 additions to 16 consecutive bytes of global memory in one request (no return value).
+__device__ __forceinline__ void red_add_v4_f32(float* gptr, float x, float y, float z, float w) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(gptr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+
 // ---- TMA ----------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

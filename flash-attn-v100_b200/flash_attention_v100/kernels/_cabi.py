@@ -15,8 +15,9 @@ _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG_DIR, "lib", "libfa_b200.so")
 
 FA_B200_F16, FA_B200_BF16, FA_B200_F32 = 0, 1, 2
-VARIANT_AUTO, VARIANT_SIMT, VARIANT_TCGEN05 = 0, 1, 2
-VARIANT_NAMES = {VARIANT_AUTO: "auto", VARIANT_SIMT: "simt", VARIANT_TCGEN05: "tcgen05"}
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_TCGEN05, VARIANT_TCGEN05_2PASS = 0, 1, 2, 3
+VARIANT_NAMES = {VARIANT_AUTO: "auto", VARIANT_SIMT: "simt", VARIANT_TCGEN05: "tcgen05",
+                 VARIANT_TCGEN05_2PASS: "tcgen05_2pass"}
 
 FA_OK, FA_EINVAL, FA_EUNSUPPORTED, FA_EALIGN, FA_EWORKSPACE, FA_ECUDA, FA_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 

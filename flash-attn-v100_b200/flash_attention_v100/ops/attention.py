@@ -50,7 +50,8 @@ _variant_override = threading.local()
 @contextlib.contextmanager
 def kernel_variant(name: str):
     """Force a kernel family ('auto', 'simt', 'tcgen05') inside the block."""
-    table = {"auto": _cabi.VARIANT_AUTO, "simt": _cabi.VARIANT_SIMT, "tcgen05": _cabi.VARIANT_TCGEN05}
+    table = {"auto": _cabi.VARIANT_AUTO, "simt": _cabi.VARIANT_SIMT, "tcgen05": _cabi.VARIANT_TCGEN05,
+             "tcgen05_2pass": _cabi.VARIANT_TCGEN05_2PASS}
     old = getattr(_variant_override, "value", _cabi.VARIANT_AUTO)
     _variant_override.value = table[name]
     try:
@@ -115,29 +116,44 @@ def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset) -> _ca
     return p
 
 
-def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0):
+def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None):
     """o, lse <- fa_b200_fwd.  Counterpart of flash_attention_forward_triton_enhanced
-    (kernels/forward_kernel.py:246-387); returns (o, lse)."""
-    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-    lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
+    (kernels/forward_kernel.py:246-387); returns (o, lse).  `out=(o, lse)` writes into
+    caller-owned buffers (o like q, lse (B, H, Nq) fp32 contiguous) instead of allocating."""
+    if out is not None:
+        o, lse = out
+    else:
+        o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
     p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset)
     rc = _cabi.load().fa_b200_fwd(ctypes.byref(p))
     _cabi.raise_for_status(rc, "fa_b200_fwd")
     return o, lse
 
 
-def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, offset=0):
+def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None,
+                    workspace=None):
     """dq, dk, dv <- fa_b200_bwd.  Counterpart of
-    flash_attention_backward_triton_enhanced (kernels/backward_kernel.py:208-318)."""
+    flash_attention_backward_triton_enhanced (kernels/backward_kernel.py:208-318).
+    `out=(dq, dk, dv)` and `workspace` (uint8, at least fa_b200_bwd_workspace_bytes)
+    use caller-owned buffers instead of allocating."""
     d_o = _last_dim_contiguous(d_o)
-    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
-    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    if out is not None:
+        dq, dk, dv = out
+    else:
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
     p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset)
     p.d_o, p.dq, p.dk, p.dv = _tensor4(d_o), _tensor4(dq), _tensor4(dk), _tensor4(dv)
     lib = _cabi.load()
     nbytes = int(lib.fa_b200_bwd_workspace_bytes(ctypes.byref(p)))
-    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    if workspace is None:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    else:
+        ws = workspace
+        if ws.numel() < nbytes:
+            raise ValueError(f"workspace holds {ws.numel()} bytes, the call needs {nbytes}")
     p.workspace, p.workspace_bytes = ws.data_ptr(), nbytes
     rc = lib.fa_b200_bwd(ctypes.byref(p))
     _cabi.raise_for_status(rc, "fa_b200_bwd")

@@ -116,3 +116,23 @@ TOLERANCE_TARGET = {torch.float16: 2e-3, torch.bfloat16: 2e-3, torch.float32: 1e
 
 def tolerance(dtype: torch.dtype, variant: str = "auto", head_dim: int = 128) -> float:
     return TOLERANCE[dtype]
+
+
+def dq_is_bit_reproducible(variant: str, dtype: torch.dtype, head_dim: int, dropout_p: float = 0.0) -> bool:
+    """Whether two backward calls on the same inputs return the same dQ bit for bit.
+    dK, dV, O and LSE always do.  The one-kernel tensor-core backward sums dQ
+    tiles with unordered fp32 additions; it serves fp16/bf16 with D = 64
+    unless the two-pass variant is asked for."""
+    if variant not in ("auto", "tcgen05"):
+        return True
+    return not (dtype in (torch.float16, torch.bfloat16) and head_dim == 64)
+
+
+def assert_same_dq(a: torch.Tensor, b: torch.Tensor, exact: bool, what: str = "dQ") -> None:
+    """Bitwise when `exact`; otherwise equal up to the reordering of fp32 sums
+    before the final rounding (a few last-place flips of the 16-bit result)."""
+    if exact:
+        assert torch.equal(a, b), f"{what} differs bitwise"
+    else:
+        err = rel_l2(a, b)
+        assert err <= 1e-3, f"{what}: rel-L2 {err:.2e} between two summation orders"

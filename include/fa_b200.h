@@ -59,7 +59,15 @@ typedef enum fa_b200_status {
 typedef enum fa_b200_variant {
     FA_B200_VARIANT_AUTO    = 0,
     FA_B200_VARIANT_SIMT    = 1,  /* CUDA-core tiles: any D <= 128, all dtypes, fp32 exact */
-    FA_B200_VARIANT_TCGEN05 = 2   /* TMA + tcgen05/TMEM: fp16/bf16, D in {64, 128}         */
+    FA_B200_VARIANT_TCGEN05 = 2,  /* TMA + tcgen05/TMEM: fp16/bf16, D in {64, 128}         */
+    FA_B200_VARIANT_TCGEN05_2PASS = 3
+                                  /* the same family with the two-pass backward: one kernel
+                                     for dK, dV and one for dQ, every output owned by one CTA,
+                                     so gradients are bit-reproducible.  TCGEN05 itself uses
+                                     one kernel that sums dQ tiles into an fp32 buffer with
+                                     unordered global additions (as the reference does,
+                                     kernels/backward_kernel.py:179-194) where that is
+                                     faster: D = 64.  Forward: identical.                   */
 } fa_b200_variant;
 
 /* One (B, N, H, D) tensor: base pointer and element strides (D stride is 1). */

@@ -12,6 +12,7 @@ import torch.multiprocessing as mp
 
 import flash_attention_v100 as fa
 from flash_attention_v100.interface import FlashAttentionV100Manager, plan_shards, _slice
+from flash_attention_v100.testing import dq_is_bit_reproducible, assert_same_dq, rel_l2
 
 pytestmark = pytest.mark.gpu
 
@@ -41,7 +42,8 @@ def test_single_process_sharding_equals_single_gpu(B, H):
         o2.backward(gc.to(dev))
     torch.cuda.synchronize()
     assert o2.device == dev and torch.equal(o1, o2) and torch.equal(lse1, lse2)
-    assert torch.equal(q1.grad, q2.grad) and torch.equal(k1.grad, k2.grad) and torch.equal(v1.grad, v2.grad)
+    assert torch.equal(k1.grad, k2.grad) and torch.equal(v1.grad, v2.grad)
+    assert_same_dq(q1.grad, q2.grad, dq_is_bit_reproducible("auto", torch.bfloat16, 128))
 
 
 def _free_port():
@@ -73,7 +75,8 @@ def _rank_main(rank, world, port, ret):
             q1, k1, v1 = (t.to(dev).requires_grad_(True) for t in (qc, kc, vc))
             o1 = fa.flash_attention_v100(q1, k1, v1, causal=True, enable_multi_gpu=False)
             o1.backward(gc.to(dev))
-            same = all(torch.equal(a, b) for a, b in zip(outs, (o1.detach(), q1.grad, k1.grad, v1.grad)))
+            same = all(torch.equal(outs[i], x) for i, x in ((0, o1.detach()), (2, k1.grad), (3, v1.grad)))
+            same = same and rel_l2(outs[1], q1.grad) <= 1e-3     # dQ: unordered fp32 sums, then rounding
             ret[0] = "ok" if same else "mismatch"
         torch.cuda.synchronize()
     except Exception as e:   # noqa: BLE001
