@@ -655,38 +655,35 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (threadIdx.x == 0 && *abort_flag && a.status) atomicExch(a.status, 2 + MODE);
 }
 
-// negated delta and negated scaled lse (the main kernels add them), one warp per (b, h, padded query row)
-template <typename T>
+// negated delta and negated scaled lse (the main kernels add them).  D / 8 lanes share one
+// (b, h, padded query row), 16 bytes of O and dO each, so a warp covers 256 / D rows.
+template <typename T, int D>
 __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
-                      float* __restrict__ lse2, float* __restrict__ delta, int B, int Nq, int H, int D, int nq_pad,
+                      float* __restrict__ lse2, float* __restrict__ delta, int B, int Nq, int H, int nq_pad,
                       int64_t o_sb, int64_t o_sn, int64_t o_sh, int64_t g_sb, int64_t g_sn, int64_t g_sh) {
-    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (row >= (int64_t)B * H * nq_pad) return;
-    const int i = (int)(row % nq_pad);
-    const int64_t bh = row / nq_pad;
+    constexpr int LPR = D / 8;                 // lanes per row
+    constexpr int RPW = 32 / LPR;              // rows per warp
+    const int lane = threadIdx.x & 31, sub = lane % LPR;
+    const int64_t row = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + lane / LPR;
+    const bool live = row < (int64_t)B * H * nq_pad;
+    const int i = live ? (int)(row % nq_pad) : 0;
+    const int64_t bh = live ? row / nq_pad : 0;
     const int h = (int)(bh % H), b = (int)(bh / H);
-    if (i >= Nq) {
-        if (lane == 0) { lse2[row] = -INFINITY; delta[row] = 0.f; }
-        return;
-    }
-    const T* po = o + b * o_sb + i * o_sn + h * o_sh;
-    const T* pg = d_o + b * g_sb + i * g_sn + h * g_sh;
     float s = 0.f;
-    if (lane * 8 < D) {        // 16-byte vectors: 8 elements per lane
-        const uint4 vo = *reinterpret_cast<const uint4*>(po + lane * 8);
-        const uint4 vg = *reinterpret_cast<const uint4*>(pg + lane * 8);
+    if (live && i < Nq) {
+        const uint4 vo = *reinterpret_cast<const uint4*>(o + b * o_sb + i * o_sn + h * o_sh + sub * 8);
+        const uint4 vg = *reinterpret_cast<const uint4*>(d_o + b * g_sb + i * g_sn + h * g_sh + sub * 8);
         const T* eo = reinterpret_cast<const T*>(&vo);
         const T* eg = reinterpret_cast<const T*>(&vg);
 #pragma unroll
         for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(eo[e]), to_f32<T>(eg[e]), s);
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) {
-        delta[row] = -s;
-        lse2[row] = -lse[bh * Nq + i] * kLog2e;
+    for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (live && sub == 0) {
+        if (i < Nq) { delta[row] = -s; lse2[row] = -lse[bh * Nq + i] * kLog2e; }
+        else        { delta[row] = 0.f; lse2[row] = -INFINITY; }
     }
 }
 
@@ -732,8 +729,9 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     if (phases & 1) {
         if (fused) FA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, ws.dq_bytes, st));
         const int64_t rows = (int64_t)p.B * p.H * nq_pad;
-        bwd_preprocess_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
-            (const T*)p.o.ptr, (const T*)p.d_o.ptr, p.lse, lse2, delta, p.B, p.Nq, p.H, D, nq_pad,
+        constexpr int kRowsPerBlock = 8 * (256 / D);
+        bwd_preprocess_kernel<T, D><<<(unsigned)((rows + kRowsPerBlock - 1) / kRowsPerBlock), 256, 0, st>>>(
+            (const T*)p.o.ptr, (const T*)p.d_o.ptr, p.lse, lse2, delta, p.B, p.Nq, p.H, nq_pad,
             p.o.stride_b, p.o.stride_n, p.o.stride_h, p.d_o.stride_b, p.d_o.stride_n, p.d_o.stride_h);
         FA_CUDA_CHECK(cudaGetLastError());
     }

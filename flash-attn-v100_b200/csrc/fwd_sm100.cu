@@ -19,7 +19,9 @@
 //                   S_t = Q_t K_j^T          (SS MMA, both operands K-major)
 //                   O_t += P_t V_j           (TS MMA: P_t from TMEM, V_j MN-major)
 //               issue order  S0(0) S1(0) | PV0(j) S0(j+1) PV1(j) S1(j+1) ...
-//               so that the softmax of one tile overlaps the MMAs of the other
+//               so that the softmax of one tile overlaps the MMAs of the other; each PV
+//               is issued in two 64-key halves, the first as soon as that half of P_t
+//               is in TMEM (the threads are still computing the second)
 //   warps 0-3   softmax + epilogue of tile 0, one thread per query row (TMEM lane)
 //   warps 4-7   softmax + epilogue of tile 1
 //   warps 10-11 idle (they complete the third warpgroup for setmaxnreg)
@@ -58,6 +60,14 @@ constexpr float kRescaleThreshold = 8.0f;   // log2 units
 // unit: in kPolyCount of every kPolyPeriod groups of four, two.  Measured on B200 (B4 N4096 H32 D128
 // causal forward): 0 % 0.559 ms, 25 % 0.544 ms, 50 % 0.563 ms.
 constexpr int kPolyPeriod = 2, kPolyCount = 1;
+// The first 64 keys of P are handed to the MMA warp after this many of the second half's 64
+// exponentials (a multiple of 4), when their tcgen05.st has had time to complete.
+constexpr int kHalfSignalAt = 16;
+// Register split after setmaxnreg.  The pool is what the CTA was launched with, 168 registers for
+// each of its 384 threads, not the whole file: a split that asks for more makes
+// setmaxnreg.inc wait for ever.
+constexpr int kRegsSoftmax = 224, kRegsOther = 56;
+static_assert(256 * kRegsSoftmax + 128 * kRegsOther <= 168 * kThreads, "register split exceeds the CTA's allocation");
 
 template <int D>
 struct FwdCfg {
@@ -74,7 +84,8 @@ struct FwdCfg {
     static constexpr int kSFull = kVEmpty + kStages;       // [2]
     static constexpr int kPFull = kSFull + 2;              // [2] one arrival per warp of the warpgroup
     static constexpr int kODone = kPFull + 2;              // [2]
-    static constexpr int kNumBars = kODone + 2;
+    static constexpr int kPHalf = kODone + 2;              // [2] first 64 keys of P_t stored (one arrival per warp)
+    static constexpr int kNumBars = kPHalf + 2;
     static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + kNumBars * 8 + 64 + 1024;
 };
 
@@ -147,7 +158,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kNumBars; ++i) {
-            const bool wg_bar = (i >= Cfg::kPFull && i < Cfg::kPFull + 2);
+            const bool wg_bar = (i >= Cfg::kPFull && i < Cfg::kPFull + 2) || (i >= Cfg::kPHalf && i < Cfg::kPHalf + 2);
             mbar_init(&bars[i], wg_bar ? 4u : 1u);
         }
         *abort_flag = 0u;
@@ -168,7 +179,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t tmem = *tmem_slot;
 
     if (warp >= 8) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
       if (warp == 9) {
         // ------------------------------------------------------------ TMA producer
         if (elect_one()) {
@@ -258,13 +269,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     mma_ss_f16(d, a0 + off, b0 + off, idesc_s, kk > 0);
                 }
             };
-            auto issue_pv = [&](int t, int vs, bool acc) {
+            // one 64-key half (hf = 0, 1) of O_t += P_t V_j
+            auto issue_pv = [&](int t, int vs, bool acc, int hf) {
                 const uint64_t b0 = dV + (uint64_t)((vs * TILE) >> 4);
                 const uint32_t d = tmem + 256u + (uint32_t)t * 128u, a0 = tmem + (uint32_t)t * 128u;
 #pragma unroll
-                for (int kk = 0; kk < kBlockN / 16; ++kk)
+                for (int k4 = 0; k4 < kBlockN / 32; ++k4) {
+                    const int kk = hf * (kBlockN / 32) + k4;
                     mma_ts_f16(d, a0 + (uint32_t)kk * 8u, b0 + (uint64_t)((kk * 2048) >> 4), idesc_pv,
                                (acc || kk > 0) ? 1u : 0u);
+                }
             };
 
             int kvc = 0;                    // K/V blocks consumed so far
@@ -306,11 +320,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                         for (int t = 0; t < 2; ++t) {
                             if (j < nblk[t]) {
+                                // the first 64 keys of P_t arrive while the second 64 are still computed
+                                ok = mbar_wait(&bars[Cfg::kPHalf + t], (uint32_t)p_waits[t] & 1u, abort_flag);
+                                if (!ok) break;
+                                tc_fence_after_sync();
+                                issue_pv(t, vs, j > 0, 0);
                                 ok = mbar_wait(&bars[Cfg::kPFull + t], (uint32_t)p_waits[t] & 1u, abort_flag);
                                 if (!ok) break;
                                 ++p_waits[t];
                                 tc_fence_after_sync();
-                                issue_pv(t, vs, j > 0);
+                                issue_pv(t, vs, j > 0, 1);
                                 if (j == nblk[t] - 1) mma_commit(&bars[Cfg::kODone + t]);
                             }
                             if (t == 1) mma_commit(&bars[Cfg::kVEmpty + vs]);
@@ -335,7 +354,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         __syncwarp();
       }   // warps 10-11 idle: they complete the third warpgroup
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         // ------------------------------------------------------------ softmax + epilogue
         using T16 = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
         const int t = warp >> 2;
@@ -420,6 +439,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         for (int cc = 0; cc < 64; cc += 4) {
                             const int c = c0 * 64 + cc;
                             float x0, x1, x2, x3, p0, p1, p2, p3;
+                            if (!DROP && c0 == 1 && cc == kHalfSignalAt) {
+                                // the first half's store has had these groups' time to complete
+                                tmem_wait_st();
+                                tc_fence_before_sync();
+                                mbar_arrive_warp(&bars[Cfg::kPHalf + t]);
+                            }
                             f2_unpack(f2_fma(f2_pack(SF(c), SF(c + 1)), c2, nm2), x0, x1);
                             f2_unpack(f2_fma(f2_pack(SF(c + 2), SF(c + 3)), c2, nm2), x2, x3);
                             p0 = ex2(x0); p1 = ex2(x1);
@@ -461,6 +486,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #undef SSET
                     tmem_wait_st();
                     tc_fence_before_sync();
+                    if (DROP) mbar_arrive_warp(&bars[Cfg::kPHalf + t]);
                     mbar_arrive_warp(&bars[Cfg::kPFull + t]);
                 }
                 if (!ok) break;
