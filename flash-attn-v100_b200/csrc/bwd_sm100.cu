@@ -86,7 +86,8 @@ struct BwdCfg {
     static constexpr int kEpi = kMask + 1;                       // one arrival per elementwise warp
     static constexpr int kDqFull = kEpi + 1;                     // fused kernel: dQ tile of the step complete
     static constexpr int kDqRead = kDqFull + 1;                  // ... and read out (one arrival per warp)
-    static constexpr int kNumBars = kDqRead + 1;
+    static constexpr int kPHalf = kDqRead + 1;                   // key-stationary: first half of each P^T slice stored
+    static constexpr int kNumBars = kPHalf + 1;
     static constexpr int kDsBytes = 128 * 128 * 2;               // fused kernel: dS^T tile for the dQ MMA
     // bytes used from the 1024-aligned base: tiles, ring, [dS], barriers, TMEM slot + flag, [masks]
     __host__ __device__ static constexpr int used_bytes(bool fused, bool drop) {
@@ -190,7 +191,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kNumBars; ++i) {
             const bool wide = (i == Cfg::kPReady || i == Cfg::kDsReady || i == Cfg::kMask || i == Cfg::kEpi ||
-                               i == Cfg::kDqRead);
+                               i == Cfg::kDqRead || i == Cfg::kPHalf);
             mbar_init(&bars[i], wide ? 4u * NWG : 1u);    // one arrival per elementwise warp
         }
         *abort_flag = 0u;
@@ -296,6 +297,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                                (acc || kk > 0) ? 1u : 0u);
                 }
             };
+            // the same product restricted to the first (hf = 0) or second 16 columns of every
+            // warpgroup's slice: K-steps kk = hf, hf + 2, hf + 4, hf + 6
+            auto issue_acc_half = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t strm_u, bool acc, int hf) {
+                static_assert(CPT == 32, "one K-step of 16 per half slice");
+                const uint64_t b0 = dmn_major + (uint64_t)(strm_u >> 4);
+#pragma unroll
+                for (int g = 0; g < kTile / 32; ++g) {
+                    const int kk = 2 * g + hf;
+                    const uint32_t a_col = (uint32_t)g * CPT + (uint32_t)hf * 8u;
+                    mma_ts_f16(d_tmem, a_tmem + a_col, b0 + (uint64_t)((kk * 2048) >> 4), idesc_acc,
+                               (acc || hf > 0 || g > 0) ? 1u : 0u);
+                }
+            };
 
             // fused kernel: the step's dQ tile (fresh accumulation) from two shared-memory operands
             constexpr uint32_t idesc_dq = make_idesc_f16(BF16, BF16, kTile, D, true, true);
@@ -324,10 +338,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 const bool more = it + 1 < n_iter;
                 if (more) { ok = mbar_wait(&bars[Cfg::kUWFull + ns], nph, abort_flag); if (!ok) break; }
                 if (KS) {
+                    ok = mbar_wait(&bars[Cfg::kPHalf], (uint32_t)it & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_acc_half(tAcc2, tT1, cur_u + TILE, it > 0, 0);         // dV += (P o Z)^T dO, first halves
                     ok = mbar_wait(&bars[Cfg::kPReady], (uint32_t)it & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_acc(tAcc2, tT1, cur_u + TILE, it > 0);                 // dV += (P o Z)^T dO
+                    issue_acc_half(tAcc2, tT1, cur_u + TILE, it > 0, 1);
                     if (more) { issue_t(tT1, sX_u, nxt_u); mma_commit(&bars[Cfg::kT1Full]); }
                 } else if (more) {
                     // dQ needs no second accumulator, so S is double-buffered in its columns: S(it+1)
@@ -471,24 +489,50 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tmem_wait_ld();
             const uint64_t sc2 = f2_pack(a.scale_log2, a.scale_log2);
             if (KS) {
-                // P = 2^(S*c - lse): the staged vector holds -lse*log2(e), two columns per 64-bit word
+                // P = 2^(S*c - lse): the staged vector holds -lse*log2(e), two columns per 64-bit word.
+                // Two halves of CPT / 2 columns: the first is packed, stored to TMEM and handed to the
+                // MMA warp (dV can start on it) while the second is computed.
+                static_assert(CPT == 32, "the half hand-off is written for 32 columns per thread");
                 const ulonglong2* l2 = reinterpret_cast<const ulonglong2*>(lse_s + cb);
+                const bool diag = a.causal && strm_tile == tile;   // key row > query column is hidden
 #pragma unroll
-                for (int c4 = 0; c4 < CPT / 4; ++c4) {
-                    const ulonglong2 L = l2[c4];
-                    float x0, x1, x2, x3;
-                    f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 0), PF(c4 * 4 + 1)), sc2, L.x), x0, x1);
-                    f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 2), PF(c4 * 4 + 3)), sc2, L.y), x2, x3);
-                    PSET(c4 * 4 + 0, ex2(x0));
-                    PSET(c4 * 4 + 1, ex2(x1));
-                    PSET(c4 * 4 + 2, ex2(x2));
-                    PSET(c4 * 4 + 3, ex2(x3));
-                }
-                if (a.causal && strm_tile == tile) {       // diagonal tile: key row > query column is hidden
+                for (int hf = 0; hf < 2; ++hf) {
 #pragma unroll
-                    for (int c = 0; c < CPT; ++c)
-                        if (row_g > col_g0 + c) PSET(c, 0.f);
+                    for (int c4 = hf * (CPT / 8); c4 < (hf + 1) * (CPT / 8); ++c4) {
+                        const ulonglong2 L = l2[c4];
+                        float x0, x1, x2, x3;
+                        f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 0), PF(c4 * 4 + 1)), sc2, L.x), x0, x1);
+                        f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 2), PF(c4 * 4 + 3)), sc2, L.y), x2, x3);
+                        PSET(c4 * 4 + 0, ex2(x0));
+                        PSET(c4 * 4 + 1, ex2(x1));
+                        PSET(c4 * 4 + 2, ex2(x2));
+                        PSET(c4 * 4 + 3, ex2(x3));
+                    }
+                    if (diag) {
+#pragma unroll
+                        for (int c = hf * (CPT / 2); c < (hf + 1) * (CPT / 2); ++c)
+                            if (row_g > col_g0 + c) PSET(c, 0.f);
+                    }
+                    uint32_t pk[CPT / 4];
+#pragma unroll
+                    for (int e = 0; e < CPT / 4; ++e) {
+                        const int c = hf * (CPT / 2) + 2 * e;
+                        float x0 = PF(c), x1 = PF(c + 1);
+                        if (drop) {
+                            if (!((kb[c >> 5] >> (c & 31)) & 1u)) x0 = 0.f;
+                            if (!((kb[(c + 1) >> 5] >> ((c + 1) & 31)) & 1u)) x1 = 0.f;
+                        }
+                        pk[e] = pack2<BF16>(x0, x1);
+                    }
+                    if (hf == 1) {
+                        // the first half's store was issued a half-phase ago
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        mbar_arrive_warp(&bars[Cfg::kPHalf]);
+                    }
+                    tmem_st_32x8(tT1 + lane_off + cb + hf * (CPT / 4), pk);
                 }
+                tmem_wait_st();
             } else {
                 const uint64_t neg2 = f2_pack(my_nlse2, my_nlse2);
 #pragma unroll
@@ -506,23 +550,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         if (col >= a.Nk || (diag && col > row_g)) PSET(c, 0.f);
                     }
                 }
-            }
-            if (KS) {
-                uint32_t pk[CPT / 2];
-                if (drop) {
-#pragma unroll
-                    for (int c = 0; c < CPT / 2; ++c) {
-                        const float x0 = ((kb[(2 * c) >> 5] >> ((2 * c) & 31)) & 1u) ? PF(2 * c) : 0.f;
-                        const float x1 = ((kb[(2 * c + 1) >> 5] >> ((2 * c + 1) & 31)) & 1u) ? PF(2 * c + 1) : 0.f;
-                        pk[c] = pack2<BF16>(x0, x1);
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < CPT / 2; ++c) pk[c] = pack2<BF16>(PF(2 * c), PF(2 * c + 1));
-                }
-                if constexpr (CPT == 64) tmem_st_32x32(tT1 + lane_off + cb, pk);
-                else                     tmem_st_32x16(tT1 + lane_off + cb, pk);
-                tmem_wait_st();
             }
             tc_fence_before_sync();
             mbar_arrive_warp(&bars[Cfg::kPReady]);
