@@ -87,7 +87,8 @@ struct BwdCfg {
     static constexpr int kDqFull = kEpi + 1;                     // fused kernel: dQ tile of the step complete
     static constexpr int kDqRead = kDqFull + 1;                  // ... and read out (one arrival per warp)
     static constexpr int kPHalf = kDqRead + 1;                   // key-stationary: first half of each P^T slice stored
-    static constexpr int kNumBars = kPHalf + 1;
+    static constexpr int kDsHalf = kPHalf + 1;                   // first half of each dS slice stored
+    static constexpr int kNumBars = kDsHalf + 1;
     static constexpr int kDsBytes = 128 * 128 * 2;               // fused kernel: dS^T tile for the dQ MMA
     // bytes used from the 1024-aligned base: tiles, ring, [dS], barriers, TMEM slot + flag, [masks]
     __host__ __device__ static constexpr int used_bytes(bool fused, bool drop) {
@@ -191,7 +192,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kNumBars; ++i) {
             const bool wide = (i == Cfg::kPReady || i == Cfg::kDsReady || i == Cfg::kMask || i == Cfg::kEpi ||
-                               i == Cfg::kDqRead || i == Cfg::kPHalf);
+                               i == Cfg::kDqRead || i == Cfg::kPHalf || i == Cfg::kDsHalf);
             mbar_init(&bars[i], wide ? 4u * NWG : 1u);    // one arrival per elementwise warp
         }
         *abort_flag = 0u;
@@ -219,7 +220,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t tDq = kDqAliasesT2 ? tT2 : tmem + 448u;
 
     if (warp >= kMmaWarp) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
       if (warp == kTmaWarp) {
         // ---------------------------------------------------------------- TMA producer
         if (elect_one()) {
@@ -357,10 +358,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     // before the dS(it-1) hand-off, so this completion cannot lap a waiter
                     mma_commit(&bars[Cfg::kT1Full + ((it + 1) & 1)]);
                 }
+                ok = mbar_wait(&bars[Cfg::kDsHalf], (uint32_t)it & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_acc_half(tAcc1, tT2, cur_u, it > 0, 0);                    // dK += dS^T Q  /  dQ += dS K
                 ok = mbar_wait(&bars[Cfg::kDsReady], (uint32_t)it & 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after_sync();
-                issue_acc(tAcc1, tT2, cur_u, it > 0);                            // dK += dS^T Q  /  dQ += dS K
+                issue_acc_half(tAcc1, tT2, cur_u, it > 0, 1);
                 mma_commit(&bars[Cfg::kUWEmpty + s]);
                 if (FUSED) {
                     // dQ tile of this step = dS K_j: A is the dS^T tile the threads left in shared memory,
@@ -570,49 +575,57 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                 for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tT2 + lane_off + cb + q * 32, dr[q]);
                 tmem_wait_ld();
-                uint32_t pk[CPT / 2];
-                // dS = P o (dP o Z - delta); the staged vector holds -delta
+                // dS = P o (dP o Z - delta); the staged vector holds -delta.  Two halves, as in phase A:
+                // the first is stored and handed over while the second is computed.
                 const ulonglong2* d2 = reinterpret_cast<const ulonglong2*>(del_s + cb);
                 const uint64_t my_nd2 = f2_pack(my_ndelta, my_ndelta);
 #pragma unroll
-                for (int c4 = 0; c4 < CPT / 4; ++c4) {
-                    ulonglong2 nd;
-                    if (KS) nd = d2[c4];
-                    else { nd.x = my_nd2; nd.y = my_nd2; }
-                    const int c = c4 * 4;
-                    uint64_t dpa = f2_pack(__uint_as_float(dr[c >> 5][c & 31]), __uint_as_float(dr[c >> 5][(c + 1) & 31]));
-                    uint64_t dpb = f2_pack(__uint_as_float(dr[c >> 5][(c + 2) & 31]), __uint_as_float(dr[c >> 5][(c + 3) & 31]));
-                    uint64_t ta, tb;
-                    if (drop) {
-                        const uint32_t kw = kb[c >> 5] >> (c & 31);
-                        const uint64_t za = f2_pack((kw & 1u) ? a.inv_keep : 0.f, (kw & 2u) ? a.inv_keep : 0.f);
-                        const uint64_t zb = f2_pack((kw & 4u) ? a.inv_keep : 0.f, (kw & 8u) ? a.inv_keep : 0.f);
-                        ta = f2_fma(dpa, za, nd.x);
-                        tb = f2_fma(dpb, zb, nd.y);
-                    } else {
-                        ta = f2_add(dpa, nd.x);
-                        tb = f2_add(dpb, nd.y);
-                    }
-                    float d0, d1, d2v, d3;
-                    f2_unpack(f2_mul(f2_pack(PF(c), PF(c + 1)), ta), d0, d1);
-                    f2_unpack(f2_mul(f2_pack(PF(c + 2), PF(c + 3)), tb), d2v, d3);
-                    pk[c4 * 2 + 0] = pack2<BF16>(d0, d1);
-                    pk[c4 * 2 + 1] = pack2<BF16>(d2v, d3);
-                }
-                if constexpr (CPT == 64) tmem_st_32x32(tT2 + lane_off + cb, pk);
-                else                     tmem_st_32x16(tT2 + lane_off + cb, pk);
-                if (FUSED) {
-                    // the same dS^T values as a shared-memory tile [key row][query], 64-query boxes with
-                    // the 128-byte swizzle: the A operand (MN-major) of the dQ MMA.  The previous
-                    // step's dQ MMA has finished reading it: its completion was awaited in drain_dq.
+                for (int hf = 0; hf < 2; ++hf) {
+                    uint32_t pk[CPT / 4];
 #pragma unroll
-                    for (int v = 0; v < CPT / 8; ++v) {
-                        const int q0 = cb + v * 8;                                  // first of 8 queries
-                        uint8_t* dst = sDs + (q0 >> 6) * kBoxBytes + r * 128 + ((((q0 & 63) >> 3) ^ (r & 7)) << 4);
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+                    for (int c4 = hf * (CPT / 8); c4 < (hf + 1) * (CPT / 8); ++c4) {
+                        ulonglong2 nd;
+                        if (KS) nd = d2[c4];
+                        else { nd.x = my_nd2; nd.y = my_nd2; }
+                        const int c = c4 * 4;
+                        uint64_t dpa = f2_pack(__uint_as_float(dr[c >> 5][c & 31]), __uint_as_float(dr[c >> 5][(c + 1) & 31]));
+                        uint64_t dpb = f2_pack(__uint_as_float(dr[c >> 5][(c + 2) & 31]), __uint_as_float(dr[c >> 5][(c + 3) & 31]));
+                        uint64_t ta, tb;
+                        if (drop) {
+                            const uint32_t kw = kb[c >> 5] >> (c & 31);
+                            const uint64_t za = f2_pack((kw & 1u) ? a.inv_keep : 0.f, (kw & 2u) ? a.inv_keep : 0.f);
+                            const uint64_t zb = f2_pack((kw & 4u) ? a.inv_keep : 0.f, (kw & 8u) ? a.inv_keep : 0.f);
+                            ta = f2_fma(dpa, za, nd.x);
+                            tb = f2_fma(dpb, zb, nd.y);
+                        } else {
+                            ta = f2_add(dpa, nd.x);
+                            tb = f2_add(dpb, nd.y);
+                        }
+                        float d0, d1, d2v, d3;
+                        f2_unpack(f2_mul(f2_pack(PF(c), PF(c + 1)), ta), d0, d1);
+                        f2_unpack(f2_mul(f2_pack(PF(c + 2), PF(c + 3)), tb), d2v, d3);
+                        pk[(c4 - hf * (CPT / 8)) * 2 + 0] = pack2<BF16>(d0, d1);
+                        pk[(c4 - hf * (CPT / 8)) * 2 + 1] = pack2<BF16>(d2v, d3);
                     }
-                    fence_proxy_async_smem();
+                    if (hf == 1) {
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        mbar_arrive_warp(&bars[Cfg::kDsHalf]);
+                    }
+                    tmem_st_32x8(tT2 + lane_off + cb + hf * (CPT / 4), pk);
+                    if (FUSED) {
+                        // the same dS^T values as a shared-memory tile [key row][query], 64-query boxes with
+                        // the 128-byte swizzle: the A operand (MN-major) of the dQ MMA.  The previous
+                        // step's dQ MMA has finished reading it: its completion was awaited in drain_dq.
+#pragma unroll
+                        for (int v = 0; v < CPT / 16; ++v) {
+                            const int q0 = cb + hf * (CPT / 2) + v * 8;                 // first of 8 queries
+                            uint8_t* dst = sDs + (q0 >> 6) * kBoxBytes + r * 128 + ((((q0 & 63) >> 3) ^ (r & 7)) << 4);
+                            *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+                        }
+                    }
                 }
+                if (FUSED) fence_proxy_async_smem();
                 tmem_wait_st();
             }
 #undef PF

@@ -66,7 +66,7 @@ constexpr int kHalfSignalAt = 16;
 // Register split after setmaxnreg.  The pool is what the CTA was launched with, 168 registers for
 // each of its 384 threads, not the whole file: a split that asks for more makes
 // setmaxnreg.inc wait for ever.
-constexpr int kRegsSoftmax = 224, kRegsOther = 56;
+constexpr int kRegsSoftmax = 208, kRegsOther = 88;   // measured best of 224/56, 216/72, 208/88, 200/104
 static_assert(256 * kRegsSoftmax + 128 * kRegsOther <= 168 * kThreads, "register split exceeds the CTA's allocation");
 
 template <int D>
