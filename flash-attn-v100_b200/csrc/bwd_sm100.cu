@@ -183,8 +183,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     // each key tile's walk at a different query tile, so that the CTAs of one head, which run at
     // the same time, add to different dQ tiles (under a causal mask the walks are staggered already).
     const int rot = (FUSED && !a.causal && n_per_head > 0) ? tile % n_per_head : 0;
-    auto q_tile_of = [&](int it) {
-        int t = it % n_per_head + rot;
+    // qi = index of the step within its query head (each role keeps qi and the head count as
+    // running counters: a division per step and warp is a visible share of the issue slots)
+    auto q_tile_of = [&](int qi) {
+        int t = qi + rot;
         if (t >= n_per_head) t -= n_per_head;
         return it0 + t;
     };
@@ -234,6 +236,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     tma_load_4d(sY + bx * kBoxBytes, &map_y, &bars[Cfg::kXYFull], bx * 64, head_x, tile * kTile, b);
                 }
             }
+            int qi = 0, hg = 0;
             for (int it = 0; it < n_iter; ++it) {
                 const int s = it % ST;
                 const uint32_t ph = (uint32_t)(it / ST) & 1u;
@@ -241,7 +244,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 if (!ok) break;
                 uint8_t* stage = sRing + s * Cfg::kStageBytes;
                 int head_u, row_u;
-                if (KS) { head_u = head_x * group + it / n_per_head; row_u = q_tile_of(it) * kTile; }
+                if (KS) { head_u = head_x * group + hg; row_u = q_tile_of(qi) * kTile; }
                 else           { head_u = head_kv; row_u = it * kTile; }
                 mbar_expect_tx(&bars[Cfg::kUWFull + s], kStageTx);
 #pragma unroll
@@ -255,6 +258,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     bulk_load_1d(stage + 2 * TILE + 512, a.delta + off, 512, &bars[Cfg::kUWFull + s]);
                 }
                 ++issued;
+                if (++qi == n_per_head) { qi = 0; ++hg; }
             }
             if (!ok) {
                 // unwinding: let copies already issued land before shared memory is given up
@@ -414,7 +418,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
         // fused kernel: add the dQ tile of step `jt` (queries on the TMEM lanes, my D / NWG columns)
         // to the fp32 sums in global memory; the order of additions across CTAs is not fixed
-        auto drain_dq = [&](int jt) -> bool {
+        auto drain_dq = [&](int jt, int q_tile, int head_q) -> bool {
             constexpr int DQC = D / NWG;
             bool good = mbar_wait(&bars[Cfg::kDqFull], (uint32_t)jt & 1u, abort_flag);
             good = __all_sync(0xffffffffu, good);
@@ -426,8 +430,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tmem_wait_ld();
             tc_fence_before_sync();
             mbar_arrive_warp(&bars[Cfg::kDqRead]);
-            const int q_tile = q_tile_of(jt);
-            const int head_q = head_x * group + jt / n_per_head;
             float* dst = a.dq_acc + (((int64_t)b * a.H + head_q) * (a.nq_pad / kTile) + q_tile) * (int64_t)(kTile * D) +
                          ((int64_t)(wg * (DQC / 4)) * kTile + r) * 4;
 #pragma unroll
@@ -437,14 +439,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             return true;
         };
 
+        int qi = 0, hg = 0;                 // step within the query head, query heads done (key-stationary)
+        int prev_tile = 0, prev_head = 0;   // query tile and head of the previous step
         for (int it = 0; it < n_iter; ++it) {
             const int s = it % ST;
             const uint8_t* stage = sRing + s * Cfg::kStageBytes;
             const float* lse_s = reinterpret_cast<const float*>(stage + 2 * TILE);
             const float* del_s = lse_s + 128;
-            const int strm_tile = (KS) ? q_tile_of(it) : it;     // query tile (0) / key tile (1)
+            const int strm_tile = (KS) ? q_tile_of(qi) : it;     // query tile (0) / key tile (1)
             const int col_g0 = strm_tile * kTile + cb;                          // global index of my first column
-            const int head_q = (KS) ? head_x * group + it / n_per_head : head_x;
+            const int head_q = (KS) ? head_x * group + hg : head_x;
             const uint32_t bh = (uint32_t)(b * a.H + head_q);
 
             // ---- dropout keep bits of my CPT columns (bit c of kb[c / 32])
@@ -561,7 +565,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
             if (FUSED && it > 0) {
                 // dQ of the previous step: its MMAs ran while phase A above did
-                ok = drain_dq(it - 1);
+                ok = drain_dq(it - 1, prev_tile, prev_head);
                 if (!ok) break;
             }
 
@@ -632,9 +636,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #undef PSET
             tc_fence_before_sync();
             mbar_arrive_warp(&bars[Cfg::kDsReady]);
+            prev_tile = strm_tile; prev_head = head_q;
+            if (++qi == n_per_head) { qi = 0; ++hg; }
         }
 
-        if (FUSED && n_iter > 0 && ok) ok = drain_dq(n_iter - 1);
+        if (FUSED && n_iter > 0 && ok) ok = drain_dq(n_iter - 1, prev_tile, prev_head);
 
         // ---- epilogue: accumulators -> 16-bit -> swizzled staging -> TMA store
         if (n_iter > 0 && ok) ok = mbar_wait(&bars[Cfg::kAccDone], 0u, abort_flag);
