@@ -43,7 +43,10 @@
 //   warps 0-15       four elementwise warpgroups; a thread owns one TMEM lane (row)
 //                    and warpgroup g owns columns [32g, 32g+32) of T1/T2
 //   warp 16          MMA issuer; order  T1(0) T2(0) | ACC2(i) T1(i+1) ACC1(i) T2(i+1) ...
-//   warp 17          TMA producer (tiles, and the lse/delta rows in MODE 0)
+//   warp 17          TMA producer: U and W tiles into rings of their own (U is read again by the
+//                    step's last MMA, so it gets three stages where shared memory allows and its
+//                    next load overlaps a whole step; W gets two), and in the key-stationary
+//                    kernels the step's -lse / -delta rows into a two-slot ring
 //   warps 18-19      idle (complete the fifth warpgroup for setmaxnreg)
 //
 // TMEM columns: T1 [0,128)  T2 [128,256)  ACC1 [256,256+D)  ACC2 [384,384+D).
@@ -67,17 +70,27 @@ constexpr int kExtraThreads = 128;       // MMA warp + TMA warp + two idle warps
                                          // four warps, so dropping the idle pair would free none
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int D>
+// Shared-memory plan of one kernel instance.  The streamed tiles U and W have rings of their own:
+// U (Q_i in the key-stationary kernels, K_j in MODE 1) is read by the first MMA of its step and again
+// by the last one, a step and a half later, so two stages leave the TMA load of the next tile no
+// time at all (it can only start when the last reader has finished and is needed at once); W is
+// done within one step.  D = 128 has room for three U stages and two W stages, except that the
+// key-stationary dropout instance needs 4 KB for its masks and stays at two and two.
+template <int D, int MODE, bool DROP>
 struct BwdCfg {
     static constexpr int kNBox = D / 64;
     static constexpr int kTileBytes = kNBox * kBoxBytes;
-    static constexpr int kStages = 2;
-    static constexpr int kStageBytes = 2 * kTileBytes + 1024;   // U, W, lse[128], delta[128]
+    static constexpr bool kFused = (MODE == 2);
+    static constexpr bool kMasks = DROP && MODE != 1;            // masks are built in shared memory when keys are rows
+    static constexpr int kUStages = (D == 64) ? 4 : (kMasks ? 2 : 3);
+    static constexpr int kWStages = (D == 64) ? 3 : 2;
     static constexpr int kMaskBytes = 2 * 128 * 8 * 2;          // two buffers of 128 x 8 uint16 keep masks
     static constexpr int kXYFull = 0;
-    static constexpr int kUWFull = 1;                            // [kStages]
-    static constexpr int kUWEmpty = kUWFull + kStages;           // [kStages]
-    static constexpr int kT1Full = kUWEmpty + kStages;           // [2]: one per S buffer (MODE 0 uses the first)
+    static constexpr int kUFull = 1;                             // [kUStages]
+    static constexpr int kUEmpty = kUFull + kUStages;            // [kUStages]
+    static constexpr int kWFull = kUEmpty + kUStages;            // [kWStages]
+    static constexpr int kWEmpty = kWFull + kWStages;            // [kWStages]
+    static constexpr int kT1Full = kWEmpty + kWStages;           // [2]: one per S buffer (MODE 0 uses the first)
     static constexpr int kT2Full = kT1Full + 2;
     static constexpr int kPReady = kT2Full + 1;                  // one arrival per elementwise warp
     static constexpr int kDsReady = kPReady + 1;                 // one arrival per elementwise warp
@@ -88,18 +101,18 @@ struct BwdCfg {
     static constexpr int kDqRead = kDqFull + 1;                  // ... and read out (one arrival per warp)
     static constexpr int kPHalf = kDqRead + 1;                   // key-stationary: first half of each P^T slice stored
     static constexpr int kDsHalf = kPHalf + 1;                   // first half of each dS slice stored
-    static constexpr int kNumBars = kDsHalf + 1;
+    static constexpr int kVFull = kDsHalf + 1;                   // [2] key-stationary: -lse, -delta rows of a step landed
+    static constexpr int kVEmpty = kVFull + 2;                   // [2] ... and read (one arrival per elementwise warp)
+    static constexpr int kNumBars = kVEmpty + 2;
+    static constexpr int kVecBytes = (MODE != 1) ? 2 * 1024 : 0; // two slots of lse[128] | delta[128]
     static constexpr int kDsBytes = 128 * 128 * 2;               // fused kernel: dS^T tile for the dQ MMA
-    // bytes used from the 1024-aligned base: tiles, ring, [dS], barriers, TMEM slot + flag, [masks]
-    __host__ __device__ static constexpr int used_bytes(bool fused, bool drop) {
-        return 2 * kTileBytes + kStages * kStageBytes + (fused ? kDsBytes : 0) + (drop ? kMaskBytes : 0) +
-               kNumBars * 8 + 64;
-    }
+    // bytes used from the 1024-aligned base: X, Y, U ring, W ring, [dS], [vectors], barriers, TMEM slot + flag, [masks]
+    static constexpr int kUsedBytes = (2 + kUStages + kWStages) * kTileBytes + (kFused ? kDsBytes : 0) + kVecBytes +
+                                      kNumBars * 8 + 64 + (kMasks ? kMaskBytes : 0);
     static constexpr int kMaxSmem = 232448;                      // 227 KB: the most one CTA can ask for
+    static_assert(kUsedBytes <= kMaxSmem, "shared-memory plan does not fit");
     // what the launch asks for: room to align the base when it fits (the kernel checks what it got)
-    static constexpr int smem_bytes(bool fused, bool drop) {
-        return used_bytes(fused, drop) + 1024 <= kMaxSmem ? used_bytes(fused, drop) + 1024 : kMaxSmem;
-    }
+    static constexpr int kSmemBytes = kUsedBytes + 1024 <= kMaxSmem ? kUsedBytes + 1024 : kMaxSmem;
 };
 
 struct BwdArgs {
@@ -129,20 +142,21 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                  const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_out1, const __grid_constant__ CUtensorMap map_out2,
                  const BwdArgs a) {
-    using Cfg = BwdCfg<D>;
+    using Cfg = BwdCfg<D, MODE, DROP>;
     constexpr bool KS = (MODE != 1);        // key-stationary: K, V stay, query tiles stream
     constexpr bool FUSED = (MODE == 2);     // key-stationary and dQ too
-    constexpr int ST = Cfg::kStages;
+    constexpr int UST = Cfg::kUStages, WST = Cfg::kWStages;
     constexpr int TILE = Cfg::kTileBytes;
-    constexpr uint32_t kStageTx = (KS) ? (2 * TILE + 1024) : (2 * TILE);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sX = smem;
     uint8_t* sY = sX + TILE;
-    uint8_t* sRing = sY + TILE;                     // stage s: U | W | lse[128] | delta[128]
-    uint8_t* sDs = sRing + ST * Cfg::kStageBytes;   // fused kernel only
-    uint64_t* bars = (uint64_t*)(sDs + (FUSED ? Cfg::kDsBytes : 0));
+    uint8_t* sU = sY + TILE;                        // U ring
+    uint8_t* sW = sU + UST * TILE;                  // W ring
+    uint8_t* sDs = sW + WST * TILE;                 // fused kernel only
+    float* sVec = (float*)(sDs + (FUSED ? Cfg::kDsBytes : 0));      // key-stationary only: 2 x (lse[128] | delta[128])
+    uint64_t* bars = (uint64_t*)((uint8_t*)sVec + Cfg::kVecBytes);
     uint32_t* tmem_slot = (uint32_t*)(bars + Cfg::kNumBars);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(tmem_slot + 1);
     uint16_t* sMask = (uint16_t*)((uint8_t*)bars + Cfg::kNumBars * 8 + 64);    // present with dropout only
@@ -150,7 +164,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         // the launch may have had no room for a full kilobyte of alignment slack
         uint32_t dyn;
         asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
-        if ((uint32_t)(smem - smem_raw) + (uint32_t)Cfg::used_bytes(FUSED, DROP) > dyn) {
+        if ((uint32_t)(smem - smem_raw) + (uint32_t)Cfg::kUsedBytes > dyn) {
             if (threadIdx.x == 0 && a.status) atomicExch(a.status, 8);
             return;
         }
@@ -194,7 +208,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kNumBars; ++i) {
             const bool wide = (i == Cfg::kPReady || i == Cfg::kDsReady || i == Cfg::kMask || i == Cfg::kEpi ||
-                               i == Cfg::kDqRead || i == Cfg::kPHalf || i == Cfg::kDsHalf);
+                               i == Cfg::kDqRead || i == Cfg::kPHalf || i == Cfg::kDsHalf ||
+                               i == Cfg::kVEmpty || i == Cfg::kVEmpty + 1);
             mbar_init(&bars[i], wide ? 4u * NWG : 1u);    // one arrival per elementwise warp
         }
         *abort_flag = 0u;
@@ -226,7 +241,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       if (warp == kTmaWarp) {
         // ---------------------------------------------------------------- TMA producer
         if (elect_one()) {
-            int issued = 0;
+            int u_issued = 0, w_issued = 0, v_issued = 0;
             bool ok = true;
             if (n_iter > 0) {
                 mbar_expect_tx(&bars[Cfg::kXYFull], 2 * TILE);
@@ -237,35 +252,57 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
             }
             int qi = 0, hg = 0;
+            int us = 0, ws = 0;                      // ring slots of this step
+            uint32_t uph = 0, wph = 0;               // how often each ring has wrapped (parity)
             for (int it = 0; it < n_iter; ++it) {
-                const int s = it % ST;
-                const uint32_t ph = (uint32_t)(it / ST) & 1u;
-                ok = mbar_wait(&bars[Cfg::kUWEmpty + s], ph ^ 1u, abort_flag);
-                if (!ok) break;
-                uint8_t* stage = sRing + s * Cfg::kStageBytes;
                 int head_u, row_u;
                 if (KS) { head_u = head_x * group + hg; row_u = q_tile_of(qi) * kTile; }
-                else           { head_u = head_kv; row_u = it * kTile; }
-                mbar_expect_tx(&bars[Cfg::kUWFull + s], kStageTx);
+                else    { head_u = head_kv; row_u = it * kTile; }
+                ok = mbar_wait(&bars[Cfg::kUEmpty + us], (uph & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+                mbar_expect_tx(&bars[Cfg::kUFull + us], TILE);
 #pragma unroll
-                for (int bx = 0; bx < Cfg::kNBox; ++bx) {
-                    tma_load_4d(stage + bx * kBoxBytes, &map_u, &bars[Cfg::kUWFull + s], bx * 64, head_u, row_u, b);
-                    tma_load_4d(stage + TILE + bx * kBoxBytes, &map_w, &bars[Cfg::kUWFull + s], bx * 64, head_u, row_u, b);
-                }
+                for (int bx = 0; bx < Cfg::kNBox; ++bx)
+                    tma_load_4d(sU + us * TILE + bx * kBoxBytes, &map_u, &bars[Cfg::kUFull + us], bx * 64, head_u, row_u, b);
+                ++u_issued;
+                ok = mbar_wait(&bars[Cfg::kWEmpty + ws], (wph & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+                mbar_expect_tx(&bars[Cfg::kWFull + ws], TILE);
+#pragma unroll
+                for (int bx = 0; bx < Cfg::kNBox; ++bx)
+                    tma_load_4d(sW + ws * TILE + bx * kBoxBytes, &map_w, &bars[Cfg::kWFull + ws], bx * 64, head_u, row_u, b);
+                ++w_issued;
                 if (KS) {
+                    // the step's -lse*log2(e) and -delta rows: a two-slot ring of their own
+                    const int vs = it & 1;
+                    ok = mbar_wait(&bars[Cfg::kVEmpty + vs], ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag);
+                    if (!ok) break;
                     const int64_t off = ((int64_t)b * a.H + head_u) * a.nq_pad + row_u;
-                    bulk_load_1d(stage + 2 * TILE, a.lse2 + off, 512, &bars[Cfg::kUWFull + s]);
-                    bulk_load_1d(stage + 2 * TILE + 512, a.delta + off, 512, &bars[Cfg::kUWFull + s]);
+                    mbar_expect_tx(&bars[Cfg::kVFull + vs], 1024);
+                    bulk_load_1d(sVec + vs * 256, a.lse2 + off, 512, &bars[Cfg::kVFull + vs]);
+                    bulk_load_1d(sVec + vs * 256 + 128, a.delta + off, 512, &bars[Cfg::kVFull + vs]);
+                    ++v_issued;
                 }
-                ++issued;
+                if (++us == UST) { us = 0; ++uph; }
+                if (++ws == WST) { ws = 0; ++wph; }
                 if (++qi == n_per_head) { qi = 0; ++hg; }
             }
             if (!ok) {
                 // unwinding: let copies already issued land before shared memory is given up
-                for (int s = 0; s < ST; ++s) {
-                    const int nf = (issued + ST - 1 - s) / ST;
+                for (int st = 0; st < UST; ++st) {
+                    const int nf = (u_issued + UST - 1 - st) / UST;
                     for (int spin = 0; spin < 4096 && nf > 0 &&
-                         !mbar_try_wait(&bars[Cfg::kUWFull + s], (uint32_t)(nf - 1) & 1u); ++spin) {}
+                         !mbar_try_wait(&bars[Cfg::kUFull + st], (uint32_t)(nf - 1) & 1u); ++spin) {}
+                }
+                for (int st = 0; st < WST; ++st) {
+                    const int nf = (w_issued + WST - 1 - st) / WST;
+                    for (int spin = 0; spin < 4096 && nf > 0 &&
+                         !mbar_try_wait(&bars[Cfg::kWFull + st], (uint32_t)(nf - 1) & 1u); ++spin) {}
+                }
+                for (int st = 0; st < 2; ++st) {
+                    const int nf = (v_issued + 1 - st) / 2;
+                    for (int spin = 0; spin < 4096 && nf > 0 &&
+                         !mbar_try_wait(&bars[Cfg::kVFull + st], (uint32_t)(nf - 1) & 1u); ++spin) {}
                 }
                 for (int spin = 0; spin < 4096 && n_iter > 0 && !mbar_try_wait(&bars[Cfg::kXYFull], 0u); ++spin) {}
             }
@@ -276,7 +313,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (elect_one() && n_iter > 0) {
             constexpr uint32_t idesc_t = make_idesc_f16(BF16, BF16, kTile, kTile, false, false);
             constexpr uint32_t idesc_acc = make_idesc_f16(BF16, BF16, kTile, D, false, true);
-            const uint32_t sX_u = smem_u32(sX), sY_u = smem_u32(sY), sRing_u = smem_u32(sRing);
+            const uint32_t sX_u = smem_u32(sX), sY_u = smem_u32(sY), sU_u = smem_u32(sU), sW_u = smem_u32(sW);
 
             // Descriptors differ only in the 16-byte-granular start address held in their low
             // bits: build the two kinds once and add offsets in the issue loops, which keeps the
@@ -328,29 +365,37 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             };
 
             bool ok = mbar_wait(&bars[Cfg::kXYFull], 0u, abort_flag);
-            if (ok) ok = mbar_wait(&bars[Cfg::kUWFull + 0], 0u, abort_flag);
+            if (ok) ok = mbar_wait(&bars[Cfg::kUFull + 0], 0u, abort_flag);
+            if (ok) ok = mbar_wait(&bars[Cfg::kWFull + 0], 0u, abort_flag);
             if (ok) {
                 tc_fence_after_sync();
-                issue_t(tT1, sX_u, sRing_u);
+                issue_t(tT1, sX_u, sU_u);
                 mma_commit(&bars[Cfg::kT1Full]);
-                issue_t(tT2, sY_u, sRing_u + TILE);
+                issue_t(tT2, sY_u, sW_u);
                 mma_commit(&bars[Cfg::kT2Full]);
+                if (!KS) mma_commit(&bars[Cfg::kWEmpty + 0]);        // MODE 1: V_j is read by dP(j) only
             }
+            int us = 0, ws = 0;                      // ring slots of this step's U and W
+            uint32_t uph = 0, wph = 0;               // wrap counts (parity of the slots' phases)
             for (int it = 0; it < n_iter && ok; ++it) {
-                const int s = it % ST, ns = (it + 1) % ST;
-                const uint32_t nph = (uint32_t)((it + 1) / ST) & 1u;
-                const uint32_t cur_u = sRing_u + s * Cfg::kStageBytes, nxt_u = sRing_u + ns * Cfg::kStageBytes;
+                int nus = us + 1, nws = ws + 1;      // slots of the next step
+                uint32_t nuph = uph, nwph = wph;
+                if (nus == UST) { nus = 0; ++nuph; }
+                if (nws == WST) { nws = 0; ++nwph; }
+                const uint32_t cur_u = sU_u + us * TILE, nxt_u = sU_u + nus * TILE;
+                const uint32_t cur_w = sW_u + ws * TILE, nxt_w = sW_u + nws * TILE;
                 const bool more = it + 1 < n_iter;
-                if (more) { ok = mbar_wait(&bars[Cfg::kUWFull + ns], nph, abort_flag); if (!ok) break; }
+                if (more) { ok = mbar_wait(&bars[Cfg::kUFull + nus], nuph & 1u, abort_flag); if (!ok) break; }
                 if (KS) {
                     ok = mbar_wait(&bars[Cfg::kPHalf], (uint32_t)it & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_acc_half(tAcc2, tT1, cur_u + TILE, it > 0, 0);         // dV += (P o Z)^T dO, first halves
+                    issue_acc_half(tAcc2, tT1, cur_w, it > 0, 0);                // dV += (P o Z)^T dO, first halves
                     ok = mbar_wait(&bars[Cfg::kPReady], (uint32_t)it & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_acc_half(tAcc2, tT1, cur_u + TILE, it > 0, 1);
+                    issue_acc_half(tAcc2, tT1, cur_w, it > 0, 1);
+                    mma_commit(&bars[Cfg::kWEmpty + ws]);                        // dO_i: dP^T(i) earlier, dV(i) last
                     if (more) { issue_t(tT1, sX_u, nxt_u); mma_commit(&bars[Cfg::kT1Full]); }
                 } else if (more) {
                     // dQ needs no second accumulator, so S is double-buffered in its columns: S(it+1)
@@ -370,7 +415,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 if (!ok) break;
                 tc_fence_after_sync();
                 issue_acc_half(tAcc1, tT2, cur_u, it > 0, 1);
-                mma_commit(&bars[Cfg::kUWEmpty + s]);
+                mma_commit(&bars[Cfg::kUEmpty + us]);                            // last reader of U(it)
                 if (FUSED) {
                     // dQ tile of this step = dS K_j: A is the dS^T tile the threads left in shared memory,
                     // read MN-major (M = queries), B is the stationary K tile read MN-major (N = D)
@@ -390,7 +435,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         tc_fence_after_sync();
                     }
                 }
-                if (more) { issue_t(tT2, sY_u, nxt_u + TILE); mma_commit(&bars[Cfg::kT2Full]); }
+                if (more) {
+                    ok = mbar_wait(&bars[Cfg::kWFull + nws], nwph & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_t(tT2, sY_u, nxt_w);
+                    mma_commit(&bars[Cfg::kT2Full]);
+                    if (!KS) mma_commit(&bars[Cfg::kWEmpty + nws]);
+                }
+                us = nus; uph = nuph; ws = nws; wph = nwph;
             }
             if (ok) mma_commit(&bars[Cfg::kAccDone]);
         }
@@ -442,14 +495,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         int qi = 0, hg = 0;                 // step within the query head, query heads done (key-stationary)
         int prev_tile = 0, prev_head = 0;   // query tile and head of the previous step
         for (int it = 0; it < n_iter; ++it) {
-            const int s = it % ST;
-            const uint8_t* stage = sRing + s * Cfg::kStageBytes;
-            const float* lse_s = reinterpret_cast<const float*>(stage + 2 * TILE);
-            const float* del_s = lse_s + 128;
             const int strm_tile = (KS) ? q_tile_of(qi) : it;     // query tile (0) / key tile (1)
             const int col_g0 = strm_tile * kTile + cb;                          // global index of my first column
             const int head_q = (KS) ? head_x * group + hg : head_x;
             const uint32_t bh = (uint32_t)(b * a.H + head_q);
+            // key-stationary: -lse*log2(e) and -delta of this step's 128 queries (slot it & 1)
+            const float* lse_s = sVec + (it & 1) * 256;
+            const float* del_s = lse_s + 128;
 
             // ---- dropout keep bits of my CPT columns (bit c of kb[c / 32])
             uint32_t kb[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};
@@ -486,6 +538,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             // ---- phase A: P from T1
             ok = (KS) ? mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag)
                              : mbar_wait(&bars[Cfg::kT1Full + (it & 1)], (uint32_t)(it >> 1) & 1u, abort_flag);
+            if (KS && ok) ok = mbar_wait(&bars[Cfg::kVFull + (it & 1)], (uint32_t)(it >> 1) & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
@@ -636,6 +689,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #undef PSET
             tc_fence_before_sync();
             mbar_arrive_warp(&bars[Cfg::kDsReady]);
+            if (KS) mbar_arrive_warp(&bars[Cfg::kVEmpty + (it & 1)]);      // this step's lse / delta rows are read
             prev_tile = strm_tile; prev_head = head_q;
             if (++qi == n_per_head) { qi = 0; ++hg; }
         }
@@ -653,7 +707,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             for (int o = 0; o < kOuts; ++o) {
                 const uint32_t tacc = (o == 0 ? tAcc1 : tAcc2) + lane_off + (uint32_t)(wg * kCols);
                 const float mul = (o == 0) ? a.scale : a.inv_keep;
-                uint8_t* stage = sRing + o * TILE;             // ring stage 0 is idle once all MMAs completed
+                uint8_t* stage = sU + o * TILE;                // the U ring is idle once all MMAs completed
 #pragma unroll
                 for (int c0 = 0; c0 < kCols; c0 += 32) {
                     constexpr int kN = kCols < 32 ? kCols : 32;
@@ -685,9 +739,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             if (tid == 0 && mbar_wait(&bars[Cfg::kEpi], 0u, abort_flag)) {
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kNBox; ++bx) {
-                    tma_store_4d(&map_out1, sRing + bx * kBoxBytes, bx * 64, head_x, tile * kTile, b);
+                    tma_store_4d(&map_out1, sU + bx * kBoxBytes, bx * 64, head_x, tile * kTile, b);
                     if (KS)
-                        tma_store_4d(&map_out2, sRing + TILE + bx * kBoxBytes, bx * 64, head_x, tile * kTile, b);
+                        tma_store_4d(&map_out2, sU + TILE + bx * kBoxBytes, bx * 64, head_x, tile * kTile, b);
                 }
                 tma_store_commit();
                 tma_store_wait_read<0>();   // the staging tile has been read; the writes complete on their own
@@ -759,7 +813,6 @@ bwd_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, int Nq,
 
 template <int D, bool BF16>
 int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
-    using Cfg = BwdCfg<D>;
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
     const CUtensorMapDataType dt = BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     cudaStream_t st = (cudaStream_t)p.stream;
@@ -810,7 +863,7 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     if constexpr (D == 64) if (fused) {
         // one key-stationary kernel for dK, dV and the fp32 dQ sums, then the conversion of dQ
         auto k2 = drop ? bwd_sm100_kernel<D, BF16, 2, kNWG, true> : bwd_sm100_kernel<D, BF16, 2, kNWG, false>;
-        const int smem2 = Cfg::smem_bytes(true, drop);
+        const int smem2 = drop ? BwdCfg<D, 2, true>::kSmemBytes : BwdCfg<D, 2, false>::kSmemBytes;
         FA_CUDA_CHECK(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
         if (phases & 2) {
             k2<<<grid_kv, kThreads, smem2, st>>>(mk, mv, mq, mg, mdk, mdv, a);
@@ -825,15 +878,16 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     }
     auto k0 = drop ? bwd_sm100_kernel<D, BF16, 0, kNWG, true> : bwd_sm100_kernel<D, BF16, 0, kNWG, false>;
     auto k1 = drop ? bwd_sm100_kernel<D, BF16, 1, kNWG, true> : bwd_sm100_kernel<D, BF16, 1, kNWG, false>;
-    const int smem01 = Cfg::smem_bytes(false, drop);
-    FA_CUDA_CHECK(cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, smem01));
-    FA_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem01));
+    const int smem0 = drop ? BwdCfg<D, 0, true>::kSmemBytes : BwdCfg<D, 0, false>::kSmemBytes;
+    const int smem1 = drop ? BwdCfg<D, 1, true>::kSmemBytes : BwdCfg<D, 1, false>::kSmemBytes;
+    FA_CUDA_CHECK(cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, smem0));
+    FA_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
     if (phases & 2) {
-        k0<<<grid_kv, kThreads, smem01, st>>>(mk, mv, mq, mg, mdk, mdv, a);
+        k0<<<grid_kv, kThreads, smem0, st>>>(mk, mv, mq, mg, mdk, mdv, a);
         FA_CUDA_CHECK(cudaGetLastError());
     }
     if (phases & 4) {
-        k1<<<grid_q, kThreads, smem01, st>>>(mq, mg, mk, mv, mdq, mdq, a);
+        k1<<<grid_q, kThreads, smem1, st>>>(mq, mg, mk, mv, mdq, mdq, a);
         FA_CUDA_CHECK(cudaGetLastError());
     }
     return FA_OK;

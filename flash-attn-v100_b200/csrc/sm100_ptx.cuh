@@ -98,6 +98,11 @@ __device__ __forceinline__ void red_add_v4_f32(float* gptr, float x, float y, fl
                  ::"l"(gptr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
 }
 
+// Ask for the 128-byte line holding `gptr` to be brought into L1.
+__device__ __forceinline__ void prefetch_l1(const void* gptr) {
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(gptr));
+}
+
 // ---- TMA ----------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
