@@ -47,7 +47,7 @@
 //                    step's last MMA, so it gets three stages where shared memory allows and its
 //                    next load overlaps a whole step; W gets two), and in the key-stationary
 //                    kernels the step's -lse / -delta rows into a two-slot ring
-//   warps 18-19      idle (complete the fifth warpgroup for setmaxnreg)
+//   warps 18-19      idle (registers are granted per four warps)
 //
 // TMEM columns: T1 [0,128)  T2 [128,256)  ACC1 [256,256+D)  ACC2 [384,384+D).
 // MODE 1 has no ACC2 and uses [384,512) as a second S buffer: S(i+1) is computed
@@ -146,6 +146,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     constexpr bool KS = (MODE != 1);        // key-stationary: K, V stay, query tiles stream
     constexpr bool FUSED = (MODE == 2);     // key-stationary and dQ too
     constexpr int UST = Cfg::kUStages, WST = Cfg::kWStages;
+    constexpr bool kMoveRegisters = (D == 128);
     constexpr int TILE = Cfg::kTileBytes;
 
     extern __shared__ uint8_t smem_raw[];
@@ -237,7 +238,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t tDq = kDqAliasesT2 ? tT2 : tmem + 448u;
 
     if (warp >= kMmaWarp) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+      // Register split.  With the launch allocation of 96 per thread nobody spills; moving 8 registers
+      // per thread from these warps (left with 64: the key-stationary issuer then spills 40 bytes) to the
+      // elementwise ones measured 1.4 % faster over the whole backward at D = 128 and 7 % slower at
+      // D = 64, so only D = 128 does it.
+      if (kMoveRegisters) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
       if (warp == kTmaWarp) {
         // ---------------------------------------------------------------- TMA producer
         if (elect_one()) {
@@ -450,8 +455,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         __syncwarp();
       }
     } else {
-        if (NWG == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
-        else          asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+        if (kMoveRegisters) asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
         // ---------------------------------------------------------------- P / dS and epilogue
         constexpr int NLD = CPT / 32;                          // 32-column TMEM loads per thread and phase
         const int wg = warp >> 2;                              // which CPT-column slice
