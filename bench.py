@@ -109,7 +109,7 @@ def measured_peak():
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
 # profiles/ncu_full_fwd_bwd_cfg3_batch1.md: measured at batch 1 of the default workload and scaled by
 # the batch (traffic is proportional to the number of independent (batch, head) columns).
-NCU_DRAM_BYTES_PER_BATCH = {"fwd": 112.8e6, "bwd_dkdv": 178.2e6, "bwd_dq": 155.8e6}
+NCU_DRAM_BYTES_PER_BATCH = {"fwd": 112.6e6, "bwd_dkdv": 177.1e6, "bwd_dq": 155.1e6}
 
 
 def ncu_traffic(kernel: str, w):
@@ -282,11 +282,15 @@ def run_ours(args, w):
 
     call(lib.fa_b200_bwd, 0)()
     ksteps = max(5, args.steps)
+    # D = 64 in fp16/bf16 takes the one-kernel backward: phase 2 is the kernel that produces dK, dV and
+    # the fp32 dQ sums (5 GEMMs), phase 4 the conversion of the sums to dQ
+    one_kernel = (w.D == 64 and w.dtype in (torch.float16, torch.bfloat16))
+    k2, k4 = ("bwd_dkdvdq", "bwd_dq_convert") if one_kernel else ("bwd_dkdv", "bwd_dq")
     kern_ms = {
         "fwd": time_steps(call(lib.fa_b200_fwd, 0), ksteps, device, world),
         "bwd_preprocess": time_steps(call(lib.fa_b200_bwd, 1), ksteps, device, world),
-        "bwd_dkdv": time_steps(call(lib.fa_b200_bwd, 2), ksteps, device, world),
-        "bwd_dq": time_steps(call(lib.fa_b200_bwd, 4), ksteps, device, world),
+        k2: time_steps(call(lib.fa_b200_bwd, 2), ksteps, device, world),
+        k4: time_steps(call(lib.fa_b200_bwd, 4), ksteps, device, world),
     }
     p.bwd_phases = 0
     status = ops._status_word(device)
@@ -295,9 +299,12 @@ def run_ours(args, w):
     kernels = {
         # name: (ms, GEMMs counted by the metric's FLOP formula, GEMMs the kernel executes)
         "fwd": (kern_ms["fwd"], 2, 2),
-        "bwd_dkdv": (kern_ms["bwd_dkdv"], 4, 4),
-        "bwd_dq": (kern_ms["bwd_dq"], 1, 3),    # S and dP are recomputed here: executed, not counted
     }
+    if one_kernel:
+        kernels[k2] = (kern_ms[k2], 5, 5)
+    else:
+        kernels[k2] = (kern_ms[k2], 4, 4)
+        kernels[k4] = (kern_ms[k4], 1, 3)       # S and dP are recomputed here: executed, not counted
     peak, peak_kind, peaks_file = measured_peak()
     dom = max(kernels, key=lambda n: kernels[n][0])
     dom_ms, dom_alg, dom_exec = kernels[dom]
@@ -316,7 +323,7 @@ def run_ours(args, w):
     e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
     tb = w.tensor_bytes()
     fwd_tf = w.fwd_flops() / (kern_ms["fwd"] * 1e-3) / 1e12
-    bwd_ms = kern_ms["bwd_preprocess"] + kern_ms["bwd_dkdv"] + kern_ms["bwd_dq"]
+    bwd_ms = kern_ms["bwd_preprocess"] + kern_ms[k2] + kern_ms[k4]
     bwd_tf = w.bwd_flops() / (bwd_ms * 1e-3) / 1e12
 
     cpu = None
