@@ -107,6 +107,39 @@ def test_workspace_estimates():
     assert est["total_memory_mb"] < 4 * 32 * 4096 * 4096 * 2 / 2 ** 20   # far below the N^2 scores
 
 
+def test_workspace_size_follows_the_backward_variant():
+    """D = 64 in 16 bits: the one-kernel backward adds the fp32 dQ sums; the two-pass variant,
+    D = 128 and fp32 need the two per-row vectors only."""
+    lib = _cabi.load()
+
+    def size(D, dtype, variant):
+        p = _cabi.Params()
+        p.struct_bytes = ctypes.sizeof(_cabi.Params)
+        p.B, p.Nq, p.Nk, p.H, p.Hkv, p.D = 2, 300, 300, 4, 4, D
+        p.dtype, p.scale, p.variant = dtype, 0.125, variant
+        return int(lib.fa_b200_bwd_workspace_bytes(ctypes.byref(p)))
+
+    rows = 2 * 4 * 384                                   # B * H * ceil128(Nq)
+    vectors = 2 * rows * 4
+    bf16 = tile_table.dtype_enum(torch.bfloat16)
+    assert size(128, bf16, _cabi.VARIANT_AUTO) == vectors
+    assert size(64, bf16, _cabi.VARIANT_TCGEN05_2PASS) == vectors
+    assert size(64, bf16, _cabi.VARIANT_AUTO) == vectors + rows * 64 * 4
+    assert size(64, bf16, _cabi.VARIANT_TCGEN05) == vectors + rows * 64 * 4
+    assert size(64, tile_table.dtype_enum(torch.float32), _cabi.VARIANT_AUTO) <= vectors
+    assert _cabi.VARIANT_NAMES[_cabi.VARIANT_TCGEN05_2PASS] == "tcgen05_2pass"
+
+
+def test_dq_reproducibility_table():
+    from flash_attention_v100.testing import dq_is_bit_reproducible
+    assert dq_is_bit_reproducible("tcgen05_2pass", torch.bfloat16, 64)
+    assert dq_is_bit_reproducible("simt", torch.float16, 64)
+    assert dq_is_bit_reproducible("auto", torch.bfloat16, 128)
+    assert dq_is_bit_reproducible("auto", torch.float32, 64)
+    assert not dq_is_bit_reproducible("auto", torch.float16, 64)
+    assert not dq_is_bit_reproducible("tcgen05", torch.bfloat16, 64, 0.1)
+
+
 def test_public_signatures_match_the_reference():
     sig = inspect.signature(fa.flash_attention_v100)
     assert list(sig.parameters) == [
