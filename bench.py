@@ -76,24 +76,32 @@ class ClockSampler:
         return False
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
+        sm, mx, power, reasons = [], [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in self.lines:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                clock, top = float(parts[0]), float(parts[1])
             except ValueError:
                 continue
+            try:
+                watts = float(parts[2])
+            except ValueError:
+                watts = float("nan")
+            if watts < 300.0:        # not under load yet (or no longer); unknown power counts as load
+                continue
+            sm.append(clock)
+            mx.append(top)
+            power.append(watts)
             for name, flag in zip(names, parts[3:7]):
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "power_w": statistics.median(power)}
 
 
 def measured_peak():
@@ -252,6 +260,11 @@ def run_ours(args, w):
         step()
     with ClockSampler(local) as clocks:
         ms_step = time_steps(step, args.steps, device, world)
+        # nvidia-smi takes ~100 ms to start and then samples every 50 ms: keep the same load on the GPU
+        # (untimed) until the sampler has seen about half a second of it
+        for _ in range(int(500.0 / max(ms_step, 0.05)) + 1):
+            step()
+        torch.cuda.synchronize(device)
     clock_info = clocks.summary()
     for _ in range(2):
         step_e2e()

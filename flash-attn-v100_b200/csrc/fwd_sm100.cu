@@ -581,6 +581,7 @@ bool tensor_ok(const fa_b200_tensor& t, int64_t B, int64_t N, int64_t H) {
 // Which calls the tensor-core family covers.  `why` names the first reason it does not.
 bool sm100_supports(const fa_b200_params& p, bool backward, const char** why) {
     if (p.dtype != FA_B200_F16 && p.dtype != FA_B200_BF16) { *why = "dtype must be fp16 or bf16"; return false; }
+    if (p.bias.ptr) { *why = "an additive bias is served by the CUDA-core kernels"; return false; }
     if (p.D != 64 && p.D != 128) { *why = "head_dim must be 64 or 128"; return false; }
     if (!(p.scale > 0.f) || !(p.scale < 1e30f)) { *why = "scale must be positive and finite"; return false; }
     if (p.B > 65535 || p.H > 65535) { *why = "batch and heads must be below 65536"; return false; }

@@ -30,6 +30,8 @@ constexpr int MAXC = 8;      // output columns per thread: D <= 16*MAXC = 128
 
 struct SimtArgs {
     fa_b200_tensor q, k, v, o, d_o, dq, dk, dv;
+    fa_b200_tensor bias;   // fp32 (B, H, Nq, Nk) with broadcast strides; ptr = nullptr: none
+    float* d_scores;       // optional dense (B, H, Nq, Nk) gradient of the scores
     float* lse;
     float* delta;
     int B, Nq, Nk, H, Hkv, D;
@@ -67,6 +69,8 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(SimtArgs a) {
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int m0 = mt * BM;
     const uint32_t bh = (uint32_t)(b * a.H + h);
+    const float* bias_b = a.bias.ptr ? (const float*)a.bias.ptr + (int64_t)b * a.bias.stride_b + (int64_t)h * a.bias.stride_h
+                                     : nullptr;
 
     const T* qb = (const T*)a.q.ptr + (int64_t)b * a.q.stride_b + (int64_t)h * a.q.stride_h;
     const T* kb = (const T*)a.k.ptr + (int64_t)b * a.k.stride_b + (int64_t)hk * a.k.stride_h;
@@ -114,6 +118,7 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(SimtArgs a) {
             for (int c = 0; c < 4; ++c) {
                 int j = n0 + tx + 16 * c;
                 float s = acc[r][c] * a.scale;
+                if (bias_b && i < a.Nq && j < a.Nk) s += bias_b[(int64_t)i * a.bias.stride_n + j];
                 if (j >= a.Nk || (a.causal && j > i)) s = -INFINITY;
                 Ss[(ty * 4 + r) * SLD + tx + 16 * c] = s;
             }
@@ -254,6 +259,9 @@ __global__ void __launch_bounds__(NT) simt_bwd_kernel(SimtArgs a) {
         const T* gb = (const T*)a.d_o.ptr + (int64_t)b * a.d_o.stride_b + (int64_t)h * a.d_o.stride_h;
         const float* lse_b = a.lse + ((int64_t)b * a.H + h) * a.Nq;
         const float* del_b = a.delta + ((int64_t)b * a.H + h) * a.Nq;
+        const float* bias_b = a.bias.ptr ? (const float*)a.bias.ptr + (int64_t)b * a.bias.stride_b +
+                                               (int64_t)h * a.bias.stride_h : nullptr;
+        float* ds_b = a.d_scores ? a.d_scores + ((int64_t)b * a.H + h) * (int64_t)a.Nq * a.Nk : nullptr;
 
         int it_begin, it_end;   // tile indices of the streamed operand
         if (MODE == 0) {
@@ -328,11 +336,17 @@ __global__ void __launch_bounds__(NT) simt_bwd_kernel(SimtArgs a) {
                     const int col = tx + 16 * c, j = n0 + col;
                     float p = 0.f, z = 1.f;
                     bool visible = (i < a.Nq) && (j < a.Nk) && !(a.causal && j > i);
-                    if (visible) p = expf(s_acc[r][c] * a.scale - lse_i);
+                    if (visible) {
+                        float s = s_acc[r][c] * a.scale;
+                        if (bias_b) s += bias_b[(int64_t)i * a.bias.stride_n + j];
+                        p = expf(s - lse_i);
+                    }
                     if (a.drop_thr)
                         z = dropout_keep(a.key, bh, (uint32_t)i, (uint32_t)j, a.drop_thr) ? a.inv_keep : 0.f;
                     Ps[row * SLD + col] = p * z;
-                    Ds[row * SLD + col] = p * (p_acc[r][c] * z - del_i);
+                    const float ds = p * (p_acc[r][c] * z - del_i);
+                    Ds[row * SLD + col] = ds;
+                    if (MODE == 1 && ds_b && visible) ds_b[(int64_t)i * a.Nk + j] = ds;
                 }
             }
             __syncthreads();
@@ -431,6 +445,7 @@ SimtArgs make_args(const fa_b200_params& p, float* delta) {
     SimtArgs a;
     a.q = p.q; a.k = p.k; a.v = p.v; a.o = p.o; a.d_o = p.d_o; a.dq = p.dq; a.dk = p.dk; a.dv = p.dv;
     a.lse = p.lse; a.delta = delta;
+    a.bias = p.bias; a.d_scores = p.d_scores;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv; a.D = p.D;
     a.causal = p.causal; a.scale = p.scale;
     a.drop_thr = dropout_threshold(p.dropout_p);

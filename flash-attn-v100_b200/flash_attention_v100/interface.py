@@ -267,7 +267,8 @@ def flash_attention_v100(
         causal: key j is visible to query i iff j <= i
         scale: defaults to 1/sqrt(head_dim)
         dropout_p: drop probability of the attention weights (quantised to 1/256)
-        bias: not supported yet (raises NotImplementedError)
+        bias: additive score bias, (B|1, H|1, Nq|1, Nk): scores = scale * q.k + bias before the causal mask;
+            -inf entries mask keys.  Served by the CUDA-core kernels; its gradient is returned
         block_size_m, block_size_n, enable_autotuning, optimization_strategy:
             accepted for source compatibility; tiles come from the static table
         return_softmax_lse: also return the (B, H, Nq) fp32 log-sum-exp
@@ -335,7 +336,16 @@ def _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, bl
             ql = _slice(q, shard).to(dev, non_blocking=True)
             kl = _slice(k, kv_shard).to(dev, non_blocking=True)
             vl = _slice(v, kv_shard).to(dev, non_blocking=True)
-            res = FlashAttentionV100Function.apply(ql, kl, vl, scale, causal, dropout_p, bias, block_size_m,
+            bl = None
+            if bias is not None:
+                # the shard's part of the bias (broadcast dimensions stay whole)
+                bl = bias
+                if bl.shape[0] > 1:
+                    bl = bl[shard[0]:shard[1]]
+                if bl.shape[1] > 1:
+                    bl = bl[:, shard[2]:shard[3]]
+                bl = bl.to(dev, non_blocking=True)
+            res = FlashAttentionV100Function.apply(ql, kl, vl, scale, causal, dropout_p, bl, block_size_m,
                                                    block_size_n, enable_autotuning, return_softmax_lse)
             o_l, lse_l = res if return_softmax_lse else (res, None)
             outs.append((shard, o_l.to(home, non_blocking=True)))

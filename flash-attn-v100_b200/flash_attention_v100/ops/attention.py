@@ -97,6 +97,24 @@ def _tensor4(t: Optional[torch.Tensor]) -> _cabi.Tensor4:
     return r
 
 
+def _bias_operand(bias: Optional[torch.Tensor]):
+    """(Tensor4, keep-alive tensor) for an additive bias: fp32, key index contiguous, size-1 batch /
+    head / query dimensions passed as stride 0 (no expanded copy is made)."""
+    if bias is None:
+        return _cabi.Tensor4(), None
+    bf = bias.detach()
+    if bf.dtype != torch.float32:
+        bf = bf.float()
+    if bf.stride(3) != 1 and bf.shape[3] > 1:
+        bf = bf.contiguous()
+    r = _cabi.Tensor4()
+    r.ptr = bf.data_ptr()
+    r.stride_b = 0 if bf.shape[0] == 1 else bf.stride(0)
+    r.stride_h = 0 if bf.shape[1] == 1 else bf.stride(1)
+    r.stride_n = 0 if bf.shape[2] == 1 else bf.stride(2)
+    return r, bf
+
+
 def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset) -> _cabi.Params:
     p = _cabi.Params()
     p.struct_bytes = ctypes.sizeof(_cabi.Params)
@@ -116,7 +134,7 @@ def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset) -> _ca
     return p
 
 
-def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None):
+def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None, bias=None):
     """o, lse <- fa_b200_fwd.  Counterpart of flash_attention_forward_triton_enhanced
     (kernels/forward_kernel.py:246-387); returns (o, lse).  `out=(o, lse)` writes into
     caller-owned buffers (o like q, lse (B, H, Nq) fp32 contiguous) instead of allocating."""
@@ -126,13 +144,14 @@ def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=
         o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
     p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset)
+    p.bias, _keep = _bias_operand(bias)        # scores = scale * q.k + bias (CUDA-core kernels)
     rc = _cabi.load().fa_b200_fwd(ctypes.byref(p))
     _cabi.raise_for_status(rc, "fa_b200_fwd")
     return o, lse
 
 
 def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None,
-                    workspace=None):
+                    workspace=None, bias=None, d_scores=None):
     """dq, dk, dv <- fa_b200_bwd.  Counterpart of
     flash_attention_backward_triton_enhanced (kernels/backward_kernel.py:208-318).
     `out=(dq, dk, dv)` and `workspace` (uint8, at least fa_b200_bwd_workspace_bytes)
@@ -146,6 +165,13 @@ def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, 
         dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
     p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset)
     p.d_o, p.dq, p.dk, p.dv = _tensor4(d_o), _tensor4(dq), _tensor4(dk), _tensor4(dv)
+    p.bias, _keep = _bias_operand(bias)
+    if d_scores is not None:
+        # dense (B, H, Nq, Nk) fp32, zero-filled by the caller: receives d loss / d scores
+        if d_scores.dtype != torch.float32 or not d_scores.is_contiguous() or \
+                tuple(d_scores.shape) != (q.shape[0], q.shape[2], q.shape[1], k.shape[1]):
+            raise ValueError("d_scores must be a contiguous fp32 (B, H, Nq, Nk) tensor")
+        p.d_scores = d_scores.data_ptr()
     lib = _cabi.load()
     nbytes = int(lib.fa_b200_bwd_workspace_bytes(ctypes.byref(p)))
     if workspace is None:
@@ -181,8 +207,8 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
         seed = offset = 0
         if dropout_p > 0.0:
             seed, offset = _next_dropout_stream()
-        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset)
-        ctx.save_for_backward(q, k, v, o, lse)
+        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias)
+        ctx.save_for_backward(q, k, v, o, lse, *([bias] if bias is not None else []))
         ctx.scale, ctx.causal, ctx.dropout_p = scale, bool(causal), float(dropout_p)
         ctx.seed, ctx.offset = seed, offset
         ctx.return_softmax_lse = bool(return_softmax_lse)
@@ -193,12 +219,22 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output: torch.Tensor, grad_softmax_lse: Optional[torch.Tensor] = None):
-        q, k, v, o, lse = ctx.saved_tensors
+        q, k, v, o, lse, *rest = ctx.saved_tensors
+        bias = rest[0] if rest else None
+        d_scores = grad_bias = None
+        if bias is not None and ctx.needs_input_grad[6]:
+            # the reference returns zeros here (ops/attention.py:297-301); this is the real gradient:
+            # d loss / d scores, dense, summed over the dimensions the bias broadcasts
+            d_scores = torch.zeros(q.shape[0], q.shape[2], q.shape[1], k.shape[1], dtype=torch.float32,
+                                   device=q.device)
         dq, dk, dv = launch_backward(grad_output, q, k, v, o, lse, ctx.scale, ctx.causal,
-                                     ctx.dropout_p, ctx.seed, ctx.offset)
+                                     ctx.dropout_p, ctx.seed, ctx.offset, bias=bias, d_scores=d_scores)
+        if d_scores is not None:
+            dims = [i for i in range(4) if bias.shape[i] == 1 and d_scores.shape[i] != 1]
+            grad_bias = (d_scores.sum(dim=dims, keepdim=True) if dims else d_scores).to(bias.dtype)
         return (dq if ctx.needs_input_grad[0] else None,
                 dk if ctx.needs_input_grad[1] else None,
-                dv if ctx.needs_input_grad[2] else None) + (None,) * 16
+                dv if ctx.needs_input_grad[2] else None, None, None, None, grad_bias) + (None,) * 12
 
 
 def flash_attention_forward_enhanced(q, k, v, scale: Optional[float] = None, causal: bool = False,
@@ -212,7 +248,7 @@ def flash_attention_forward_enhanced(q, k, v, scale: Optional[float] = None, cau
     if dropout_p > 0.0:
         seed, offset = kwargs.get("dropout_stream") or _next_dropout_stream()
     with torch.no_grad():
-        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset)
+        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias)
     return (o, lse) if kwargs.get("return_softmax_lse", False) else o
 
 
@@ -222,12 +258,14 @@ def flash_attention_backward_enhanced(grad_output, q, k, v, output, lse, max_val
                                       ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Explicit backward (reference ops/attention.py:536-600).  `max_vals` is
     accepted and ignored: the kernels recompute P from the log-sum-exp alone.
-    kwargs: dropout_p and dropout_stream=(seed, offset) to replay a mask."""
-    q, k, v, scale = validate_inputs(q, k, v, scale, None, kwargs.get("dropout_p", 0.0))
+    kwargs: dropout_p and dropout_stream=(seed, offset) to replay a mask; bias (the forward's additive
+    bias) and d_scores (zero-filled fp32 (B, H, Nq, Nk) that receives d loss / d scores)."""
+    q, k, v, scale = validate_inputs(q, k, v, scale, kwargs.get("bias"), kwargs.get("dropout_p", 0.0))
     seed, offset = kwargs.get("dropout_stream", (0, 0))
     with torch.no_grad():
         return launch_backward(grad_output, q, k, v, _last_dim_contiguous(output), lse.contiguous(),
-                               scale, causal, kwargs.get("dropout_p", 0.0), seed, offset)
+                               scale, causal, kwargs.get("dropout_p", 0.0), seed, offset,
+                               bias=kwargs.get("bias"), d_scores=kwargs.get("d_scores"))
 
 
 def compare_with_pytorch_attention_enhanced(q, k, v, causal: bool = False,

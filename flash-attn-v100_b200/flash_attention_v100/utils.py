@@ -69,7 +69,18 @@ def validate_inputs(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
         # there is no CPU path here, so this is always an error
         raise ValueError("Flash Attention V100 requires CUDA tensors")
     if bias is not None:
-        raise NotImplementedError("additive attention bias is not supported by the B200 kernels yet")
+        # reference interface.py:505-525
+        if not isinstance(bias, torch.Tensor):
+            raise TypeError("bias must be a torch.Tensor")
+        b, nq, h = q.shape[0], q.shape[1], q.shape[2]
+        nk = k.shape[1]
+        expected = [(b, h, nq, nk), (1, h, nq, nk), (b, 1, nq, nk), (1, 1, nq, nk),
+                    (b, 1, 1, nk), (1, 1, 1, nk)]       # the last two: key-padding masks (broadcast over queries)
+        if tuple(bias.shape) not in expected:
+            raise ValueError(f"bias shape {tuple(bias.shape)} not compatible with attention shape. "
+                             f"Expected one of: {expected}")
+        if bias.device != q.device:
+            raise ValueError("bias must be on the same device as input tensors")
     if not (0.0 <= dropout_p < 1.0):
         raise ValueError(f"dropout_p must be in [0.0, 1.0), got {dropout_p}")
     if dq > 128:

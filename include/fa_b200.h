@@ -109,6 +109,17 @@ typedef struct fa_b200_params {
                                       2 = dK/dV kernel, 4 = dQ kernel.  Bits 2 and 4 need
                                       a workspace that an earlier call with bit 1 filled. */
     int32_t        reserved;
+    /* Additive score bias, scores = scale * q.k + bias (reference kernels/forward_kernel.py:171-176;
+       the reference's backward ignores it and returns a zero grad_bias, ops/attention.py:297-301).
+       fp32, logical shape (B, H, Nq, Nk): stride_b / stride_h / stride_n are the element strides over
+       batch, head and QUERY index, the key index has stride 1; a stride of 0 broadcasts (a key-padding
+       mask is (B, 1, 1, Nk): stride_h = stride_n = 0).  -inf entries mask keys.  ptr = NULL: no bias.
+       Calls with a bias are served by the CUDA-core kernels. */
+    fa_b200_tensor bias;
+    /* backward, optional: dense (B, H, Nq, Nk) fp32 buffer, zero-filled by the caller, that receives
+       d(loss)/d(scores) = P o (dP o Z - delta); the caller sums it over the bias' broadcast
+       dimensions to get grad_bias.  NULL: not produced. */
+    float*         d_scores;
 } fa_b200_params;
 
 /* Static tile choice for a (D, dtype, causal) key; replaces the reference's

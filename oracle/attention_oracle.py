@@ -37,14 +37,19 @@ from typing import Optional, Tuple
 import torch
 
 
-def _scores(q, k, scale, causal):
-    """(B,H,Nq,Nk) scaled, masked scores; reference __init__.py:36-48."""
+def _scores(q, k, scale, causal, bias=None):
+    """(B,H,Nq,Nk) scaled, masked scores; reference __init__.py:36-48.  `bias`
+    (broadcastable to (B,H,Nq,Nk)) is added after the scaling and before the
+    causal mask, as the reference's test twin does (tests/test_attention.py:48-58)
+    and its forward kernel intends (kernels/forward_kernel.py:171-176)."""
     qt = q.transpose(1, 2)
     kt = k.transpose(1, 2)
     hq, hk = qt.shape[1], kt.shape[1]
     if hq != hk:  # grouped K/V heads: query head h reads kv head h // (H/Hkv)
         kt = kt.repeat_interleave(hq // hk, dim=1)
     s = torch.matmul(qt * scale, kt.transpose(-2, -1))
+    if bias is not None:
+        s = s + bias.to(s.dtype)
     if causal:
         nq, nk = s.shape[-2], s.shape[-1]
         # reference: triu(ones(seq, seq), diagonal=1) -> key j masked iff j > i
@@ -56,7 +61,7 @@ def _scores(q, k, scale, causal):
 def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                       causal: bool = False, scale: Optional[float] = None,
                       dropout_p: float = 0.0, keep_mask: Optional[torch.Tensor] = None,
-                      compute_dtype: torch.dtype = torch.float32
+                      compute_dtype: torch.dtype = torch.float32, bias: Optional[torch.Tensor] = None
                       ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Dense attention, returns (O (B,Nq,H,D), LSE (B,H,Nq)) in compute_dtype.
 
@@ -69,7 +74,7 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     v = v.to(compute_dtype)
     if scale is None:
         scale = q.shape[-1] ** -0.5          # reference __init__.py:32
-    s = _scores(q, k, scale, causal)
+    s = _scores(q, k, scale, causal, bias)
     lse = torch.logsumexp(s, dim=-1)
     p = torch.softmax(s, dim=-1)             # reference __init__.py:50
     if keep_mask is not None:
@@ -82,14 +87,15 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
 
 
 def attention_forward_backward(q, k, v, d_o, *, causal=False, scale=None, dropout_p=0.0,
-                               keep_mask=None, compute_dtype=torch.float32):
+                               keep_mask=None, compute_dtype=torch.float32, bias=None):
     """(O, LSE, dQ, dK, dV) with gradients from autograd through the restated
-    forward (the same route a user of the reference's math path takes)."""
+    forward (the same route a user of the reference's math path takes).  With a
+    `bias` that requires grad, its gradient is left in bias.grad."""
     q = q.detach().to(compute_dtype).requires_grad_(True)
     k = k.detach().to(compute_dtype).requires_grad_(True)
     v = v.detach().to(compute_dtype).requires_grad_(True)
     o, lse = attention_forward(q, k, v, causal=causal, scale=scale, dropout_p=dropout_p,
-                               keep_mask=keep_mask, compute_dtype=compute_dtype)
+                               keep_mask=keep_mask, compute_dtype=compute_dtype, bias=bias)
     o.backward(d_o.to(compute_dtype))
     return o.detach(), lse.detach(), q.grad, k.grad, v.grad
 

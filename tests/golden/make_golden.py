@@ -56,6 +56,30 @@ def main():
             causal=np.array(causal), scale=np.array(d ** -0.5 if scale is None else scale, np.float64))
         print("wrote", name, tuple(o.shape))
 
+    # Additive bias: the top-level math path takes none, so these come from the dense twin the
+    # reference's own tests compare against (tests/test_attention.py:30-87: scores * scale + bias,
+    # then the causal mask, softmax, P V), with autograd through it for dQ, dK, dV and dBias.
+    with redirect_stdout(io.StringIO()):
+        import reference.tests.test_attention as ref_tests
+    twin = ref_tests.flash_attention_v100
+    assert twin.__doc__ == "Simple flash attention implementation for testing"
+    for name, b, n, h, d, causal, bias_shape in [
+            ("bias_full_b2n80h3d32", 2, 80, 3, 32, False, (2, 3, 80, 80)),
+            ("bias_heads_bcast_b2n96h2d64_causal", 2, 96, 2, 64, True, (2, 1, 96, 96)),
+            ("bias_both_bcast_b1n70h2d16", 1, 70, 2, 16, False, (1, 1, 70, 70))]:
+        g = torch.Generator().manual_seed(4321 + n)
+        q, k, v, d_o = (torch.randn(b, n, h, d, generator=g) for _ in range(4))
+        bias = torch.randn(bias_shape, generator=g)
+        qa, ka, va, ba = (t.clone().requires_grad_(True) for t in (q, k, v, bias))
+        o = twin(qa, ka, va, causal=causal, bias=ba)
+        o.backward(d_o)
+        np.savez_compressed(
+            os.path.join(HERE, f"test_twin_{name}.npz"),
+            q=q.numpy(), k=k.numpy(), v=v.numpy(), d_o=d_o.numpy(), bias=bias.numpy(), o=o.detach().numpy(),
+            dq=qa.grad.numpy(), dk=ka.grad.numpy(), dv=va.grad.numpy(), dbias=ba.grad.numpy(),
+            causal=np.array(causal), scale=np.array(d ** -0.5, np.float64))
+        print("wrote", name, tuple(o.shape))
+
     # README quick-start shape (B2 N1024 H12 D64 fp32 causal, seed 0): inputs come from
     # the package's seeded generator; every 37th query row of O is stored.
     from flash_attention_v100.testing import WORKLOADS, make_inputs

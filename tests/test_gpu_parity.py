@@ -320,8 +320,11 @@ def test_error_codes_on_device(device):
     with pytest.raises(ValueError, match="tcgen05"):
         with kernel_variant("tcgen05"):
             launch_forward(q[..., :40].contiguous(), q[..., :40].contiguous(), q[..., :40].contiguous(), 1.0, False)
-    with pytest.raises(NotImplementedError):
-        fa.flash_attention_v100(q, q, q, bias=torch.zeros(1, 2, 16, 16, device=device))
+    with pytest.raises(ValueError, match="bias shape"):
+        fa.flash_attention_v100(q, q, q, bias=torch.zeros(1, 2, 8, 16, device=device))
+    with pytest.raises(ValueError, match="tcgen05"):          # a bias is served by the CUDA-core kernels only
+        with kernel_variant("tcgen05"):
+            launch_forward(q, q, q, 1.0, False, bias=torch.zeros(1, 2, 16, 16, device=device))
     # empty problems are legal and return empty tensors
     e = torch.zeros(0, 16, 2, 64, device=device, dtype=torch.float16)
     assert fa.flash_attention_v100(e, e, e, enable_multi_gpu=False).shape == (0, 16, 2, 64)
@@ -353,3 +356,47 @@ def test_many_small_heads_and_long_sequence_shapes(device):
     _run_case(device, "tcgen05", 3, 130, 130, 70, 70, 64, torch.float16, True, seed=77)
     _run_case(device, "tcgen05", 1, 2304, 2304, 1, 1, 128, torch.float16, True, seed=78)
     _run_case(device, "tcgen05", 1, 1100, 2500, 2, 1, 128, torch.bfloat16, False, seed=79)
+
+
+BIAS_CASES = sorted(glob.glob(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden",
+                                           "test_twin_bias_*.npz")))
+
+
+@pytest.mark.parametrize("path", BIAS_CASES, ids=[os.path.basename(p)[15:-4] for p in BIAS_CASES])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_additive_bias_against_the_reference_test_twin(device, path, dtype):
+    """scores = scale * q.k + bias; O, dQ, dK, dV and dBias against the fixtures made from the dense
+    twin in the reference's tests (fp32 directly; bf16 inputs against the oracle on the rounded inputs)."""
+    z = np.load(path)
+    causal, scale = bool(z["causal"]), float(z["scale"])
+    t = {k: torch.from_numpy(z[k]) for k in ("q", "k", "v", "d_o", "bias", "o", "dq", "dk", "dv", "dbias")}
+    tol = tolerance(dtype)
+    if dtype == torch.float32:
+        ref = {n: t[n] for n in ("o", "dq", "dk", "dv", "dbias")}
+    else:
+        rb = t["bias"].clone().requires_grad_(True)
+        o, _, dq, dk, dv = ao.attention_forward_backward(*(t[n].to(dtype).float() for n in ("q", "k", "v", "d_o")),
+                                                         causal=causal, scale=scale, bias=rb)
+        ref = {"o": o, "dq": dq, "dk": dk, "dv": dv, "dbias": rb.grad}
+    q, k, v = (t[n].to(dtype).to(device).requires_grad_(True) for n in ("q", "k", "v"))
+    bias = t["bias"].to(device).requires_grad_(True)               # fp32 bias with 16-bit inputs is allowed
+    o = fa.flash_attention_v100(q, k, v, causal=causal, scale=scale, bias=bias, enable_multi_gpu=False)
+    o.backward(t["d_o"].to(dtype).to(device))
+    _check("O", o, ref["o"], tol)
+    _check("dQ", q.grad, ref["dq"], tol)
+    _check("dK", k.grad, ref["dk"], tol)
+    _check("dV", v.grad, ref["dv"], tol)
+    assert bias.grad.shape == bias.shape
+    _check("dBias", bias.grad, ref["dbias"], tol)
+
+
+def test_key_padding_mask_as_bias(device):
+    """A (B, 1, 1, Nk) bias of 0 / -inf hides keys: equal to attention over the kept keys only."""
+    B, N, H, D, keep = 2, 150, 3, 64, 101
+    dtype = torch.float16
+    q, k, v = (_rand((B, N, H, D), dtype, 60 + i).to(device) for i in range(3))
+    mask = torch.zeros(B, 1, 1, N, device=device)
+    mask[..., keep:] = float("-inf")
+    o = fa.flash_attention_v100(q, k, v, bias=mask, enable_multi_gpu=False)
+    o_ref = fa.flash_attention_v100(q, k[:, :keep].contiguous(), v[:, :keep].contiguous(), enable_multi_gpu=False)
+    assert rel_l2(o, o_ref) < 2e-3

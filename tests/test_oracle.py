@@ -41,6 +41,26 @@ def test_python_oracle_matches_reference_math_path(path):
                           torch.ones_like(lse, dtype=torch.float64), atol=1e-5)
 
 
+BIAS_CASES = sorted(glob.glob(os.path.join(GOLDEN, "test_twin_bias_*.npz")))
+
+
+@pytest.mark.parametrize("path", BIAS_CASES, ids=[os.path.basename(p)[15:-4] for p in BIAS_CASES])
+def test_python_oracle_matches_reference_test_twin_with_bias(path):
+    """Additive bias: the fixtures come from the dense twin in the reference's own tests
+    (tests/test_attention.py:30-87), gradients by autograd through it, dBias included."""
+    z = np.load(path)
+    t = {k: torch.from_numpy(z[k]) for k in ("q", "k", "v", "d_o", "bias", "o", "dq", "dk", "dv", "dbias")}
+    bias = t["bias"].clone().requires_grad_(True)
+    o, lse, dq, dk, dv = ao.attention_forward_backward(t["q"], t["k"], t["v"], t["d_o"], causal=bool(z["causal"]),
+                                                       scale=float(z["scale"]), bias=bias)
+    for name, got in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv), ("dbias", bias.grad)):
+        assert ao.rel_l2(got, t[name]) < 2e-6, name
+
+
+def test_bias_fixtures_present():
+    assert len(BIAS_CASES) == 3
+
+
 @pytest.mark.parametrize("path", CASES, ids=[os.path.basename(p)[10:-4] for p in CASES])
 def test_c_oracle_matches_reference_math_path(path):
     t, causal, scale = _load(path)
