@@ -29,6 +29,7 @@ from .ops.attention import (
     kernel_variant,
 )
 from .ops.host_pipeline import HostAttentionStep
+from .modules import EnhancedMultiHeadAttention
 
 __version__ = "0.1.0"
 __author__ = "flash_attention_v100 B200 build"
@@ -61,5 +62,5 @@ __all__ = [
     "flash_attention_v100_with_dropout", "flash_attention_v100_multi_gpu",
     "FlashAttentionV100Manager", "get_flash_attention_manager", "flash_attention_performance_mode",
     "flash_attention_memory_mode", "get_enhanced_config", "plan_shards", "set_dropout_seed",
-    "kernel_variant", "HostAttentionStep",
+    "kernel_variant", "HostAttentionStep", "EnhancedMultiHeadAttention",
 ]
