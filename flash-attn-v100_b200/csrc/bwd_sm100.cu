@@ -119,6 +119,7 @@ struct BwdArgs {
     const float* lse2;     // [B*H][nq_pad]  -lse * log2(e), -inf in the padding
     const float* delta;    // [B*H][nq_pad]  -delta, 0 in the padding
     float* dq_acc;         // fused kernel: fp32 dQ sums, [B*H][nq_pad/128] tiles of [D/4][128 rows][4]
+    const int32_t* kv_len; // optional per-batch key counts
     int32_t* status;
     int B, Nq, Nk, H, Hkv, nq_pad;
     int causal;
@@ -177,18 +178,20 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const int nq_tiles = (a.Nq + kTile - 1) / kTile;
 
     // iteration space (uniform over the CTA)
+    const int nk = kv_len_of(a.kv_len, b, a.Nk);    // keys this batch entry attends to
     int tile, head_x, it0, n_per_head, n_iter;
     if (KS) {
         tile = blockIdx.x;                          // key tile
         head_x = blockIdx.y;                        // kv head
         it0 = a.causal ? tile : 0;                  // first query tile that sees this key tile
         n_per_head = nq_tiles > it0 ? nq_tiles - it0 : 0;
+        if (tile * kTile >= nk) n_per_head = 0;     // a tile of padding keys: dK = dV = 0
         n_iter = n_per_head * group;
     } else {
         tile = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;   // query tile, heavy first
         head_x = blockIdx.y;                        // query head
         it0 = 0;
-        int kv_end = a.Nk;
+        int kv_end = nk;
         if (a.causal && tile * kTile + kTile < kv_end) kv_end = tile * kTile + kTile;
         n_per_head = (kv_end + kTile - 1) / kTile;
         n_iter = n_per_head;
@@ -579,6 +582,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         for (int c = hf * (CPT / 2); c < (hf + 1) * (CPT / 2); ++c)
                             if (row_g > col_g0 + c) PSET(c, 0.f);
                     }
+                    if (row_g >= nk) {                    // a padding key inside a live tile (or beyond Nk)
+#pragma unroll
+                        for (int c = hf * (CPT / 2); c < (hf + 1) * (CPT / 2); ++c) PSET(c, 0.f);
+                    }
                     uint32_t pk[CPT / 4];
 #pragma unroll
                     for (int e = 0; e < CPT / 4; ++e) {
@@ -609,11 +616,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     PSET(c + 1, ex2(x1));
                 }
                 const bool diag = a.causal && strm_tile == tile;
-                if (diag || strm_tile * kTile + kTile > a.Nk) {
+                if (diag || strm_tile * kTile + kTile > nk) {
 #pragma unroll
                     for (int c = 0; c < CPT; ++c) {
                         const int col = col_g0 + c;
-                        if (col >= a.Nk || (diag && col > row_g)) PSET(c, 0.f);
+                        if (col >= nk || (diag && col > row_g)) PSET(c, 0.f);
                     }
                 }
             }
@@ -853,6 +860,7 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     }
     BwdArgs a;
     a.lse2 = lse2; a.delta = delta; a.dq_acc = dq_acc; a.status = p.status_word;
+    a.kv_len = p.kv_lengths;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv; a.nq_pad = nq_pad;
     a.causal = p.causal;
     a.scale = p.scale;

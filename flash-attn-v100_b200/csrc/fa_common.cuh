@@ -38,6 +38,13 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 static inline size_t dtype_bytes(int dtype) { return dtype == FA_B200_F32 ? 4 : 2; }
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Keys batch entry b attends to: its entry of the optional per-batch count array, clamped to [1, Nk].
+__device__ __forceinline__ int kv_len_of(const int32_t* lens, int b, int Nk) {
+    if (!lens) return Nk;
+    const int l = lens[b];
+    return l < 1 ? 1 : (l > Nk ? Nk : l);
+}
+
 // ---- workspace layout (backward) -------------------------------------------
 // [ delta : B*H*nq_pad fp32 | pad to 256 | lse*log2(e) : B*H*nq_pad fp32 (tensor-core family only)
 //   | pad to 256 | dQ sums : B*H*nq_pad*D fp32 (one-kernel tensor-core backward only) ]

@@ -94,6 +94,7 @@ struct FwdArgs {
     int64_t o_sb, o_sn, o_sh;
     float* lse;
     int32_t* status;
+    const int32_t* kv_len;         // optional per-batch key counts
     int B, Nq, Nk, H, Hkv;
     int causal;
     int n_pairs;                   // ceil(Nq / 256)
@@ -126,9 +127,9 @@ __device__ __forceinline__ bool decode_work(const FwdArgs& a, int w, int u, Pair
 }
 
 // key blocks tile t of a pair visits
-__device__ __forceinline__ int num_blocks(const FwdArgs& a, int pair, int t) {
+__device__ __forceinline__ int num_blocks(const FwdArgs& a, int pair, int t, int nk) {
     const int row0 = (pair * 2 + t) * kBlockM;
-    int kv_end = a.Nk;
+    int kv_end = nk;               // keys this batch entry attends to
     if (a.causal && row0 + kBlockM < kv_end) kv_end = row0 + kBlockM;
     return (row0 < a.Nq) ? (kv_end + kBlockN - 1) / kBlockN : 0;
 }
@@ -192,7 +193,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     if (!decode_work(a, w, u, pr)) continue;
                     const int hk = pr.h / group;
                     const int q0 = pr.pair * 2 * kBlockM;
-                    const int n0 = num_blocks(a, pr.pair, 0), n1 = num_blocks(a, pr.pair, 1);
+                    const int nk = kv_len_of(a.kv_len, pr.b, a.Nk);
+                    const int n0 = num_blocks(a, pr.pair, 0, nk), n1 = num_blocks(a, pr.pair, 1, nk);
                     const int nmax = n0 > n1 ? n0 : n1;
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
@@ -289,7 +291,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int u = 0; u < 2 && ok; ++u) {
                     Pair pr;
                     if (!decode_work(a, w, u, pr)) continue;
-                    int nblk[2] = {num_blocks(a, pr.pair, 0), num_blocks(a, pr.pair, 1)};
+                    const int nk = kv_len_of(a.kv_len, pr.b, a.Nk);
+                    int nblk[2] = {num_blocks(a, pr.pair, 0, nk), num_blocks(a, pr.pair, 1, nk)};
                     const int nmax = nblk[0] > nblk[1] ? nblk[0] : nblk[1];
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
@@ -370,7 +373,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             for (int u = 0; u < 2 && ok; ++u) {
                 Pair pr;
                 if (!decode_work(a, w, u, pr)) continue;
-                const int n = num_blocks(a, pr.pair, t);
+                const int nk = kv_len_of(a.kv_len, pr.b, a.Nk);
+                const int n = num_blocks(a, pr.pair, t, nk);
                 if (n == 0) continue;
                 const int tile = pr.pair * 2 + t;
                 const int i = tile * kBlockM + r;                    // global query row
@@ -391,12 +395,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     tmem_wait_ld();
 
                     const int col0 = j * kBlockN;
-                    const bool need_mask = (a.causal && col0 + kBlockN - 1 > tile * kBlockM) || (col0 + kBlockN > a.Nk);
+                    const bool need_mask = (a.causal && col0 + kBlockN - 1 > tile * kBlockM) || (col0 + kBlockN > nk);
                     if (need_mask) {
 #pragma unroll
                         for (int c = 0; c < 128; ++c) {
                             const int col = col0 + c;
-                            if (col >= a.Nk || (a.causal && col > i)) SSET(c, -INFINITY);
+                            if (col >= nk || (a.causal && col > i)) SSET(c, -INFINITY);
                         }
                     }
                     float mx0 = SF(0), mx1 = SF(1), mx2 = SF(2), mx3 = SF(3);
@@ -548,6 +552,7 @@ int launch(const fa_b200_params& p) {
     a.lse = p.lse;
     a.status = p.status_word;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv;
+    a.kv_len = p.kv_lengths;
     a.causal = p.causal;
     a.n_pairs = (p.Nq + 2 * kBlockM - 1) / (2 * kBlockM);
     a.items_per_head = p.causal ? (a.n_pairs + 1) / 2 : a.n_pairs;

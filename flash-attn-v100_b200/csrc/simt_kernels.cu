@@ -32,6 +32,7 @@ struct SimtArgs {
     fa_b200_tensor q, k, v, o, d_o, dq, dk, dv;
     fa_b200_tensor bias;   // fp32 (B, H, Nq, Nk) with broadcast strides; ptr = nullptr: none
     float* d_scores;       // optional dense (B, H, Nq, Nk) gradient of the scores
+    const int32_t* kv_len; // optional per-batch key counts
     float* lse;
     float* delta;
     int B, Nq, Nk, H, Hkv, D;
@@ -86,7 +87,8 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(SimtArgs a) {
 #pragma unroll
         for (int c = 0; c < MAXC; ++c) oacc[r][c] = 0.f;
 
-    int kv_end = a.Nk;
+    const int nk = kv_len_of(a.kv_len, b, a.Nk);      // keys this batch entry attends to
+    int kv_end = nk;
     if (a.causal && m0 + BM < kv_end) kv_end = m0 + BM;
 
     for (int n0 = 0; n0 < kv_end; n0 += BN) {
@@ -118,8 +120,8 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(SimtArgs a) {
             for (int c = 0; c < 4; ++c) {
                 int j = n0 + tx + 16 * c;
                 float s = acc[r][c] * a.scale;
-                if (bias_b && i < a.Nq && j < a.Nk) s += bias_b[(int64_t)i * a.bias.stride_n + j];
-                if (j >= a.Nk || (a.causal && j > i)) s = -INFINITY;
+                if (bias_b && i < a.Nq && j < nk) s += bias_b[(int64_t)i * a.bias.stride_n + j];
+                if (j >= nk || (a.causal && j > i)) s = -INFINITY;
                 Ss[(ty * 4 + r) * SLD + tx + 16 * c] = s;
             }
         }
@@ -241,6 +243,7 @@ __global__ void __launch_bounds__(NT) simt_bwd_kernel(SimtArgs a) {
         for (int c = 0; c < MAXC; ++c) { acc0[r][c] = 0.f; acc1[r][c] = 0.f; }
 
     const int tile = blockIdx.x;
+    const int nk = kv_len_of(a.kv_len, b, a.Nk);      // keys this batch entry attends to
     const int hk = (MODE == 0) ? blockIdx.y : blockIdx.y / group;
     const int h_begin = (MODE == 0) ? hk * group : blockIdx.y;
     const int h_end = (MODE == 0) ? h_begin + group : h_begin + 1;
@@ -268,7 +271,7 @@ __global__ void __launch_bounds__(NT) simt_bwd_kernel(SimtArgs a) {
             it_begin = a.causal ? (tile * BN) / BM : 0;
             it_end = (a.Nq + BM - 1) / BM;
         } else {
-            int kv_end = a.Nk;
+            int kv_end = nk;
             if (a.causal && tile * BM + BM < kv_end) kv_end = tile * BM + BM;
             it_begin = 0;
             it_end = (kv_end + BN - 1) / BN;
@@ -335,7 +338,7 @@ __global__ void __launch_bounds__(NT) simt_bwd_kernel(SimtArgs a) {
                 for (int c = 0; c < 4; ++c) {
                     const int col = tx + 16 * c, j = n0 + col;
                     float p = 0.f, z = 1.f;
-                    bool visible = (i < a.Nq) && (j < a.Nk) && !(a.causal && j > i);
+                    bool visible = (i < a.Nq) && (j < nk) && !(a.causal && j > i);
                     if (visible) {
                         float s = s_acc[r][c] * a.scale;
                         if (bias_b) s += bias_b[(int64_t)i * a.bias.stride_n + j];
@@ -445,7 +448,7 @@ SimtArgs make_args(const fa_b200_params& p, float* delta) {
     SimtArgs a;
     a.q = p.q; a.k = p.k; a.v = p.v; a.o = p.o; a.d_o = p.d_o; a.dq = p.dq; a.dk = p.dk; a.dv = p.dv;
     a.lse = p.lse; a.delta = delta;
-    a.bias = p.bias; a.d_scores = p.d_scores;
+    a.bias = p.bias; a.d_scores = p.d_scores; a.kv_len = p.kv_lengths;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv; a.D = p.D;
     a.causal = p.causal; a.scale = p.scale;
     a.drop_thr = dropout_threshold(p.dropout_p);

@@ -259,6 +259,7 @@ def flash_attention_v100(
     enable_profiling: bool = False,
     fallback_on_error: bool = True,
     validate_inputs: bool = True,
+    key_lengths: Optional[torch.Tensor] = None,
 ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
     """Exact attention on (B, N, H, D) tensors; signature of reference interface.py:199-217.
 
@@ -269,6 +270,9 @@ def flash_attention_v100(
         dropout_p: drop probability of the attention weights (quantised to 1/256)
         bias: additive score bias, (B|1, H|1, Nq|1, Nk): scores = scale * q.k + bias before the causal mask;
             -inf entries mask keys.  Served by the CUDA-core kernels; its gradient is returned
+        key_lengths: (not in the reference) int tensor (B,): batch entry b attends to its first
+            key_lengths[b] keys only (right-padded batches); key blocks beyond are skipped on every
+            kernel family, dK / dV of the padding are zero
         block_size_m, block_size_n, enable_autotuning, optimization_strategy:
             accepted for source compatibility; tiles come from the static table
         return_softmax_lse: also return the (B, H, Nq) fp32 log-sum-exp
@@ -296,10 +300,11 @@ def flash_attention_v100(
 
     if use_multi and len(manager.devices) > 1:
         result = _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, block_size_n,
-                                    enable_autotuning, return_softmax_lse, manager)
+                                    enable_autotuning, return_softmax_lse, manager, key_lengths)
     else:
         result = FlashAttentionV100Function.apply(q, k, v, scale, causal, dropout_p, bias, block_size_m,
-                                                  block_size_n, enable_autotuning, return_softmax_lse)
+                                                  block_size_n, enable_autotuning, return_softmax_lse,
+                                                  False, True, None, True, "balanced", False, 1, 0, key_lengths)
     if profile:
         end.record(torch.cuda.current_stream(q.device))
         end.synchronize()
@@ -308,7 +313,7 @@ def flash_attention_v100(
 
 
 def _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, block_size_n,
-                       enable_autotuning, return_softmax_lse, manager):
+                       enable_autotuning, return_softmax_lse, manager, key_lengths=None):
     """Single-process sharding over manager.devices (reference interface.py:351-434).
 
     Shards are planned over heads or batch; each device gets its slice by an
@@ -345,8 +350,10 @@ def _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, bl
                 if bl.shape[1] > 1:
                     bl = bl[:, shard[2]:shard[3]]
                 bl = bl.to(dev, non_blocking=True)
+            ll = key_lengths[shard[0]:shard[1]].to(dev, non_blocking=True) if key_lengths is not None else None
             res = FlashAttentionV100Function.apply(ql, kl, vl, scale, causal, dropout_p, bl, block_size_m,
-                                                   block_size_n, enable_autotuning, return_softmax_lse)
+                                                   block_size_n, enable_autotuning, return_softmax_lse,
+                                                   False, True, None, True, "balanced", False, 1, 0, ll)
             o_l, lse_l = res if return_softmax_lse else (res, None)
             outs.append((shard, o_l.to(home, non_blocking=True)))
             if lse_l is not None:

@@ -49,7 +49,7 @@ class Params(ctypes.Structure):
         ("variant", ctypes.c_int32), ("device", ctypes.c_int32),
         ("scale", ctypes.c_float), ("dropout_p", ctypes.c_float),
         ("bwd_phases", ctypes.c_int32), ("reserved", ctypes.c_int32),
-        ("bias", Tensor4), ("d_scores", ctypes.c_void_p),
+        ("bias", Tensor4), ("d_scores", ctypes.c_void_p), ("kv_lengths", ctypes.c_void_p),
     ]
 
 

@@ -90,8 +90,12 @@ class EnhancedMultiHeadAttention(nn.Module):
     def forward(self, query: torch.Tensor, key: Optional[torch.Tensor] = None,
                 value: Optional[torch.Tensor] = None, key_padding_mask: Optional[torch.Tensor] = None,
                 attn_mask: Optional[torch.Tensor] = None, need_weights: bool = False,
-                average_attn_weights: bool = True, is_causal: bool = False
+                average_attn_weights: bool = True, is_causal: bool = False,
+                key_lengths: Optional[torch.Tensor] = None
                 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """Reference signature plus key_lengths (B,): for right-padded batches, the number of real keys
+        of each batch entry.  Unlike a key_padding_mask (which becomes a bias and runs on the CUDA-core
+        kernels) it keeps the call on the tensor-core kernels and skips the padding's key blocks."""
         if not self.batch_first:
             query = query.transpose(0, 1)
             key = key.transpose(0, 1) if key is not None else None
@@ -112,7 +116,7 @@ class EnhancedMultiHeadAttention(nn.Module):
         out = flash_attention_v100(q, k, v, causal=is_causal, dropout_p=self.dropout if self.training else 0.0,
                                    bias=bias, optimization_strategy=self.optimization_strategy,
                                    enable_multi_gpu=self.enable_multi_gpu,
-                                   enable_profiling=self.enable_performance_monitoring)
+                                   enable_profiling=self.enable_performance_monitoring, key_lengths=key_lengths)
         out = self.out_proj(out.reshape(batch, seq_q, self.embed_dim))
         if not self.batch_first:
             out = out.transpose(0, 1)

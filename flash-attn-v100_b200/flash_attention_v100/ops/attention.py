@@ -115,6 +115,17 @@ def _bias_operand(bias: Optional[torch.Tensor]):
     return r, bf
 
 
+def _lengths_operand(key_lengths: Optional[torch.Tensor], q: torch.Tensor):
+    """(device pointer or None, keep-alive tensor) for per-batch key counts: int32, one per batch entry,
+    on q's device."""
+    if key_lengths is None:
+        return None, None
+    if key_lengths.dim() != 1 or key_lengths.shape[0] != q.shape[0]:
+        raise ValueError(f"key_lengths must have shape ({q.shape[0]},), got {tuple(key_lengths.shape)}")
+    kl = key_lengths.detach().to(device=q.device, dtype=torch.int32).contiguous()
+    return kl.data_ptr(), kl
+
+
 def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset) -> _cabi.Params:
     p = _cabi.Params()
     p.struct_bytes = ctypes.sizeof(_cabi.Params)
@@ -134,7 +145,8 @@ def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset) -> _ca
     return p
 
 
-def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None, bias=None):
+def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None, bias=None,
+                   key_lengths=None):
     """o, lse <- fa_b200_fwd.  Counterpart of flash_attention_forward_triton_enhanced
     (kernels/forward_kernel.py:246-387); returns (o, lse).  `out=(o, lse)` writes into
     caller-owned buffers (o like q, lse (B, H, Nq) fp32 contiguous) instead of allocating."""
@@ -145,13 +157,14 @@ def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=
         lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
     p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset)
     p.bias, _keep = _bias_operand(bias)        # scores = scale * q.k + bias (CUDA-core kernels)
+    p.kv_lengths, _keep_len = _lengths_operand(key_lengths, q)
     rc = _cabi.load().fa_b200_fwd(ctypes.byref(p))
     _cabi.raise_for_status(rc, "fa_b200_fwd")
     return o, lse
 
 
 def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None,
-                    workspace=None, bias=None, d_scores=None):
+                    workspace=None, bias=None, d_scores=None, key_lengths=None):
     """dq, dk, dv <- fa_b200_bwd.  Counterpart of
     flash_attention_backward_triton_enhanced (kernels/backward_kernel.py:208-318).
     `out=(dq, dk, dv)` and `workspace` (uint8, at least fa_b200_bwd_workspace_bytes)
@@ -166,6 +179,7 @@ def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, 
     p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset)
     p.d_o, p.dq, p.dk, p.dv = _tensor4(d_o), _tensor4(dq), _tensor4(dk), _tensor4(dv)
     p.bias, _keep = _bias_operand(bias)
+    p.kv_lengths, _keep_len = _lengths_operand(key_lengths, q)
     if d_scores is not None:
         # dense (B, H, Nq, Nk) fp32, zero-filled by the caller: receives d loss / d scores
         if d_scores.dtype != torch.float32 or not d_scores.is_contiguous() or \
@@ -197,7 +211,7 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
                 enable_gradient_checkpointing: bool = False, enable_mixed_precision: bool = True,
                 num_checkpoints: Optional[int] = None, memory_efficient: bool = True,
                 performance_mode: str = "balanced", enable_multi_gpu: bool = False,
-                world_size: int = 1, rank: int = 0
+                world_size: int = 1, rank: int = 0, key_lengths: Optional[torch.Tensor] = None
                 ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
         # block sizes, autotuning, checkpointing, mixed precision and the
         # multi-GPU arguments are accepted for source compatibility: tiles come
@@ -207,8 +221,11 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
         seed = offset = 0
         if dropout_p > 0.0:
             seed, offset = _next_dropout_stream()
-        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias)
+        # key_lengths (one int per batch entry, after the reference's 19 parameters): batch entry b
+        # attends to its first key_lengths[b] keys only
+        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias, key_lengths=key_lengths)
         ctx.save_for_backward(q, k, v, o, lse, *([bias] if bias is not None else []))
+        ctx.key_lengths = key_lengths
         ctx.scale, ctx.causal, ctx.dropout_p = scale, bool(causal), float(dropout_p)
         ctx.seed, ctx.offset = seed, offset
         ctx.return_softmax_lse = bool(return_softmax_lse)
@@ -228,13 +245,14 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
             d_scores = torch.zeros(q.shape[0], q.shape[2], q.shape[1], k.shape[1], dtype=torch.float32,
                                    device=q.device)
         dq, dk, dv = launch_backward(grad_output, q, k, v, o, lse, ctx.scale, ctx.causal,
-                                     ctx.dropout_p, ctx.seed, ctx.offset, bias=bias, d_scores=d_scores)
+                                     ctx.dropout_p, ctx.seed, ctx.offset, bias=bias, d_scores=d_scores,
+                                     key_lengths=ctx.key_lengths)
         if d_scores is not None:
             dims = [i for i in range(4) if bias.shape[i] == 1 and d_scores.shape[i] != 1]
             grad_bias = (d_scores.sum(dim=dims, keepdim=True) if dims else d_scores).to(bias.dtype)
         return (dq if ctx.needs_input_grad[0] else None,
                 dk if ctx.needs_input_grad[1] else None,
-                dv if ctx.needs_input_grad[2] else None, None, None, None, grad_bias) + (None,) * 12
+                dv if ctx.needs_input_grad[2] else None, None, None, None, grad_bias) + (None,) * 13
 
 
 def flash_attention_forward_enhanced(q, k, v, scale: Optional[float] = None, causal: bool = False,
@@ -248,7 +266,8 @@ def flash_attention_forward_enhanced(q, k, v, scale: Optional[float] = None, cau
     if dropout_p > 0.0:
         seed, offset = kwargs.get("dropout_stream") or _next_dropout_stream()
     with torch.no_grad():
-        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias)
+        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias,
+                                key_lengths=kwargs.get("key_lengths"))
     return (o, lse) if kwargs.get("return_softmax_lse", False) else o
 
 
@@ -265,7 +284,8 @@ def flash_attention_backward_enhanced(grad_output, q, k, v, output, lse, max_val
     with torch.no_grad():
         return launch_backward(grad_output, q, k, v, _last_dim_contiguous(output), lse.contiguous(),
                                scale, causal, kwargs.get("dropout_p", 0.0), seed, offset,
-                               bias=kwargs.get("bias"), d_scores=kwargs.get("d_scores"))
+                               bias=kwargs.get("bias"), d_scores=kwargs.get("d_scores"),
+                               key_lengths=kwargs.get("key_lengths"))
 
 
 def compare_with_pytorch_attention_enhanced(q, k, v, causal: bool = False,

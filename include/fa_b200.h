@@ -120,6 +120,12 @@ typedef struct fa_b200_params {
        d(loss)/d(scores) = P o (dP o Z - delta); the caller sums it over the bias' broadcast
        dimensions to get grad_bias.  NULL: not produced. */
     float*         d_scores;
+    /* Optional per-batch key counts (device pointer to B int32; NULL: every batch entry has Nk keys):
+       batch entry b attends to keys [0, kv_lengths[b]) only, the rest of its K/V rows are padding.
+       Values are clamped to [1, Nk].  dK and dV rows of the padding are written as zeros.  No counterpart
+       in the reference, which expresses padding as a dense -inf bias (examples/basic_usage.py:243-248);
+       here whole key blocks beyond the count are skipped, on every kernel family. */
+    const int32_t* kv_lengths;
 } fa_b200_params;
 
 /* Static tile choice for a (D, dtype, causal) key; replaces the reference's

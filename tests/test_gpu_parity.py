@@ -400,3 +400,38 @@ def test_key_padding_mask_as_bias(device):
     o = fa.flash_attention_v100(q, k, v, bias=mask, enable_multi_gpu=False)
     o_ref = fa.flash_attention_v100(q, k[:, :keep].contiguous(), v[:, :keep].contiguous(), enable_multi_gpu=False)
     assert rel_l2(o, o_ref) < 2e-3
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 64), (torch.float32, 32)],
+                         ids=["bf16-d128", "fp16-d64", "fp32-d32"])
+@pytest.mark.parametrize("causal", [False, True], ids=["full", "causal"])
+def test_key_lengths_equal_a_padding_mask(device, dtype, D, causal):
+    """Per-batch key counts: the same result as the oracle with a -inf key-padding bias, zero dK / dV
+    for the padding, on every kernel family (whole key blocks beyond the count are skipped)."""
+    B, N, H = 3, 333, 2
+    lengths = torch.tensor([333, 130, 1], dtype=torch.int32)
+    q, k, v, d_o = (_rand((B, N, H, D), dtype, 70 + i) for i in range(4))
+    pad = torch.zeros(B, 1, 1, N)
+    for b in range(B):
+        pad[b, ..., int(lengths[b]):] = float("-inf")
+    ro, rlse, rdq, rdk, rdv = ao.attention_forward_backward(q.float(), k.float(), v.float(), d_o.float(),
+                                                            causal=causal, bias=pad)
+    qd, kd, vd, gd = (t.to(device) for t in (q, k, v, d_o))
+    for variant in _variants(dtype, D):
+        tol = tolerance(dtype, variant, D)
+        with kernel_variant(variant):
+            o, lse = launch_forward(qd, kd, vd, D ** -0.5, causal, key_lengths=lengths.to(device))
+            dq, dk, dv = launch_backward(gd, qd, kd, vd, o, lse, D ** -0.5, causal, key_lengths=lengths.to(device))
+        _check("O", o, ro, tol)
+        _check("LSE", lse, rlse, tol)
+        _check("dQ", dq, rdq, tol)
+        _check("dK", dk, rdk, tol)
+        _check("dV", dv, rdv, tol)
+        for b in range(B):
+            assert (dk[b, int(lengths[b]):] == 0).all() and (dv[b, int(lengths[b]):] == 0).all(), variant
+    # the public entry point and autograd carry the counts too
+    q2, k2, v2 = (t.clone().requires_grad_(True) for t in (qd, kd, vd))
+    o2 = fa.flash_attention_v100(q2, k2, v2, causal=causal, key_lengths=lengths.to(device), enable_multi_gpu=False)
+    o2.backward(gd)
+    _check("O (autograd)", o2, ro, tolerance(dtype))
+    _check("dK (autograd)", k2.grad, rdk, tolerance(dtype))
