@@ -147,7 +147,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     constexpr bool KS = (MODE != 1);        // key-stationary: K, V stay, query tiles stream
     constexpr bool FUSED = (MODE == 2);     // key-stationary and dQ too
     constexpr int UST = Cfg::kUStages, WST = Cfg::kWStages;
-    constexpr bool kMoveRegisters = (D == 128);
     constexpr int TILE = Cfg::kTileBytes;
 
     extern __shared__ uint8_t smem_raw[];
@@ -241,11 +240,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t tDq = kDqAliasesT2 ? tT2 : tmem + 448u;
 
     if (warp >= kMmaWarp) {
-      // Register split.  With the launch allocation of 96 per thread nobody spills; moving 8 registers
-      // per thread from these warps (left with 64: the key-stationary issuer then spills 40 bytes) to the
-      // elementwise ones measured 1.4 % faster over the whole backward at D = 128 and 7 % slower at
-      // D = 64, so only D = 128 does it.
-      if (kMoveRegisters) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+      // No setmaxnreg in this kernel: with the launch allocation of 96 registers per thread no role
+      // spills; moving registers from these warps to the elementwise ones (104 / 64, 104 / 40) made one
+      // side or the other spill and measured the same or slower.
       if (warp == kTmaWarp) {
         // ---------------------------------------------------------------- TMA producer
         if (elect_one()) {
@@ -458,7 +455,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         __syncwarp();
       }
     } else {
-        if (kMoveRegisters) asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
         // ---------------------------------------------------------------- P / dS and epilogue
         constexpr int NLD = CPT / 32;                          // 32-column TMEM loads per thread and phase
         const int wg = warp >> 2;                              // which CPT-column slice
@@ -535,13 +531,148 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     ok = mbar_wait(&bars[Cfg::kMask], (uint32_t)it & 1u, abort_flag);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
-                    const int jw = r >> 4, jbit = r & 15;
+                    if (FUSED) {      // (the fragment-layout phases read their keep bits from mbuf themselves)
+                        const int jw = r >> 4, jbit = r & 15;
 #pragma unroll
-                    for (int c = 0; c < CPT; ++c)
-                        kb[c >> 5] |= (((uint32_t)mbuf[(cb + c) * 8 + jw] >> jbit) & 1u) << (c & 31);
+                        for (int c = 0; c < CPT; ++c)
+                            kb[c >> 5] |= (((uint32_t)mbuf[(cb + c) * 8 + jw] >> jbit) & 1u) << (c & 31);
+                    }
                 }
             }
 
+            if constexpr (MODE == 0) {
+            // ---- dK/dV kernel, fragment layout: a thread holds 4 rows x 8 columns of its warp's
+            // 32 x 32 block (rows lane/4 + {0, 8, 16, 24}, columns 8j + 2(lane%4) + {0, 1}, j = 0..3) instead
+            // of 1 row x 32 columns, so it needs the -lse / -delta values of 8 query columns, four 8-byte
+            // loads that one wavefront serves, instead of 32 values through eight broadcast 16-byte loads.
+            ok = mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag);
+            if (ok) ok = mbar_wait(&bars[Cfg::kVFull + (it & 1)], (uint32_t)(it >> 1) & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int lq = lane & 3, lr = lane >> 2;
+            const int rbase = (warp & 3) * 32 + lr;                 // my first row inside the tile
+            const uint32_t t_lo = lane_off + cb, t_hi = lane_off + (16u << 16) + cb;
+            // element (h, j, k, e): row rbase + 16h + 8k, column 8j + 2lq + e, register [h][4j + 2k + e]
+            uint32_t pf[2][16];
+            tmem_ld_16x256b_x4(tT1 + t_lo, pf[0]);
+            tmem_ld_16x256b_x4(tT1 + t_hi, pf[1]);
+            tmem_wait_ld();
+            uint32_t kbits = 0xFFFFFFFFu;                           // keep bit of element (h, j, k, e): bit 16h + 4j + 2k + e
+            if (drop) {
+                const uint16_t* mbuf = sMask + (it & 1) * (128 * 8);
+                kbits = 0u;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int k = 0; k < 2; ++k)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int row = rbase + 16 * h + 8 * k, col = cb + 8 * j + 2 * lq + e;
+                                kbits |= (((uint32_t)mbuf[col * 8 + (row >> 4)] >> (row & 15)) & 1u) << (16 * h + 4 * j + 2 * k + e);
+                            }
+            }
+            const uint64_t sc2 = f2_pack(a.scale_log2, a.scale_log2);
+            const bool diag = a.causal && strm_tile == tile;       // key row > query column is hidden
+            const bool tail = tile * kTile + kTile > nk;            // the tile holds padding keys
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                uint32_t pk[2][4];                                  // [h][2j' + k], j' = j - 2hf
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj) {
+                    const int j = 2 * hf + jj;
+                    const uint64_t L = *reinterpret_cast<const uint64_t*>(lse_s + cb + 8 * j + 2 * lq);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+                            const int i0 = 4 * j + 2 * k;
+                            float x0, x1;
+                            f2_unpack(f2_fma(f2_pack(__uint_as_float(pf[h][i0]), __uint_as_float(pf[h][i0 + 1])), sc2, L), x0, x1);
+                            float p0 = ex2(x0), p1 = ex2(x1);
+                            const int row_k = tile * kTile + rbase + 16 * h + 8 * k;
+                            if (diag) {
+                                const int col = col_g0 + 8 * j + 2 * lq;
+                                if (row_k > col) p0 = 0.f;
+                                if (row_k > col + 1) p1 = 0.f;
+                            }
+                            if (tail && row_k >= nk) { p0 = 0.f; p1 = 0.f; }
+                            pf[h][i0] = __float_as_uint(p0);
+                            pf[h][i0 + 1] = __float_as_uint(p1);
+                            float z0 = p0, z1 = p1;
+                            if (drop) {
+                                const uint32_t kw = kbits >> (16 * h + i0);
+                                if (!(kw & 1u)) z0 = 0.f;
+                                if (!(kw & 2u)) z1 = 0.f;
+                            }
+                            pk[h][2 * jj + k] = pack2<BF16>(z0, z1);
+                        }
+                }
+                if (hf == 1) {
+                    tmem_wait_st();                                 // the first half's stores were issued a half-phase ago
+                    tc_fence_before_sync();
+                    mbar_arrive_warp(&bars[Cfg::kPHalf]);
+                }
+                tmem_st_16x128b_x2(tT1 + t_lo + hf * 8, pk[0]);
+                tmem_st_16x128b_x2(tT1 + t_hi + hf * 8, pk[1]);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive_warp(&bars[Cfg::kPReady]);
+
+            ok = mbar_wait(&bars[Cfg::kT2Full], (uint32_t)it & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            {
+                uint32_t df[2][16];
+                tmem_ld_16x256b_x4(tT2 + t_lo, df[0]);
+                tmem_ld_16x256b_x4(tT2 + t_hi, df[1]);
+                tmem_wait_ld();
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    uint32_t pk[2][4];
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {
+                        const int j = 2 * hf + jj;
+                        const uint64_t nd = *reinterpret_cast<const uint64_t*>(del_s + cb + 8 * j + 2 * lq);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {
+                                const int i0 = 4 * j + 2 * k;
+                                const uint64_t dp = f2_pack(__uint_as_float(df[h][i0]), __uint_as_float(df[h][i0 + 1]));
+                                uint64_t tt;
+                                if (drop) {
+                                    const uint32_t kw = kbits >> (16 * h + i0);
+                                    tt = f2_fma(dp, f2_pack((kw & 1u) ? a.inv_keep : 0.f, (kw & 2u) ? a.inv_keep : 0.f), nd);
+                                } else {
+                                    tt = f2_add(dp, nd);
+                                }
+                                float d0, d1;
+                                f2_unpack(f2_mul(f2_pack(__uint_as_float(pf[h][i0]), __uint_as_float(pf[h][i0 + 1])), tt), d0, d1);
+                                pk[h][2 * jj + k] = pack2<BF16>(d0, d1);
+                            }
+                    }
+                    if (hf == 1) {
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        mbar_arrive_warp(&bars[Cfg::kDsHalf]);
+                    }
+                    tmem_st_16x128b_x2(tT2 + t_lo + hf * 8, pk[0]);
+                    tmem_st_16x128b_x2(tT2 + t_hi + hf * 8, pk[1]);
+                }
+                tmem_wait_st();
+            }
+            tc_fence_before_sync();
+            mbar_arrive_warp(&bars[Cfg::kDsReady]);
+            } else {
+            // ---- one row and 32 columns per thread: the query-stationary kernel (lse and delta are
+            // per-thread scalars there), and the one-kernel backward, whose dS^T tile for the dQ MMA is
+            // written with 16-byte stores from this layout (with the fragment layout above it measured
+            // 5-10 % slower)
             // ---- phase A: P from T1
             ok = (KS) ? mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag)
                              : mbar_wait(&bars[Cfg::kT1Full + (it & 1)], (uint32_t)(it >> 1) & 1u, abort_flag);
@@ -700,6 +831,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #undef PSET
             tc_fence_before_sync();
             mbar_arrive_warp(&bars[Cfg::kDsReady]);
+            }
             if (KS) mbar_arrive_warp(&bars[Cfg::kVEmpty + (it & 1)]);      // this step's lse / delta rows are read
             prev_tile = strm_tile; prev_head = head_q;
             if (++qi == n_per_head) { qi = 0; ++hg; }
