@@ -591,17 +591,34 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             const int i0 = 4 * j + 2 * k;
                             float x0, x1;
                             f2_unpack(f2_fma(f2_pack(__uint_as_float(pf[h][i0]), __uint_as_float(pf[h][i0 + 1])), sc2, L), x0, x1);
-                            float p0 = ex2(x0), p1 = ex2(x1);
-                            const int row_k = tile * kTile + rbase + 16 * h + 8 * k;
-                            if (diag) {
+                            pf[h][i0] = __float_as_uint(ex2(x0));
+                            pf[h][i0 + 1] = __float_as_uint(ex2(x1));
+                        }
+                }
+                if (diag || tail) {
+                    // one branch for the whole half: the diagonal tile and a tile with padding keys are rare
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {
+                                const int j = 2 * hf + jj, i0 = 4 * j + 2 * k;
+                                const int row_k = tile * kTile + rbase + 16 * h + 8 * k;
                                 const int col = col_g0 + 8 * j + 2 * lq;
-                                if (row_k > col) p0 = 0.f;
-                                if (row_k > col + 1) p1 = 0.f;
+                                const bool dead = tail && row_k >= nk;
+                                if (dead || (diag && row_k > col)) pf[h][i0] = 0u;
+                                if (dead || (diag && row_k > col + 1)) pf[h][i0 + 1] = 0u;
                             }
-                            if (tail && row_k >= nk) { p0 = 0.f; p1 = 0.f; }
-                            pf[h][i0] = __float_as_uint(p0);
-                            pf[h][i0 + 1] = __float_as_uint(p1);
-                            float z0 = p0, z1 = p1;
+                }
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+                            const int i0 = 4 * (2 * hf + jj) + 2 * k;
+                            float z0 = __uint_as_float(pf[h][i0]), z1 = __uint_as_float(pf[h][i0 + 1]);
                             if (drop) {
                                 const uint32_t kw = kbits >> (16 * h + i0);
                                 if (!(kw & 1u)) z0 = 0.f;
@@ -609,7 +626,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             }
                             pk[h][2 * jj + k] = pack2<BF16>(z0, z1);
                         }
-                }
                 if (hf == 1) {
                     tmem_wait_st();                                 // the first half's stores were issued a half-phase ago
                     tc_fence_before_sync();
