@@ -117,7 +117,7 @@ def measured_peak():
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
 # profiles/ncu_full_fwd_bwd_cfg3_batch1.md: measured at batch 1 of the default workload and scaled by
 # the batch (traffic is proportional to the number of independent (batch, head) columns).
-NCU_DRAM_BYTES_PER_BATCH = {"fwd": 112.6e6, "bwd_dkdv": 177.1e6, "bwd_dq": 155.1e6}
+NCU_DRAM_BYTES_PER_BATCH = {"fwd": 111.5e6, "bwd_dkdv": 175.9e6, "bwd_dq": 155.3e6}
 
 
 def ncu_traffic(kernel: str, w):
