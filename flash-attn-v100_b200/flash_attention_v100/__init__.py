@@ -30,6 +30,7 @@ from .ops.attention import (
 )
 from .ops.host_pipeline import HostAttentionStep
 from .modules import EnhancedMultiHeadAttention
+from .ops.sequence_parallel import flash_attention_v100_sequence_parallel
 
 __version__ = "0.1.0"
 __author__ = "flash_attention_v100 B200 build"
@@ -63,4 +64,5 @@ __all__ = [
     "FlashAttentionV100Manager", "get_flash_attention_manager", "flash_attention_performance_mode",
     "flash_attention_memory_mode", "get_enhanced_config", "plan_shards", "set_dropout_seed",
     "kernel_variant", "HostAttentionStep", "EnhancedMultiHeadAttention",
+    "flash_attention_v100_sequence_parallel",
 ]

@@ -24,7 +24,7 @@ FA_OK, FA_EINVAL, FA_EUNSUPPORTED, FA_EALIGN, FA_EWORKSPACE, FA_ECUDA, FA_ETIMEO
 EXPORTS = (
     "fa_b200_fwd", "fa_b200_bwd", "fa_b200_bwd_static", "fa_b200_bwd_workspace_bytes", "fa_b200_tile_config",
     "fa_b200_dropout_mask_host", "fa_b200_dropout_mask_device", "fa_b200_dropout_effective_p",
-    "fa_b200_philox4x32_10", "fa_b200_strerror", "fa_b200_last_error", "fa_b200_version",
+    "fa_b200_philox4x32_10", "fa_b200_strerror", "fa_b200_last_error", "fa_b200_version", "fa_b200_combine",
 )
 
 
@@ -50,6 +50,17 @@ class Params(ctypes.Structure):
         ("scale", ctypes.c_float), ("dropout_p", ctypes.c_float),
         ("bwd_phases", ctypes.c_int32), ("reserved", ctypes.c_int32),
         ("bias", Tensor4), ("d_scores", ctypes.c_void_p), ("kv_lengths", ctypes.c_void_p),
+    ]
+
+
+class CombineParams(ctypes.Structure):
+    _fields_ = [
+        ("struct_bytes", ctypes.c_size_t),
+        ("acc", ctypes.c_void_p), ("lse_acc", ctypes.c_void_p),
+        ("part", Tensor4), ("lse_part", ctypes.c_void_p), ("out", Tensor4),
+        ("B", ctypes.c_int32), ("N", ctypes.c_int32), ("H", ctypes.c_int32), ("D", ctypes.c_int32),
+        ("dtype", ctypes.c_int32), ("first", ctypes.c_int32), ("device", ctypes.c_int32),
+        ("reserved", ctypes.c_int32), ("stream", ctypes.c_void_p),
     ]
 
 
@@ -93,6 +104,8 @@ def load():
         lib.fa_b200_bwd_static.restype = ctypes.c_int
         lib.fa_b200_bwd_workspace_bytes.argtypes = [pp]
         lib.fa_b200_bwd_workspace_bytes.restype = ctypes.c_size_t
+        lib.fa_b200_combine.argtypes = [ctypes.POINTER(CombineParams)]
+        lib.fa_b200_combine.restype = ctypes.c_int
         lib.fa_b200_tile_config.argtypes = [ctypes.c_int] * 4 + [ctypes.POINTER(Tile)]
         lib.fa_b200_tile_config.restype = ctypes.c_int
         lib.fa_b200_dropout_mask_host.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float] + \

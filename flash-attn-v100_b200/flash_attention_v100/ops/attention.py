@@ -200,6 +200,38 @@ def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, 
     return dq, dk, dv
 
 
+def launch_combine(acc, part=None, lse_acc=None, lse_part=None, out=None, first=False):
+    """fa_b200_combine: fold one block's partial result into the fp32 running total `acc` ((B, N, H, D)
+    contiguous).  With lse_acc / lse_part ((B, H, N) fp32) the two are weighted by their log-sum-exps
+    (attention outputs); without, they are added (gradients).  `first`: acc holds nothing yet.
+    `out`: also write the new total there in out's dtype.  `part=None`: only that conversion."""
+    like = part if part is not None else out
+    if like is None:
+        raise ValueError("launch_combine needs a partial, an output, or both")
+    if acc.dtype != torch.float32 or not acc.is_contiguous() or acc.shape != like.shape:
+        raise ValueError("acc must be a contiguous fp32 tensor of the partial's shape")
+    if part is not None and out is not None and part.dtype != out.dtype:
+        raise ValueError("part and out must have the same dtype")
+    for t in (lse_acc, lse_part):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()
+                              or tuple(t.shape) != (acc.shape[0], acc.shape[2], acc.shape[1])):
+            raise ValueError("log-sum-exps must be contiguous fp32 (B, H, N) tensors")
+    p = _cabi.CombineParams()
+    p.struct_bytes = ctypes.sizeof(_cabi.CombineParams)
+    p.acc = acc.data_ptr()
+    p.lse_acc = lse_acc.data_ptr() if lse_acc is not None else None
+    p.lse_part = lse_part.data_ptr() if lse_part is not None else None
+    p.part = _tensor4(_last_dim_contiguous(part)) if part is not None else _cabi.Tensor4()
+    p.out = _tensor4(out) if out is not None else _cabi.Tensor4()
+    p.B, p.N, p.H, p.D = acc.shape
+    p.dtype = dtype_enum(like.dtype)
+    p.first = int(bool(first))
+    p.device = acc.device.index if acc.device.index is not None else torch.cuda.current_device()
+    p.stream = torch.cuda.current_stream(acc.device).cuda_stream or None
+    rc = _cabi.load().fa_b200_combine(ctypes.byref(p))
+    _cabi.raise_for_status(rc, "fa_b200_combine")
+
+
 class EnhancedFlashAttentionV100Function(torch.autograd.Function):
     """Attention as an autograd op; parameter list of reference ops/attention.py:50-72."""
 

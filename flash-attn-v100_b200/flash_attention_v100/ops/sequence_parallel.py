@@ -1,0 +1,214 @@
+"""Sequence-parallel (ring) attention: every rank holds one slice of the sequence.
+
+The reference names this strategy but does not implement it: its
+_execute_sequence_parallel warns and runs on one GPU (interface.py:437-450;
+the strategy table is config.py:153-157).  Here rank r keeps its queries
+q_r (B, n, H, D) and the key/value blocks travel around the ring
+r -> r + 1: at step t rank r holds block (r - t) mod G, runs one ordinary
+forward (or backward) call on (q_r, block) and folds the result into a running
+total with fa_b200_combine:
+
+    forward   O_r, LSE_r = merge over blocks of (O_part, LSE_part)
+    backward  dQ_r = sum over blocks of dQ_part;  dK_b, dV_b = sum over ranks,
+              accumulated in fp32 buffers that travel with their block and are
+              back home after G hops
+
+The block calls use the final O_r and LSE_r (P = exp(S - LSE) and
+delta = rowsum(dO * O) are then those of the whole row), so the backward needs
+no second softmax pass.  Under a causal mask block b is hidden from rank r when
+b > r, takes the diagonal mask when b == r and none when b < r; hidden blocks
+are neither computed nor sent on.  The sequence is split in contiguous slices,
+so under a causal mask rank r computes r + 1 of the G blocks.
+
+The next block's transfer is posted before the current block's kernels are
+launched, into the other half of a double buffer in this GPU's own memory:
+kernels only ever read local memory.  Every transfer is a batch of one send
+and one receive, so the ring cannot deadlock on a single communication stream.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import attention as _ops
+
+
+def ring_schedule(rank: int, world: int, causal: bool) -> List[Tuple[int, str]]:
+    """[(block, mode)] for steps 0 .. world - 1 of `rank`; mode is 'full', 'causal' or 'skip'."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside a ring of {world}")
+    steps = []
+    for t in range(world):
+        block = (rank - t) % world
+        if not causal:
+            mode = "full"
+        elif block == rank:
+            mode = "causal"
+        else:
+            mode = "full" if block < rank else "skip"
+        steps.append((block, mode))
+    return steps
+
+
+def kv_transfer(rank: int, world: int, causal: bool, step: int) -> Tuple[bool, bool]:
+    """(send, receive): does `rank` pass its current block on after `step`, and does it get one?
+    Without a mask every block visits every rank.  Under a causal mask block b is only of use to
+    ranks above b, so it stops at the last rank and blocks that wrapped around are never sent."""
+    if step >= world - 1:
+        return False, False
+    if not causal:
+        return True, True
+    send = rank - step >= 0 and rank + 1 < world
+    recv = rank >= 1 and rank - 1 - step >= 0
+    return send, recv
+
+
+class DistributedRing:
+    """The ring over a torch.distributed process group (NCCL on GPUs, gloo on CPU)."""
+
+    def __init__(self, group=None):
+        if not (dist.is_available() and dist.is_initialized()):
+            raise RuntimeError("sequence-parallel attention needs an initialised torch.distributed")
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        to_global = (lambda r: r) if group is None else (lambda r: dist.get_global_rank(group, r))
+        self.next = to_global((self.rank + 1) % self.world)
+        self.prev = to_global((self.rank - 1) % self.world)
+
+    def exchange(self, send: Optional[torch.Tensor], recv: Optional[torch.Tensor]):
+        """Post `send` to the next rank and `recv` from the previous one as one batch."""
+        if self.world == 1:                      # a ring of one: the message goes to this rank itself
+            if send is not None and recv is not None:
+                recv.copy_(send)
+            return []
+        ops = []
+        if send is not None:
+            ops.append(dist.P2POp(dist.isend, send, self.next, self.group))
+        if recv is not None:
+            ops.append(dist.P2POp(dist.irecv, recv, self.prev, self.group))
+        return dist.batch_isend_irecv(ops) if ops else []
+
+    @staticmethod
+    def wait(pending) -> None:
+        for req in pending:
+            req.wait()
+
+
+class CudaBlockKernels:
+    """The per-block work through the C ABI (fa_b200_fwd, fa_b200_bwd, fa_b200_combine)."""
+
+    @staticmethod
+    def forward_block(q, k, v, scale, causal):
+        return _ops.launch_forward(q, k, v, scale, causal)
+
+    @staticmethod
+    def backward_block(d_o, q, k, v, o, lse, scale, causal):
+        return _ops.launch_backward(d_o, q, k, v, o, lse, scale, causal)
+
+    combine = staticmethod(_ops.launch_combine)
+
+
+def ring_forward(q, k, v, scale: float, causal: bool, ring, kernels=CudaBlockKernels):
+    """(o, lse) of this rank's queries against the keys of every rank."""
+    rank, world = ring.rank, ring.world
+    sched = ring_schedule(rank, world, causal)
+    last = max(t for t, (_, mode) in enumerate(sched) if mode != "skip")
+    B, n, H, D = q.shape
+    kv = [torch.stack((k, v)), None]                      # (2, B, n, Hkv, D): one message per hop
+    kv[1] = torch.empty_like(kv[0])
+    acc = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    lse = torch.empty(B, H, n, dtype=torch.float32, device=q.device)
+    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    for t, (_, mode) in enumerate(sched):
+        cur, nxt = kv[t % 2], kv[(t + 1) % 2]
+        send, recv = kv_transfer(rank, world, causal, t)
+        pending = ring.exchange(cur if send else None, nxt if recv else None)
+        if mode != "skip":
+            o_part, lse_part = kernels.forward_block(q, cur[0], cur[1], scale, mode == "causal")
+            kernels.combine(acc, o_part, lse, lse_part, out=o if t == last else None, first=(t == 0))
+        ring.wait(pending)
+    return o, lse
+
+
+def ring_backward(d_o, q, k, v, o, lse, scale: float, causal: bool, ring, kernels=CudaBlockKernels):
+    """(dq, dk, dv) of this rank's slices; o and lse are ring_forward's results."""
+    rank, world = ring.rank, ring.world
+    sched = ring_schedule(rank, world, causal)
+    last = max(t for t, (_, mode) in enumerate(sched) if mode != "skip")
+    kv = [torch.stack((k, v)), None]
+    kv[1] = torch.empty_like(kv[0])
+    # fp32 totals of dK and dV of the block this rank holds: they travel with the block
+    dkv = [torch.empty(kv[0].shape, dtype=torch.float32, device=q.device) for _ in range(2)]
+    dq_acc = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    dq = torch.empty_like(q)
+    coming = []                                            # the transfer that fills dkv[t % 2]
+    for t, (_, mode) in enumerate(sched):
+        cur, nxt = kv[t % 2], kv[(t + 1) % 2]
+        send, recv = kv_transfer(rank, world, causal, t)
+        pending = ring.exchange(cur if send else None, nxt if recv else None)
+        if mode != "skip":
+            dq_p, dk_p, dv_p = kernels.backward_block(d_o, q, cur[0], cur[1], o, lse, scale, mode == "causal")
+            kernels.combine(dq_acc, dq_p, out=dq if t == last else None, first=(t == 0))
+        ring.wait(coming)
+        if mode != "skip":
+            kernels.combine(dkv[t % 2][0], dk_p, first=(t == 0))
+            kernels.combine(dkv[t % 2][1], dv_p, first=(t == 0))
+        coming = ring.exchange(dkv[t % 2], dkv[(t + 1) % 2])   # after the last step: the way home
+        ring.wait(pending)
+    ring.wait(coming)
+    home = dkv[world % 2]
+    dk, dv = torch.empty_like(k), torch.empty_like(v)
+    kernels.combine(home[0], None, out=dk)
+    kernels.combine(home[1], None, out=dv)
+    return dq, dk, dv
+
+
+class RingAttentionFunction(torch.autograd.Function):
+    """autograd wrapper: apply(q, k, v, scale, causal, ring, kernels) -> (o, lse)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, causal, ring, kernels):
+        o, lse = ring_forward(q, k, v, scale, causal, ring, kernels)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.scale, ctx.causal, ctx.ring, ctx.kernels = scale, causal, ring, kernels
+        ctx.mark_non_differentiable(lse)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, grad_o, grad_lse=None):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = ring_backward(grad_o, q, k, v, o, lse, ctx.scale, ctx.causal, ctx.ring, ctx.kernels)
+        return dq, dk, dv, None, None, None, None
+
+
+def flash_attention_v100_sequence_parallel(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                                           causal: bool = False, scale: Optional[float] = None,
+                                           group=None, return_softmax_lse: bool = False,
+                                           ring=None, kernels=None):
+    """Attention over a sequence that is split across the ranks of `group`.
+
+    q, k, v are this rank's slices, (B, n, H, D) / (B, n, Hkv, D), the same n on every rank; rank r
+    holds positions [r n, (r + 1) n).  Returns this rank's slice of the output (and of the
+    log-sum-exp, (B, H, n) fp32, with return_softmax_lse).  Differentiable: the backward is a second
+    trip around the ring.  Every rank of the group must make the call.  Dropout and bias are not
+    offered on this path."""
+    if q.dim() != 4 or k.shape != v.shape or q.shape[0] != k.shape[0] or q.shape[3] != k.shape[3]:
+        raise ValueError("expected q (B, n, H, D) and k, v (B, n, Hkv, D)")
+    if q.shape[1] != k.shape[1]:
+        raise ValueError("sequence-parallel attention splits one sequence: q and k must have the same length")
+    if ring is None:
+        ring = DistributedRing(group)
+    if kernels is None:
+        if not q.is_cuda:
+            raise RuntimeError("flash_attention_v100 has no CPU path: q, k and v must be CUDA tensors")
+        kernels = CudaBlockKernels
+    scale = float(q.shape[3] ** -0.5 if scale is None else scale)
+    o, lse = RingAttentionFunction.apply(q, k.contiguous(), v.contiguous(), scale, bool(causal), ring, kernels)
+    return (o, lse) if return_softmax_lse else o
+
+
+__all__ = ["ring_schedule", "kv_transfer", "DistributedRing", "CudaBlockKernels", "ring_forward", "ring_backward",
+           "RingAttentionFunction", "flash_attention_v100_sequence_parallel"]

@@ -171,6 +171,42 @@ int fa_b200_bwd(const fa_b200_params* p);
  */
 int fa_b200_bwd_static(const fa_b200_params* p);
 
+/*
+ * Running combination of per-block partial results, for sequence-parallel
+ * attention (every rank holds a slice of the sequence; key/value blocks travel
+ * around a ring; each (query slice, key block) pair is one fa_b200_fwd or
+ * fa_b200_bwd call).  No counterpart in the reference: its sequence-parallel
+ * strategy is a stub that splits heads instead (interface.py:437-450,
+ * config.py:153-157).
+ *
+ *   lse_acc != NULL (outputs):   lse' = log(e^lse_acc + e^lse_part),
+ *       acc <- acc * e^(lse_acc - lse') + part * e^(lse_part - lse'),  lse_acc <- lse'
+ *   lse_acc == NULL (gradients): acc <- acc + part
+ *
+ * acc is (B, N, H, D) contiguous fp32, lse_acc / lse_part are (B, H, N) fp32
+ * (natural log, as fa_b200_fwd writes them).  `first` != 0: acc and lse_acc
+ * hold nothing yet and are overwritten, not read.  out.ptr != NULL: the new
+ * total is also written there in `dtype` (the caller sets it on the step it
+ * knows to be the last).  part.ptr == NULL with out.ptr != NULL: only that
+ * conversion.  D must be a multiple of 8; pointers and strides 16-byte aligned.
+ */
+typedef struct fa_b200_combine_params {
+    size_t         struct_bytes;   /* = sizeof(fa_b200_combine_params); checked */
+    float*         acc;
+    float*         lse_acc;
+    fa_b200_tensor part;           /* (B, N, H, D) in `dtype`, element strides */
+    const float*   lse_part;
+    fa_b200_tensor out;            /* optional */
+    int32_t        B, N, H, D;
+    int32_t        dtype;          /* fa_b200_dtype of part and out */
+    int32_t        first;
+    int32_t        device;
+    int32_t        reserved;
+    void*          stream;         /* cudaStream_t */
+} fa_b200_combine_params;
+
+int fa_b200_combine(const fa_b200_combine_params* p);
+
 /* Bytes of scratch fa_b200_bwd needs for these sizes (delta, fp32 dQ
  * accumulator, ...).  Counterpart of the 'delta' entry of
  * ops/memory.py:653-760 allocate_attention_workspace_enhanced. */
