@@ -27,6 +27,8 @@ struct CombineArgs {
     void* out;
     int64_t part_sb, part_sn, part_sh;
     int64_t out_sb, out_sn, out_sh;
+    int64_t acc_sb;             // batch stride of acc (elements); rows of one batch entry are dense
+    int64_t lse_sb, lse_sh;     // batch and head strides of lse_acc (lse_part is dense)
     int N, H, D;
     int64_t n_chunks;           // B * N * H * D / 8
     int first;
@@ -94,8 +96,8 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineArgs a) {
         const int64_t b = bn / a.N;
         float wa = a.first ? 0.f : 1.f, wp = a.part ? 1.f : 0.f;
         if (MERGE) {
-            const int64_t li = (b * a.H + h) * a.N + n;
-            const float lp = a.part ? a.lse_part[li] : -INFINITY;
+            const int64_t li = b * a.lse_sb + h * a.lse_sh + n;
+            const float lp = a.part ? a.lse_part[(b * a.H + h) * a.N + n] : -INFINITY;
             const float la = a.first ? -INFINITY : a.lse_acc[li];
             const float m = fmaxf(la, lp);
             float ln = -INFINITY;
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineArgs a) {
             if (c == 0) a.lse_acc[li] = ln;
         }
         float x[8], y[8];
-        float* accp = a.acc + row * a.D + c * 8;
+        float* accp = a.acc + b * a.acc_sb + ((int64_t)n * a.H + h) * a.D + c * 8;
         if (a.first) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) x[i] = 0.f;
@@ -171,6 +173,10 @@ extern "C" int fa_b200_combine(const fa_b200_combine_params* p) {
         return ((uintptr_t)t.ptr % 16 == 0) && (t.stride_b * esz % 16 == 0) && (t.stride_n * esz % 16 == 0) &&
                (t.stride_h * esz % 16 == 0);
     };
+    if (p->acc_stride_b % 4 != 0 || p->acc_stride_b < 0 || p->lse_stride_b < 0 || p->lse_stride_h < 0) {
+        set_error("acc_stride_b must be a non-negative multiple of 4 elements, lse strides non-negative");
+        return FA_EALIGN;
+    }
     if ((uintptr_t)p->acc % 16 != 0 || (p->part.ptr && !aligned(p->part)) || (p->out.ptr && !aligned(p->out))) {
         set_error("acc, part and out must be 16-byte aligned with strides that are multiples of 16 bytes");
         return FA_EALIGN;
@@ -180,6 +186,9 @@ extern "C" int fa_b200_combine(const fa_b200_combine_params* p) {
     a.part_sb = p->part.stride_b; a.part_sn = p->part.stride_n; a.part_sh = p->part.stride_h;
     a.out_sb = p->out.stride_b; a.out_sn = p->out.stride_n; a.out_sh = p->out.stride_h;
     a.N = p->N; a.H = p->H; a.D = p->D;
+    a.acc_sb = p->acc_stride_b ? p->acc_stride_b : (int64_t)p->N * p->H * p->D;
+    a.lse_sb = p->lse_stride_b ? p->lse_stride_b : (int64_t)p->H * p->N;
+    a.lse_sh = p->lse_stride_h ? p->lse_stride_h : (int64_t)p->N;
     a.n_chunks = rows * (p->D / 8);
     a.first = p->first ? 1 : 0;
     int prev = -1;

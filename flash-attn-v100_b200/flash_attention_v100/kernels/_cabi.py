@@ -61,6 +61,7 @@ class CombineParams(ctypes.Structure):
         ("B", ctypes.c_int32), ("N", ctypes.c_int32), ("H", ctypes.c_int32), ("D", ctypes.c_int32),
         ("dtype", ctypes.c_int32), ("first", ctypes.c_int32), ("device", ctypes.c_int32),
         ("reserved", ctypes.c_int32), ("stream", ctypes.c_void_p),
+        ("acc_stride_b", ctypes.c_int64), ("lse_stride_b", ctypes.c_int64), ("lse_stride_h", ctypes.c_int64),
     ]
 
 

@@ -208,14 +208,19 @@ def launch_combine(acc, part=None, lse_acc=None, lse_part=None, out=None, first=
     like = part if part is not None else out
     if like is None:
         raise ValueError("launch_combine needs a partial, an output, or both")
-    if acc.dtype != torch.float32 or not acc.is_contiguous() or acc.shape != like.shape:
-        raise ValueError("acc must be a contiguous fp32 tensor of the partial's shape")
+    B, N, H, D = like.shape
+    # acc may be a range of rows of a larger total: any batch stride, dense below it
+    if acc.dtype != torch.float32 or acc.shape != like.shape or \
+            (N > 0 and (acc.stride(3), acc.stride(2), acc.stride(1)) != (1, D, H * D)):
+        raise ValueError("acc must be an fp32 tensor of the partial's shape, dense within a batch entry")
     if part is not None and out is not None and part.dtype != out.dtype:
         raise ValueError("part and out must have the same dtype")
-    for t in (lse_acc, lse_part):
-        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()
-                              or tuple(t.shape) != (acc.shape[0], acc.shape[2], acc.shape[1])):
-            raise ValueError("log-sum-exps must be contiguous fp32 (B, H, N) tensors")
+    if lse_acc is not None and (lse_acc.dtype != torch.float32 or tuple(lse_acc.shape) != (B, H, N)
+                                or (N > 1 and lse_acc.stride(2) != 1)):
+        raise ValueError("lse_acc must be an fp32 (B, H, N) tensor with unit stride along N")
+    if lse_part is not None and (lse_part.dtype != torch.float32 or not lse_part.is_contiguous()
+                                 or tuple(lse_part.shape) != (B, H, N)):
+        raise ValueError("lse_part must be a contiguous fp32 (B, H, N) tensor")
     p = _cabi.CombineParams()
     p.struct_bytes = ctypes.sizeof(_cabi.CombineParams)
     p.acc = acc.data_ptr()
@@ -224,6 +229,9 @@ def launch_combine(acc, part=None, lse_acc=None, lse_part=None, out=None, first=
     p.part = _tensor4(_last_dim_contiguous(part)) if part is not None else _cabi.Tensor4()
     p.out = _tensor4(out) if out is not None else _cabi.Tensor4()
     p.B, p.N, p.H, p.D = acc.shape
+    p.acc_stride_b = acc.stride(0)
+    if lse_acc is not None:
+        p.lse_stride_b, p.lse_stride_h = lse_acc.stride(0), lse_acc.stride(1)
     p.dtype = dtype_enum(like.dtype)
     p.first = int(bool(first))
     p.device = acc.device.index if acc.device.index is not None else torch.cuda.current_device()

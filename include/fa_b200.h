@@ -183,8 +183,11 @@ int fa_b200_bwd_static(const fa_b200_params* p);
  *       acc <- acc * e^(lse_acc - lse') + part * e^(lse_part - lse'),  lse_acc <- lse'
  *   lse_acc == NULL (gradients): acc <- acc + part
  *
- * acc is (B, N, H, D) contiguous fp32, lse_acc / lse_part are (B, H, N) fp32
- * (natural log, as fa_b200_fwd writes them).  `first` != 0: acc and lse_acc
+ * acc is (B, N, H, D) fp32, dense within a batch entry (acc_stride_b elements
+ * between entries; 0 = N*H*D), lse_acc is (B, H, N) fp32 with strides
+ * lse_stride_b / lse_stride_h (0 = dense) and lse_part is dense (B, H, N) fp32
+ * (natural log, as fa_b200_fwd writes them): the strides let a call work on a
+ * range of rows of a larger total.  `first` != 0: acc and lse_acc
  * hold nothing yet and are overwritten, not read.  out.ptr != NULL: the new
  * total is also written there in `dtype` (the caller sets it on the step it
  * knows to be the last).  part.ptr == NULL with out.ptr != NULL: only that
@@ -203,6 +206,9 @@ typedef struct fa_b200_combine_params {
     int32_t        device;
     int32_t        reserved;
     void*          stream;         /* cudaStream_t */
+    int64_t        acc_stride_b;   /* elements; 0 = N*H*D */
+    int64_t        lse_stride_b;   /* elements of lse_acc; 0 = H*N */
+    int64_t        lse_stride_h;   /* 0 = N */
 } fa_b200_combine_params;
 
 int fa_b200_combine(const fa_b200_combine_params* p);

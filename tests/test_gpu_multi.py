@@ -12,6 +12,7 @@ import torch.multiprocessing as mp
 
 import flash_attention_v100 as fa
 from flash_attention_v100.interface import FlashAttentionV100Manager, plan_shards, _slice
+from flash_attention_v100.ops import sequence_parallel
 from flash_attention_v100.testing import dq_is_bit_reproducible, assert_same_dq, rel_l2
 
 pytestmark = pytest.mark.gpu
@@ -99,7 +100,7 @@ def test_nccl_scatter_compute_gather_equals_single_gpu():
     assert dict(ret).get(0) == "ok", dict(ret)
 
 
-def _ring_rank_main(rank, world, port, ret):
+def _ring_rank_main(rank, world, port, layout, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
@@ -107,18 +108,22 @@ def _ring_rank_main(rank, world, port, ret):
     try:
         B, n, H, D = 2, 384, 4, 128
         qc, kc, vc, gc = _inputs(B, n * world, H, D, torch.bfloat16, seed=5)
-        sl = slice(rank * n, (rank + 1) * n)
-        ql, kl, vl = (t[:, sl].to(dev).requires_grad_(True) for t in (qc, kc, vc))
-        o, lse = fa.flash_attention_v100_sequence_parallel(ql, kl, vl, causal=True, return_softmax_lse=True)
-        o.backward(gc[:, sl].to(dev))
+        if layout == "zigzag":
+            cut = lambda t, dim=1: sequence_parallel.zigzag_split(t, world, rank, dim)
+        else:
+            cut = lambda t, dim=1: t.chunk(world, dim=dim)[rank]
+        ql, kl, vl = (cut(t).to(dev).requires_grad_(True) for t in (qc, kc, vc))
+        o, lse = fa.flash_attention_v100_sequence_parallel(ql, kl, vl, causal=True, return_softmax_lse=True,
+                                                           layout=layout)
+        o.backward(cut(gc).to(dev))
         # one call over the whole sequence on this rank's own GPU, sliced, is the reference
         q1, k1, v1 = (t.to(dev).requires_grad_(True) for t in (qc, kc, vc))
         o1, lse1 = fa.flash_attention_v100(q1, k1, v1, causal=True, return_softmax_lse=True, enable_multi_gpu=False)
         o1.backward(gc.to(dev))
         torch.cuda.synchronize()
-        errs = {"o": rel_l2(o.detach(), o1.detach()[:, sl]), "lse": rel_l2(lse, lse1[:, :, sl]),
-                "dq": rel_l2(ql.grad, q1.grad[:, sl]), "dk": rel_l2(kl.grad, k1.grad[:, sl]),
-                "dv": rel_l2(vl.grad, v1.grad[:, sl])}
+        errs = {"o": rel_l2(o.detach(), cut(o1.detach())), "lse": rel_l2(lse, cut(lse1, 2)),
+                "dq": rel_l2(ql.grad, cut(q1.grad)), "dk": rel_l2(kl.grad, cut(k1.grad)),
+                "dv": rel_l2(vl.grad, cut(v1.grad))}
         bad = {k: v for k, v in errs.items() if not v < (1e-5 if k == "lse" else 4e-3)}
         ret[rank] = "ok" if not bad else f"mismatch: {bad}"
     except Exception as e:   # noqa: BLE001
@@ -127,12 +132,13 @@ def _ring_rank_main(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_nccl_ring_attention_equals_whole_sequence():
+@pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
+def test_nccl_ring_attention_equals_whole_sequence(layout):
     _need_gpus(2)
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_ring_rank_main, args=(r, 2, port, ret)) for r in range(2)]
+    procs = [ctx.Process(target=_ring_rank_main, args=(r, 2, port, layout, ret)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:

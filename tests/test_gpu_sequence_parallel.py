@@ -61,6 +61,24 @@ def test_combine_sum_and_convert_only(device, dtype):
     assert torch.equal(out, want.to(dtype))
 
 
+def test_combine_on_a_range_of_rows(device):
+    """acc and lse_acc may be a range of rows of a larger total (the zigzag layout's second chunk)."""
+    B, N, H, D, c = 2, 40, 3, 64, 24
+    g = torch.Generator().manual_seed(5)
+    acc = torch.randn(B, N, H, D, generator=g).to(device)
+    lse = torch.randn(B, H, N, generator=g).to(device)
+    part = torch.randn(B, N - c, H, D, generator=g).to(torch.bfloat16).to(device)
+    lse_part = torch.randn(B, H, N - c, generator=g).to(device)
+    acc_ref, lse_ref = acc.cpu().clone(), lse.cpu().clone()
+    ops.launch_combine(acc[:, c:], part, lse[:, :, c:], lse_part)
+    OracleBlockKernels.combine(acc_ref[:, c:], part.cpu(), lse_ref[:, :, c:], lse_part.cpu())
+    assert torch.equal(acc[:, :c].cpu(), acc_ref[:, :c]) and torch.equal(lse[:, :, :c].cpu(), lse_ref[:, :, :c])
+    assert torch.allclose(acc.cpu(), acc_ref, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(lse.cpu(), lse_ref, rtol=0, atol=5e-6)
+    with pytest.raises(ValueError):
+        ops.launch_combine(acc[:, :, :2], part[:, :, :2])            # rows of a batch entry not dense
+
+
 def test_combine_rejects_bad_operands(device):
     acc = torch.zeros(1, 8, 1, 64, device=device)
     part = torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16, device=device)
@@ -74,26 +92,31 @@ def test_combine_rejects_bad_operands(device):
         ops.launch_combine(acc, part, lse_acc=torch.zeros(1, 8, 1, device=device))
 
 
-def _rank_call(ring, q, k, v, d_o, causal):
+def _rank_call(ring, q, k, v, d_o, causal, layout="contiguous"):
     # ring_forward / ring_backward are called directly: autograd would run every rank's backward on
     # the one worker thread it keeps per device, where the ranks of a thread ring would wait for each
     # other for ever.  The autograd wrapper is covered below with one rank and, over NCCL, with two GPUs.
-    n = q.shape[1] // ring.world
-    sl = slice(ring.rank * n, (ring.rank + 1) * n)
-    ql, kl, vl, gl = (t[:, sl].contiguous() for t in (q, k, v, d_o))
+    if layout == "zigzag":
+        ql, kl, vl, gl = (sp.zigzag_split(t, ring.world, ring.rank) for t in (q, k, v, d_o))
+    else:
+        ql, kl, vl, gl = (t.chunk(ring.world, dim=1)[ring.rank].contiguous() for t in (q, k, v, d_o))
     scale = q.shape[3] ** -0.5
-    o, lse = sp.ring_forward(ql, kl, vl, scale, causal, ring)
-    dq, dk, dv = sp.ring_backward(gl, ql, kl, vl, o, lse, scale, causal, ring)
+    o, lse = sp.ring_forward(ql, kl, vl, scale, causal, ring, layout=layout)
+    dq, dk, dv = sp.ring_backward(gl, ql, kl, vl, o, lse, scale, causal, ring, layout=layout)
     return o, lse, dq, dk, dv
 
 
-@pytest.mark.parametrize("world,causal,dtype,H,Hkv,D,n", [
-    (2, True, torch.bfloat16, 4, 4, 128, 256),
-    (4, True, torch.bfloat16, 4, 2, 128, 192),       # ragged slices (not a multiple of the 128-row tile), GQA
-    (3, False, torch.float16, 2, 2, 64, 128),
-    (2, True, torch.float32, 2, 2, 64, 96),          # CUDA-core kernels
+@pytest.mark.parametrize("world,causal,dtype,H,Hkv,D,n,layout", [
+    (2, True, torch.bfloat16, 4, 4, 128, 256, "contiguous"),
+    (4, True, torch.bfloat16, 4, 2, 128, 192, "contiguous"),   # ragged slices (not a multiple of 128), GQA
+    (3, False, torch.float16, 2, 2, 64, 128, "contiguous"),
+    (2, True, torch.float32, 2, 2, 64, 96, "contiguous"),      # CUDA-core kernels
+    (2, True, torch.bfloat16, 4, 4, 128, 256, "zigzag"),
+    (4, True, torch.bfloat16, 4, 2, 128, 176, "zigzag"),       # chunks of 88 rows, GQA
+    (3, True, torch.float16, 2, 2, 64, 256, "zigzag"),
+    (2, True, torch.float32, 2, 1, 64, 96, "zigzag"),
 ])
-def test_ring_on_one_device_equals_whole_sequence(device, world, causal, dtype, H, Hkv, D, n):
+def test_ring_on_one_device_equals_whole_sequence(device, world, causal, dtype, H, Hkv, D, n, layout):
     B, N = 2, n * world
     g = torch.Generator().manual_seed(3)
     qc = (0.5 * torch.randn(B, N, H, D, generator=g)).to(dtype)
@@ -101,11 +124,13 @@ def test_ring_on_one_device_equals_whole_sequence(device, world, causal, dtype, 
     vc = (0.5 * torch.randn(B, N, Hkv, D, generator=g)).to(dtype)
     gc = torch.randn(B, N, H, D, generator=g).to(dtype)
     q, k, v, d_o = (t.to(device) for t in (qc, kc, vc, gc))
-    res = run_ring(world, lambda ring: _rank_call(ring, q, k, v, d_o, causal))
+    res = run_ring(world, lambda ring: _rank_call(ring, q, k, v, d_o, causal, layout))
     torch.cuda.synchronize()
     ops.check_status(device)
-    o, dq, dk, dv = (torch.cat([r[i] for r in res], dim=1) for i in (0, 2, 3, 4))
-    lse = torch.cat([r[1] for r in res], dim=2)
+    join = (lambda parts, dim: sp.zigzag_merge(parts, dim)) if layout == "zigzag" else \
+        (lambda parts, dim: torch.cat(parts, dim=dim))
+    o, dq, dk, dv = (join([r[i] for r in res], 1) for i in (0, 2, 3, 4))
+    lse = join([r[1] for r in res], 2)
     # against the oracle on the dtype-rounded inputs ...
     ref = orc.attention_forward_backward(qc.float(), kc.float(), vc.float(), gc.float(), causal=causal)
     # ... and against one call over the whole sequence on the same device
