@@ -87,6 +87,59 @@ def run_benchmark(batch: int, seq_len: int, heads: int, head_dim: int, dtype: to
             "fwd_bwd_tflops": (fl["fwd"] + fl["bwd"]) / (f + b) * 1e-9}
 
 
+def run_sequence_parallel_benchmark(batch: int, seq_len: int, heads: int, head_dim: int, dtype: torch.dtype,
+                                    causal: bool, layout: str, steps: int = 5, warmup: int = 3,
+                                    heads_kv: Optional[int] = None) -> Dict[str, Any]:
+    """Forward + backward of one sequence of `seq_len` positions split over the ranks of a torchrun
+    launch (one process per GPU, NCCL).  Time: CUDA events around `steps` steps, the maximum over
+    ranks; TFLOP/s of the whole job."""
+    from . import flash_attention_v100_sequence_parallel
+    if not torch.cuda.is_available():
+        raise RuntimeError("flash-attn-benchmark needs a CUDA device: there is no CPU path")
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    started = not dist.is_initialized()
+    if started:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        if seq_len % (2 * world) != 0:
+            raise ValueError(f"--seq-len must be a multiple of {2 * world}")
+        n, hkv = seq_len // world, heads if heads_kv is None else heads_kv
+        gen = torch.Generator().manual_seed(rank)
+        mk = lambda h: torch.randn(batch, n, h, head_dim, generator=gen).to(dtype).to(dev).requires_grad_(True)
+        q, k, v = mk(heads), mk(hkv), mk(hkv)
+        d_o = torch.randn(batch, n, heads, head_dim, generator=gen).to(dtype).to(dev)
+
+        def step():
+            o = flash_attention_v100_sequence_parallel(q, k, v, causal=causal, layout=layout)
+            o.backward(d_o)
+            q.grad = k.grad = v.grad = None
+
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        fl = attention_flops(batch, seq_len, seq_len, heads, head_dim, causal)
+        return {"rank": rank, "n_gpus": world, "shape": [batch, seq_len, heads, head_dim], "per_rank": n,
+                "heads_kv": hkv, "dtype": str(dtype).replace("torch.", ""), "causal": causal, "layout": layout,
+                "steps": steps, "warmup": warmup, "ms_per_step": ms.item(),
+                "fwd_bwd_tflops": (fl["fwd"] + fl["bwd"]) / ms.item() * 1e-9}
+    finally:
+        if started:
+            dist.destroy_process_group()
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="flash-attn-benchmark", description=__doc__.split("\n\n")[0])
     ap.add_argument("--batch", type=int, default=4)
@@ -101,7 +154,22 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--json", action="store_true", help="print one JSON line instead of text")
+    ap.add_argument("--sequence-parallel", choices=("contiguous", "zigzag"), default=None,
+                    help="under torchrun: split one sequence of --seq-len over the ranks (ring attention)")
     args = ap.parse_args(argv)
+    if args.sequence_parallel:
+        if not torch.cuda.is_available():
+            print("CUDA not available: nothing to time (there is no CPU path).")
+            return 1
+        res = run_sequence_parallel_benchmark(args.batch, args.seq_len, args.heads, args.head_dim,
+                                              _DTYPES[args.dtype], args.causal, args.sequence_parallel,
+                                              args.steps, args.warmup, args.heads_kv)
+        if res["rank"] == 0:
+            print(json.dumps(res) if args.json else
+                  f"{res['n_gpus']} GPUs, (B, N, H, D) = {tuple(res['shape'])}, {res['per_rank']} positions per "
+                  f"rank, causal={res['causal']}, {res['layout']}: {res['ms_per_step']:.3f} ms per forward + "
+                  f"backward, {res['fwd_bwd_tflops']:.1f} TFLOP/s")
+        return 0
 
     info = get_device_info()
     if not args.json:
