@@ -123,6 +123,7 @@ struct BwdArgs {
     int32_t* status;
     int B, Nq, Nk, H, Hkv, nq_pad;
     int causal;
+    int shift;                     // key j is visible to query i iff j <= i + shift
     float scale, scale_log2;
     uint32_t drop_thr;
     float inv_keep;
@@ -182,7 +183,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (KS) {
         tile = blockIdx.x;                          // key tile
         head_x = blockIdx.y;                        // kv head
-        it0 = a.causal ? tile : 0;                  // first query tile that sees this key tile
+        // first query tile that sees this key tile: query i sees key j iff j <= i + shift
+        it0 = a.causal ? (tile * kTile > a.shift ? (tile * kTile - a.shift) / kTile : 0) : 0;
         n_per_head = nq_tiles > it0 ? nq_tiles - it0 : 0;
         if (tile * kTile >= nk) n_per_head = 0;     // a tile of padding keys: dK = dV = 0
         n_iter = n_per_head * group;
@@ -191,7 +193,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         head_x = blockIdx.y;                        // query head
         it0 = 0;
         int kv_end = nk;
-        if (a.causal && tile * kTile + kTile < kv_end) kv_end = tile * kTile + kTile;
+        if (a.causal && tile * kTile + kTile + a.shift < kv_end) kv_end = tile * kTile + kTile + a.shift;
         n_per_head = (kv_end + kTile - 1) / kTile;
         n_iter = n_per_head;
     }
@@ -575,7 +577,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             }
             }
             const uint64_t sc2 = f2_pack(a.scale_log2, a.scale_log2);
-            const bool diag = a.causal && strm_tile == tile;       // key row > query column is hidden
+            // key row > query column + shift is hidden: only tiles the mask's edge crosses need the test
+            const bool diag = a.causal && strm_tile * kTile + a.shift < tile * kTile + kTile - 1;
             const bool tail = tile * kTile + kTile > nk;            // the tile holds padding keys
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
@@ -605,7 +608,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             for (int k = 0; k < 2; ++k) {
                                 const int j = 2 * hf + jj, i0 = 4 * j + 2 * k;
                                 const int row_k = tile * kTile + rbase + 16 * h + 8 * k;
-                                const int col = col_g0 + 8 * j + 2 * lq;
+                                const int col = col_g0 + 8 * j + 2 * lq + a.shift;
                                 const bool dead = tail && row_k >= nk;
                                 if (dead || (diag && row_k > col)) pf[h][i0] = 0u;
                                 if (dead || (diag && row_k > col + 1)) pf[h][i0 + 1] = 0u;
@@ -710,7 +713,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 // MMA warp (dV can start on it) while the second is computed.
                 static_assert(CPT == 32, "the half hand-off is written for 32 columns per thread");
                 const ulonglong2* l2 = reinterpret_cast<const ulonglong2*>(lse_s + cb);
-                const bool diag = a.causal && strm_tile == tile;   // key row > query column is hidden
+                const bool diag = a.causal && strm_tile * kTile + a.shift < tile * kTile + kTile - 1;
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
 #pragma unroll
@@ -727,7 +730,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     if (diag) {
 #pragma unroll
                         for (int c = hf * (CPT / 2); c < (hf + 1) * (CPT / 2); ++c)
-                            if (row_g > col_g0 + c) PSET(c, 0.f);
+                            if (row_g > col_g0 + c + a.shift) PSET(c, 0.f);
                     }
                     if (row_g >= nk) {                    // a padding key inside a live tile (or beyond Nk)
 #pragma unroll
@@ -771,12 +774,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         PSET(c + 1, ex2(x1));
                     }
                 }
-                const bool diag = a.causal && strm_tile == tile;
+                const bool diag = a.causal && strm_tile * kTile + kTile - 1 > tile * kTile + a.shift;
                 if (diag || strm_tile * kTile + kTile > nk) {
 #pragma unroll
                     for (int c = 0; c < CPT; ++c) {
                         const int col = col_g0 + c;
-                        if (col >= nk || (diag && col > row_g)) PSET(c, 0.f);
+                        if (col >= nk || (diag && col > row_g + a.shift)) PSET(c, 0.f);
                     }
                 }
             }
@@ -1020,6 +1023,7 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     a.kv_len = p.kv_lengths;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv; a.nq_pad = nq_pad;
     a.causal = p.causal;
+    a.shift = p.causal ? p.causal_shift : 0;
     a.scale = p.scale;
     a.scale_log2 = p.scale * kLog2e;
     a.drop_thr = dropout_threshold(p.dropout_p);

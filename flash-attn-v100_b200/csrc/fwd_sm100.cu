@@ -97,6 +97,7 @@ struct FwdArgs {
     const int32_t* kv_len;         // optional per-batch key counts
     int B, Nq, Nk, H, Hkv;
     int causal;
+    int shift;                     // key j is visible to query i iff j <= i + shift
     int n_pairs;                   // ceil(Nq / 256)
     int items_per_head;            // causal: ceil(n_pairs / 2) mirrored items; else n_pairs
     int n_items;                   // items_per_head * B * H
@@ -130,7 +131,7 @@ __device__ __forceinline__ bool decode_work(const FwdArgs& a, int w, int u, Pair
 __device__ __forceinline__ int num_blocks(const FwdArgs& a, int pair, int t, int nk) {
     const int row0 = (pair * 2 + t) * kBlockM;
     int kv_end = nk;               // keys this batch entry attends to
-    if (a.causal && row0 + kBlockM < kv_end) kv_end = row0 + kBlockM;
+    if (a.causal && row0 + kBlockM + a.shift < kv_end) kv_end = row0 + kBlockM + a.shift;
     return (row0 < a.Nq) ? (kv_end + kBlockN - 1) / kBlockN : 0;
 }
 
@@ -395,12 +396,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     tmem_wait_ld();
 
                     const int col0 = j * kBlockN;
-                    const bool need_mask = (a.causal && col0 + kBlockN - 1 > tile * kBlockM) || (col0 + kBlockN > nk);
+                    const bool need_mask = (a.causal && col0 + kBlockN - 1 > tile * kBlockM + a.shift) || (col0 + kBlockN > nk);
                     if (need_mask) {
 #pragma unroll
                         for (int c = 0; c < 128; ++c) {
                             const int col = col0 + c;
-                            if (col >= nk || (a.causal && col > i)) SSET(c, -INFINITY);
+                            if (col >= nk || (a.causal && col > i + a.shift)) SSET(c, -INFINITY);
                         }
                     }
                     float mx0 = SF(0), mx1 = SF(1), mx2 = SF(2), mx3 = SF(3);
@@ -554,6 +555,7 @@ int launch(const fa_b200_params& p) {
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv;
     a.kv_len = p.kv_lengths;
     a.causal = p.causal;
+    a.shift = p.causal ? p.causal_shift : 0;
     a.n_pairs = (p.Nq + 2 * kBlockM - 1) / (2 * kBlockM);
     a.items_per_head = p.causal ? (a.n_pairs + 1) / 2 : a.n_pairs;
     const int64_t n_items = (int64_t)a.items_per_head * p.B * p.H;

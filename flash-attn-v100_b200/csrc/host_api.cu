@@ -78,6 +78,10 @@ int validate_common(const fa_b200_params* p, bool backward) {
                   p->struct_bytes, sizeof(fa_b200_params));
         return FA_EINVAL;
     }
+    if (p->causal_shift < 0) {
+        set_error("causal_shift %d is negative: the first queries would see no key", p->causal_shift);
+        return FA_EINVAL;
+    }
     if (p->B < 0 || p->Nq < 0 || p->Nk < 0 || p->H <= 0 || p->Hkv <= 0 || p->D <= 0) {
         set_error("sizes must be non-negative and H, Hkv, D positive (B=%d Nq=%d Nk=%d H=%d Hkv=%d D=%d)",
                   p->B, p->Nq, p->Nk, p->H, p->Hkv, p->D);

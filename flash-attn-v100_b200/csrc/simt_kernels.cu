@@ -37,6 +37,7 @@ struct SimtArgs {
     float* delta;
     int B, Nq, Nk, H, Hkv, D;
     int causal;
+    int shift;          // key j is visible to query i iff j <= i + shift
     float scale;
     uint32_t drop_thr;   // 0 = no dropout
     float inv_keep;      // 1 / (1 - effective p)
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(SimtArgs a) {
 
     const int nk = kv_len_of(a.kv_len, b, a.Nk);      // keys this batch entry attends to
     int kv_end = nk;
-    if (a.causal && m0 + BM < kv_end) kv_end = m0 + BM;
+    if (a.causal && m0 + BM + a.shift < kv_end) kv_end = m0 + BM + a.shift;
 
     for (int n0 = 0; n0 < kv_end; n0 += BN) {
         __syncthreads();
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(SimtArgs a) {
                 int j = n0 + tx + 16 * c;
                 float s = acc[r][c] * a.scale;
                 if (bias_b && i < a.Nq && j < nk) s += bias_b[(int64_t)i * a.bias.stride_n + j];
-                if (j >= nk || (a.causal && j > i)) s = -INFINITY;
+                if (j >= nk || (a.causal && j > i + a.shift)) s = -INFINITY;
                 Ss[(ty * 4 + r) * SLD + tx + 16 * c] = s;
             }
         }
@@ -268,11 +269,11 @@ __global__ void __launch_bounds__(NT) simt_bwd_kernel(SimtArgs a) {
 
         int it_begin, it_end;   // tile indices of the streamed operand
         if (MODE == 0) {
-            it_begin = a.causal ? (tile * BN) / BM : 0;
+            it_begin = (a.causal && tile * BN > a.shift) ? (tile * BN - a.shift) / BM : 0;
             it_end = (a.Nq + BM - 1) / BM;
         } else {
             int kv_end = nk;
-            if (a.causal && tile * BM + BM < kv_end) kv_end = tile * BM + BM;
+            if (a.causal && tile * BM + BM + a.shift < kv_end) kv_end = tile * BM + BM + a.shift;
             it_begin = 0;
             it_end = (kv_end + BN - 1) / BN;
         }
@@ -338,7 +339,7 @@ __global__ void __launch_bounds__(NT) simt_bwd_kernel(SimtArgs a) {
                 for (int c = 0; c < 4; ++c) {
                     const int col = tx + 16 * c, j = n0 + col;
                     float p = 0.f, z = 1.f;
-                    bool visible = (i < a.Nq) && (j < nk) && !(a.causal && j > i);
+                    bool visible = (i < a.Nq) && (j < nk) && !(a.causal && j > i + a.shift);
                     if (visible) {
                         float s = s_acc[r][c] * a.scale;
                         if (bias_b) s += bias_b[(int64_t)i * a.bias.stride_n + j];
@@ -450,7 +451,7 @@ SimtArgs make_args(const fa_b200_params& p, float* delta) {
     a.lse = p.lse; a.delta = delta;
     a.bias = p.bias; a.d_scores = p.d_scores; a.kv_len = p.kv_lengths;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv; a.D = p.D;
-    a.causal = p.causal; a.scale = p.scale;
+    a.causal = p.causal; a.shift = p.causal ? p.causal_shift : 0; a.scale = p.scale;
     a.drop_thr = dropout_threshold(p.dropout_p);
     a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
     a.key = philox_make_key(p.seed, p.offset);

@@ -260,6 +260,7 @@ def flash_attention_v100(
     fallback_on_error: bool = True,
     validate_inputs: bool = True,
     key_lengths: Optional[torch.Tensor] = None,
+    causal_alignment: str = "top_left",
 ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
     """Exact attention on (B, N, H, D) tensors; signature of reference interface.py:199-217.
 
@@ -273,6 +274,9 @@ def flash_attention_v100(
         key_lengths: (not in the reference) int tensor (B,): batch entry b attends to its first
             key_lengths[b] keys only (right-padded batches); key blocks beyond are skipped on every
             kernel family, dK / dV of the padding are zero
+        causal_alignment: (not in the reference) "top_left" (the reference's mask: key j visible to
+            query i iff j <= i) or "bottom_right" (j <= i + Nk - Nq: the last query sees every key;
+            needs Nk >= Nq); the same for Nq == Nk
         block_size_m, block_size_n, enable_autotuning, optimization_strategy:
             accepted for source compatibility; tiles come from the static table
         return_softmax_lse: also return the (B, H, Nq) fp32 log-sum-exp
@@ -291,6 +295,7 @@ def flash_attention_v100(
     elif scale is None:
         scale = q.shape[-1] ** -0.5
 
+    shift = _causal_shift(causal, causal_alignment, q.shape[1], k.shape[1], key_lengths)
     use_multi = manager.enable_multi_gpu if enable_multi_gpu is None else (
         bool(enable_multi_gpu) and torch.cuda.is_available())
     profile = manager.enable_profiling or enable_profiling
@@ -300,11 +305,12 @@ def flash_attention_v100(
 
     if use_multi and len(manager.devices) > 1:
         result = _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, block_size_n,
-                                    enable_autotuning, return_softmax_lse, manager, key_lengths)
+                                    enable_autotuning, return_softmax_lse, manager, key_lengths, shift)
     else:
         result = FlashAttentionV100Function.apply(q, k, v, scale, causal, dropout_p, bias, block_size_m,
                                                   block_size_n, enable_autotuning, return_softmax_lse,
-                                                  False, True, None, True, "balanced", False, 1, 0, key_lengths)
+                                                  False, True, None, True, "balanced", False, 1, 0, key_lengths,
+                                                  shift)
     if profile:
         end.record(torch.cuda.current_stream(q.device))
         end.synchronize()
@@ -312,8 +318,26 @@ def flash_attention_v100(
     return result
 
 
+def _causal_shift(causal, alignment: str, seq_q: int, seq_k: int, key_lengths) -> int:
+    """Offset of the causal mask's diagonal: key j is visible to query i iff j <= i + shift.
+    "top_left" (the reference: kernels/forward_kernel.py:179-182 masks row >= col) is 0;
+    "bottom_right" lets the last query see every key, shift = Nk - Nq (decoding and chunked prefill
+    against a longer key/value cache)."""
+    if alignment not in ("top_left", "bottom_right"):
+        raise ValueError('causal_alignment must be "top_left" or "bottom_right"')
+    if not causal or alignment == "top_left":
+        return 0
+    if seq_k < seq_q:
+        raise ValueError(f"bottom-right causal alignment needs Nk >= Nq (got Nq={seq_q}, Nk={seq_k}): "
+                         "the first queries would see no key")
+    if key_lengths is not None:
+        raise ValueError("bottom-right causal alignment is defined by the tensors' lengths: it cannot be "
+                         "combined with key_lengths")
+    return seq_k - seq_q
+
+
 def _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, block_size_n,
-                       enable_autotuning, return_softmax_lse, manager, key_lengths=None):
+                       enable_autotuning, return_softmax_lse, manager, key_lengths=None, causal_shift=0):
     """Single-process sharding over manager.devices (reference interface.py:351-434).
 
     Shards are planned over heads or batch; each device gets its slice by an
@@ -353,7 +377,7 @@ def _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, bl
             ll = key_lengths[shard[0]:shard[1]].to(dev, non_blocking=True) if key_lengths is not None else None
             res = FlashAttentionV100Function.apply(ql, kl, vl, scale, causal, dropout_p, bl, block_size_m,
                                                    block_size_n, enable_autotuning, return_softmax_lse,
-                                                   False, True, None, True, "balanced", False, 1, 0, ll)
+                                                   False, True, None, True, "balanced", False, 1, 0, ll, causal_shift)
             o_l, lse_l = res if return_softmax_lse else (res, None)
             outs.append((shard, o_l.to(home, non_blocking=True)))
             if lse_l is not None:

@@ -48,7 +48,7 @@ class Params(ctypes.Structure):
         ("dtype", ctypes.c_int32), ("causal", ctypes.c_int32),
         ("variant", ctypes.c_int32), ("device", ctypes.c_int32),
         ("scale", ctypes.c_float), ("dropout_p", ctypes.c_float),
-        ("bwd_phases", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("bwd_phases", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
         ("bias", Tensor4), ("d_scores", ctypes.c_void_p), ("kv_lengths", ctypes.c_void_p),
     ]
 

@@ -126,7 +126,7 @@ def _lengths_operand(key_lengths: Optional[torch.Tensor], q: torch.Tensor):
     return kl.data_ptr(), kl
 
 
-def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset) -> _cabi.Params:
+def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift=0) -> _cabi.Params:
     p = _cabi.Params()
     p.struct_bytes = ctypes.sizeof(_cabi.Params)
     p.q, p.k, p.v, p.o = _tensor4(q), _tensor4(k), _tensor4(v), _tensor4(o)
@@ -135,6 +135,7 @@ def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset) -> _ca
     p.Nk, p.Hkv = k.shape[1], k.shape[2]
     p.dtype = dtype_enum(q.dtype)
     p.causal = int(bool(causal))
+    p.causal_shift = int(causal_shift) if causal else 0
     p.variant = getattr(_variant_override, "value", _cabi.VARIANT_AUTO)
     p.device = q.device.index if q.device.index is not None else torch.cuda.current_device()
     p.scale = float(scale)
@@ -146,7 +147,7 @@ def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset) -> _ca
 
 
 def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None, bias=None,
-                   key_lengths=None):
+                   key_lengths=None, causal_shift=0):
     """o, lse <- fa_b200_fwd.  Counterpart of flash_attention_forward_triton_enhanced
     (kernels/forward_kernel.py:246-387); returns (o, lse).  `out=(o, lse)` writes into
     caller-owned buffers (o like q, lse (B, H, Nq) fp32 contiguous) instead of allocating."""
@@ -155,7 +156,7 @@ def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=
     else:
         o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
-    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset)
+    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift)
     p.bias, _keep = _bias_operand(bias)        # scores = scale * q.k + bias (CUDA-core kernels)
     p.kv_lengths, _keep_len = _lengths_operand(key_lengths, q)
     rc = _cabi.load().fa_b200_fwd(ctypes.byref(p))
@@ -164,7 +165,7 @@ def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=
 
 
 def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None,
-                    workspace=None, bias=None, d_scores=None, key_lengths=None):
+                    workspace=None, bias=None, d_scores=None, key_lengths=None, causal_shift=0):
     """dq, dk, dv <- fa_b200_bwd.  Counterpart of
     flash_attention_backward_triton_enhanced (kernels/backward_kernel.py:208-318).
     `out=(dq, dk, dv)` and `workspace` (uint8, at least fa_b200_bwd_workspace_bytes)
@@ -176,7 +177,7 @@ def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, 
         dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
         dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
-    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset)
+    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift)
     p.d_o, p.dq, p.dk, p.dv = _tensor4(d_o), _tensor4(dq), _tensor4(dk), _tensor4(dv)
     p.bias, _keep = _bias_operand(bias)
     p.kv_lengths, _keep_len = _lengths_operand(key_lengths, q)
@@ -251,8 +252,8 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
                 enable_gradient_checkpointing: bool = False, enable_mixed_precision: bool = True,
                 num_checkpoints: Optional[int] = None, memory_efficient: bool = True,
                 performance_mode: str = "balanced", enable_multi_gpu: bool = False,
-                world_size: int = 1, rank: int = 0, key_lengths: Optional[torch.Tensor] = None
-                ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
+                world_size: int = 1, rank: int = 0, key_lengths: Optional[torch.Tensor] = None,
+                causal_shift: int = 0) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
         # block sizes, autotuning, checkpointing, mixed precision and the
         # multi-GPU arguments are accepted for source compatibility: tiles come
         # from the static table, the backward always recomputes P, and sharding
@@ -263,9 +264,13 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
             seed, offset = _next_dropout_stream()
         # key_lengths (one int per batch entry, after the reference's 19 parameters): batch entry b
         # attends to its first key_lengths[b] keys only
-        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias, key_lengths=key_lengths)
+        # causal_shift: key j is visible to query i iff j <= i + causal_shift (0: the reference's top-left
+        # alignment; Nk - Nq: bottom-right)
+        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias, key_lengths=key_lengths,
+                                causal_shift=causal_shift)
         ctx.save_for_backward(q, k, v, o, lse, *([bias] if bias is not None else []))
         ctx.key_lengths = key_lengths
+        ctx.causal_shift = int(causal_shift)
         ctx.scale, ctx.causal, ctx.dropout_p = scale, bool(causal), float(dropout_p)
         ctx.seed, ctx.offset = seed, offset
         ctx.return_softmax_lse = bool(return_softmax_lse)
@@ -286,13 +291,13 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
                                    device=q.device)
         dq, dk, dv = launch_backward(grad_output, q, k, v, o, lse, ctx.scale, ctx.causal,
                                      ctx.dropout_p, ctx.seed, ctx.offset, bias=bias, d_scores=d_scores,
-                                     key_lengths=ctx.key_lengths)
+                                     key_lengths=ctx.key_lengths, causal_shift=ctx.causal_shift)
         if d_scores is not None:
             dims = [i for i in range(4) if bias.shape[i] == 1 and d_scores.shape[i] != 1]
             grad_bias = (d_scores.sum(dim=dims, keepdim=True) if dims else d_scores).to(bias.dtype)
         return (dq if ctx.needs_input_grad[0] else None,
                 dk if ctx.needs_input_grad[1] else None,
-                dv if ctx.needs_input_grad[2] else None, None, None, None, grad_bias) + (None,) * 13
+                dv if ctx.needs_input_grad[2] else None, None, None, None, grad_bias) + (None,) * 14
 
 
 def flash_attention_forward_enhanced(q, k, v, scale: Optional[float] = None, causal: bool = False,

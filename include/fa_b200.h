@@ -98,7 +98,7 @@ typedef struct fa_b200_params {
     uint64_t       seed, offset;   /* dropout stream (Philox key / counter word)   */
     int32_t        B, Nq, Nk, H, Hkv, D;
     int32_t        dtype;          /* fa_b200_dtype                                */
-    int32_t        causal;         /* key j visible to query i iff j <= i          */
+    int32_t        causal;         /* key j visible to query i iff j <= i + causal_shift */
     int32_t        variant;        /* fa_b200_variant                              */
     int32_t        device;         /* CUDA ordinal the pointers live on            */
     float          scale;          /* scores = scale * q.k                         */
@@ -108,7 +108,9 @@ typedef struct fa_b200_params {
                                       alone: 1 = preprocess (delta, scaled lse),
                                       2 = dK/dV kernel, 4 = dQ kernel.  Bits 2 and 4 need
                                       a workspace that an earlier call with bit 1 filled. */
-    int32_t        reserved;
+    int32_t        causal_shift;   /* >= 0; 0 aligns the mask's diagonal with the top-left corner (the
+                                      reference, kernels/forward_kernel.py:179-182), Nk - Nq with the
+                                      bottom-right one (the last query sees every key)                */
     /* Additive score bias, scores = scale * q.k + bias (reference kernels/forward_kernel.py:171-176;
        the reference's backward ignores it and returns a zero grad_bias, ops/attention.py:297-301).
        fp32, logical shape (B, H, Nq, Nk): stride_b / stride_h / stride_n are the element strides over

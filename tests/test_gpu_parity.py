@@ -435,3 +435,49 @@ def test_key_lengths_equal_a_padding_mask(device, dtype, D, causal):
     o2.backward(gd)
     _check("O (autograd)", o2, ro, tolerance(dtype))
     _check("dK (autograd)", k2.grad, rdk, tolerance(dtype))
+
+
+@pytest.mark.parametrize("dtype,D,H,Hkv", [(torch.bfloat16, 128, 4, 2), (torch.float16, 64, 2, 2), (torch.float32, 32, 2, 1)],
+                         ids=["bf16-d128-gqa", "fp16-d64", "fp32-d32"])
+@pytest.mark.parametrize("Nq,Nk", [(128, 384), (100, 333), (1, 500), (300, 301), (256, 256)])
+def test_bottom_right_causal_alignment(device, dtype, D, H, Hkv, Nq, Nk):
+    """causal_shift = Nk - Nq moves the mask's diagonal to the bottom-right corner: the same result as
+    the oracle with that mask as a 0 / -inf bias, on every kernel family (shifts that are and are not
+    multiples of the 128-row tile, one query against a long cache, and the square case)."""
+    B, shift = 2, Nk - Nq
+    q, d_o = _rand((B, Nq, H, D), dtype, 80), _rand((B, Nq, H, D), dtype, 83)
+    k, v = _rand((B, Nk, Hkv, D), dtype, 81), _rand((B, Nk, Hkv, D), dtype, 82)
+    i, j = torch.arange(Nq)[:, None], torch.arange(Nk)[None, :]
+    mask = torch.zeros(1, 1, Nq, Nk).masked_fill_((j > i + shift)[None, None], float("-inf"))
+    ro, rlse, rdq, rdk, rdv = ao.attention_forward_backward(q.float(), k.float(), v.float(), d_o.float(),
+                                                            causal=False, bias=mask)
+    qd, kd, vd, gd = (t.to(device) for t in (q, k, v, d_o))
+    for variant in _variants(dtype, D):
+        tol = tolerance(dtype, variant, D)
+        with kernel_variant(variant):
+            o, lse = launch_forward(qd, kd, vd, D ** -0.5, True, causal_shift=shift)
+            dq, dk, dv = launch_backward(gd, qd, kd, vd, o, lse, D ** -0.5, True, causal_shift=shift)
+        for name, got, ref in (("O", o, ro), ("LSE", lse, rlse), ("dQ", dq, rdq), ("dK", dk, rdk), ("dV", dv, rdv)):
+            _check(f"{name} [{variant}]", got, ref, tol)
+    q2, k2, v2 = (t.clone().requires_grad_(True) for t in (qd, kd, vd))
+    o2 = fa.flash_attention_v100(q2, k2, v2, causal=True, causal_alignment="bottom_right", enable_multi_gpu=False)
+    o2.backward(gd)
+    _check("O (autograd)", o2, ro, tolerance(dtype))
+    _check("dK (autograd)", k2.grad, rdk, tolerance(dtype))
+    if Nq == Nk:
+        o3 = fa.flash_attention_v100(qd, kd, vd, causal=True, enable_multi_gpu=False)
+        assert torch.equal(o2.detach(), o3)
+
+
+def test_bottom_right_rejections(device):
+    q = torch.zeros(1, 64, 1, 64, dtype=torch.float16, device=device)
+    k = torch.zeros(1, 32, 1, 64, dtype=torch.float16, device=device)
+    with pytest.raises(ValueError, match="Nk >= Nq"):
+        fa.flash_attention_v100(q, k, k, causal=True, causal_alignment="bottom_right")
+    with pytest.raises(ValueError, match="key_lengths"):
+        fa.flash_attention_v100(k, q, q, causal=True, causal_alignment="bottom_right",
+                                key_lengths=torch.tensor([10], device=device))
+    with pytest.raises(ValueError, match="causal_alignment"):
+        fa.flash_attention_v100(q, q, q, causal=True, causal_alignment="middle")
+    with pytest.raises(ValueError, match="negative"):
+        launch_forward(q, q, q, 0.125, True, causal_shift=-1)

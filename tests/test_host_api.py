@@ -146,7 +146,7 @@ def test_public_signatures_match_the_reference():
         "q", "k", "v", "causal", "scale", "dropout_p", "bias", "block_size_m", "block_size_n",
         "enable_autotuning", "return_softmax_lse", "optimization_strategy", "enable_multi_gpu",
         "enable_profiling", "fallback_on_error", "validate_inputs",     # reference interface.py:199-217
-        "key_lengths"]                                                   # this build's addition, last and optional
+        "key_lengths", "causal_alignment"]                                                   # this build's addition, last and optional
     assert sig.parameters["causal"].default is False and sig.parameters["dropout_p"].default == 0.0
     fwd = inspect.signature(fa.FlashAttentionV100Function.forward)
     assert list(fwd.parameters)[1:] == [
@@ -154,7 +154,7 @@ def test_public_signatures_match_the_reference():
         "enable_autotuning", "return_softmax_lse", "enable_gradient_checkpointing",
         "enable_mixed_precision", "num_checkpoints", "memory_efficient", "performance_mode",
         "enable_multi_gpu", "world_size", "rank",                          # reference ops/attention.py:50-72
-        "key_lengths"]                                                     # addition, after the reference's 19
+        "key_lengths", "causal_shift"]                                                     # addition, after the reference's 19
     mgr = inspect.signature(fa.FlashAttentionV100Manager.__init__)
     assert list(mgr.parameters)[1:] == ["enable_multi_gpu", "optimization_strategy", "enable_profiling"]
     assert fa.SUPPORTED_DTYPES == {torch.float16, torch.bfloat16, torch.float32}
@@ -189,3 +189,17 @@ def test_manager_is_a_context_manager_and_caches_configs():
     c1 = m.get_optimal_config(1024, 1024, 8, 64)
     assert m.get_optimal_config(1024, 1024, 8, 64) is c1
     assert m.get_optimal_config(1024, 1024, 8, 64, force_recompute=True) is not c1
+
+
+def test_causal_shift_of_the_alignments():
+    from flash_attention_v100.interface import _causal_shift
+    assert _causal_shift(True, "top_left", 10, 50, None) == 0
+    assert _causal_shift(True, "bottom_right", 10, 50, None) == 40
+    assert _causal_shift(True, "bottom_right", 50, 50, None) == 0
+    assert _causal_shift(False, "bottom_right", 50, 10, None) == 0      # no mask: nothing to align
+    with pytest.raises(ValueError):
+        _causal_shift(True, "bottom_right", 50, 10, None)
+    with pytest.raises(ValueError):
+        _causal_shift(True, "bottom_right", 10, 50, object())
+    with pytest.raises(ValueError):
+        _causal_shift(True, "center", 10, 10, None)
