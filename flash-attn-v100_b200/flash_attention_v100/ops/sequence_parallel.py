@@ -148,7 +148,11 @@ class CudaBlockKernels:
 
     @staticmethod
     def backward_block(d_o, q, k, v, o, lse, scale, causal):
-        return _ops.launch_backward(d_o, q, k, v, o, lse, scale, causal)
+        """(dq, dkv): dK and dV share one (2, B, Nk, Hkv, D) tensor, which one combine launch folds in."""
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dkv = torch.empty((2,) + tuple(k.shape), dtype=k.dtype, device=k.device)
+        _ops.launch_backward(d_o, q, k, v, o, lse, scale, causal, out=(dq, dkv[0], dkv[1]))
+        return dq, dkv
 
     combine = staticmethod(_ops.launch_combine)
 
@@ -215,25 +219,24 @@ def ring_backward(d_o, q, k, v, o, lse, scale: float, causal: bool, ring, kernel
                 lse_rows = lse_upper
             else:
                 lse_rows = lse
-            dq_p, dk_p, dv_p = kernels.backward_block(d_o[:, rows], q[:, rows], cur[0][:, keys], cur[1][:, keys],
-                                                      o[:, rows], lse_rows, scale, mode == "causal")
+            dq_p, dkv_p = kernels.backward_block(d_o[:, rows], q[:, rows], cur[0][:, keys], cur[1][:, keys],
+                                                 o[:, rows], lse_rows, scale, mode == "causal")
             final = t == last and t in whole
             kernels.combine(dq_acc[:, rows], dq_p, out=dq if final else None, first=(t == 0))
             written = written or final
         ring.wait(coming)
         if mode != "skip":
-            kernels.combine(dkv[t % 2][0][:, keys], dk_p, first=(t == 0))
-            kernels.combine(dkv[t % 2][1][:, keys], dv_p, first=(t == 0))
+            # dK and dV in one launch: (2, B, n, Hkv, D) seen as 2 B batch entries
+            kernels.combine(dkv[t % 2].flatten(0, 1)[:, keys], dkv_p.flatten(0, 1), first=(t == 0))
         coming = ring.exchange(dkv[t % 2], dkv[(t + 1) % 2])   # after the last step: the way home
         ring.wait(pending)
     if not written:
         kernels.combine(dq_acc, None, out=dq)
     ring.wait(coming)
     home = dkv[world % 2]
-    dk, dv = torch.empty_like(k), torch.empty_like(v)
-    kernels.combine(home[0], None, out=dk)
-    kernels.combine(home[1], None, out=dv)
-    return dq, dk, dv
+    dkv_out = torch.empty(home.shape, dtype=k.dtype, device=k.device)
+    kernels.combine(home.flatten(0, 1), None, out=dkv_out.flatten(0, 1))
+    return dq, dkv_out[0], dkv_out[1]
 
 
 class RingAttentionFunction(torch.autograd.Function):

@@ -62,7 +62,7 @@ class OracleBlockKernels:
     @staticmethod
     def backward_block(d_o, q, k, v, o, lse, scale, causal):
         dq, dk, dv = orc.attention_backward_closed_form(q, k, v, o, lse, d_o, causal=causal, scale=scale)
-        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+        return dq.to(q.dtype), torch.stack((dk.to(k.dtype), dv.to(v.dtype)))
 
     @staticmethod
     def combine(acc, part=None, lse_acc=None, lse_part=None, out=None, first=False):
