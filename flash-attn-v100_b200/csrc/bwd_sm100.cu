@@ -728,9 +728,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         PSET(c4 * 4 + 3, ex2(x3));
                     }
                     if (diag) {
+                        const int hidden = row_g - col_g0 - a.shift;   // my first `hidden` columns: query + shift < key
 #pragma unroll
                         for (int c = hf * (CPT / 2); c < (hf + 1) * (CPT / 2); ++c)
-                            if (row_g > col_g0 + c + a.shift) PSET(c, 0.f);
+                            if (c < hidden) PSET(c, 0.f);
                     }
                     if (row_g >= nk) {                    // a padding key inside a live tile (or beyond Nk)
 #pragma unroll

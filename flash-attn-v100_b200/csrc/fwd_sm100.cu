@@ -398,11 +398,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     const int col0 = j * kBlockN;
                     const bool need_mask = (a.causal && col0 + kBlockN - 1 > tile * kBlockM + a.shift) || (col0 + kBlockN > nk);
                     if (need_mask) {
+                        // my row sees the block's first `seen` columns: keys below the count, at most i + shift
+                        int seen = nk - col0;
+                        if (a.causal && i + a.shift + 1 - col0 < seen) seen = i + a.shift + 1 - col0;
 #pragma unroll
-                        for (int c = 0; c < 128; ++c) {
-                            const int col = col0 + c;
-                            if (col >= nk || (a.causal && col > i + a.shift)) SSET(c, -INFINITY);
-                        }
+                        for (int c = 0; c < 128; ++c)
+                            if (c >= seen) SSET(c, -INFINITY);
                     }
                     float mx0 = SF(0), mx1 = SF(1), mx2 = SF(2), mx3 = SF(3);
 #pragma unroll
