@@ -30,7 +30,8 @@ struct CombineArgs {
     int64_t acc_sb;             // batch stride of acc (elements); rows of one batch entry are dense
     int64_t lse_sb, lse_sh;     // batch and head strides of lse_acc (lse_part is dense)
     int N, H, D;
-    int64_t n_chunks;           // B * N * H * D / 8
+    int64_t n_chunks;           // B * N * H * 2^cshift
+    int cshift;                 // 2^cshift >= D / 8
     int first;
 };
 
@@ -82,18 +83,25 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const fl
     *reinterpret_cast<uint4*>(p) = r;
 }
 
-// MERGE: weights from the two log-sum-exps; otherwise a plain sum.
-template <typename T, bool MERGE>
+// MERGE: weights from the two log-sum-exps; otherwise a plain sum.  Idx: the type the element index is
+// taken apart in (32-bit whenever the tensor allows it: 64-bit divisions are emulated and would
+// make this streaming kernel ALU-bound).
+template <typename T, bool MERGE, typename Idx>
 __global__ void __launch_bounds__(256) combine_kernel(const CombineArgs a) {
-    const int cpr = a.D >> 3;                                   // 8-element chunks per (b, n, h) row
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < a.n_chunks;
-         idx += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t row = idx / cpr;                          // (b * N + n) * H + h
-        const int c = (int)(idx - row * cpr);
-        const int h = (int)(row % a.H);
-        const int64_t bn = row / a.H;
-        const int n = (int)(bn % a.N);
-        const int64_t b = bn / a.N;
+    // A (b, n, h) row of D / 8 chunks takes 2^cshift consecutive threads (the surplus ones idle), so a
+    // row never straddles a warp: its threads read the old log-sum-exp with one warp-wide load, on
+    // which the one store of the new value depends.
+    const int cpr = a.D >> 3;
+    const Idx total = (Idx)a.n_chunks, step = (Idx)(gridDim.x * blockDim.x);
+    for (Idx idx = (Idx)(blockIdx.x * blockDim.x + threadIdx.x); idx < total; idx += step) {
+        const Idx row_i = idx >> a.cshift;                      // (b * N + n) * H + h
+        const int c = (int)(idx & (Idx)((1 << a.cshift) - 1));
+        if (c >= cpr) continue;
+        const Idx bn = row_i / (Idx)a.H;
+        const int h = (int)(row_i - bn * (Idx)a.H);
+        const Idx b_i = bn / (Idx)a.N;
+        const int n = (int)(bn - b_i * (Idx)a.N);
+        const int64_t b = (int64_t)b_i;
         float wa = a.first ? 0.f : 1.f, wp = a.part ? 1.f : 0.f;
         if (MERGE) {
             const int64_t li = b * a.lse_sb + h * a.lse_sh + n;
@@ -137,8 +145,15 @@ int launch(const CombineArgs& a, bool merge, int device, cudaStream_t stream) {
     int64_t blocks = (a.n_chunks + 255) / 256;
     const int64_t cap = (int64_t)sms * 8;                       // 8 resident CTAs of 256 threads per SM
     if (blocks > cap) blocks = cap;
-    if (merge) combine_kernel<T, true><<<(unsigned)blocks, 256, 0, stream>>>(a);
-    else       combine_kernel<T, false><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    // idx + one grid stride must not wrap
+    const bool small = a.n_chunks + blocks * 256 < (int64_t)0x7fffffff;
+    if (merge) {
+        if (small) combine_kernel<T, true, uint32_t><<<(unsigned)blocks, 256, 0, stream>>>(a);
+        else       combine_kernel<T, true, int64_t><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    } else {
+        if (small) combine_kernel<T, false, uint32_t><<<(unsigned)blocks, 256, 0, stream>>>(a);
+        else       combine_kernel<T, false, int64_t><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    }
     FA_CUDA_CHECK(cudaGetLastError());
     return FA_OK;
 }
@@ -156,6 +171,7 @@ extern "C" int fa_b200_combine(const fa_b200_combine_params* p) {
         return FA_EINVAL;
     }
     if (p->B < 0 || p->N < 0 || p->H < 0 || p->D <= 0) { set_error("negative size"); return FA_EINVAL; }
+    if (p->D > 256) { set_error("D=%d: the combination kernel takes rows of at most 256 elements", p->D); return FA_EUNSUPPORTED; }
     if (p->D % 8 != 0) { set_error("D=%d: the combination kernel moves 8 elements per thread", p->D); return FA_EUNSUPPORTED; }
     if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_F32) {
         set_error("bad dtype %d", p->dtype);
@@ -189,7 +205,9 @@ extern "C" int fa_b200_combine(const fa_b200_combine_params* p) {
     a.acc_sb = p->acc_stride_b ? p->acc_stride_b : (int64_t)p->N * p->H * p->D;
     a.lse_sb = p->lse_stride_b ? p->lse_stride_b : (int64_t)p->H * p->N;
     a.lse_sh = p->lse_stride_h ? p->lse_stride_h : (int64_t)p->N;
-    a.n_chunks = rows * (p->D / 8);
+    a.cshift = 0;
+    while ((1 << a.cshift) < p->D / 8) ++a.cshift;
+    a.n_chunks = rows << a.cshift;
     a.first = p->first ? 1 : 0;
     int prev = -1;
     if (cudaGetDevice(&prev) != cudaSuccess) { set_error("cudaGetDevice failed"); return FA_ECUDA; }

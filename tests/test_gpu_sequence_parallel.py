@@ -15,9 +15,10 @@ from ring_helpers import OracleBlockKernels, run_ring
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("D", [64, 40, 8, 128])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-def test_combine_merge_matches_formula(device, dtype):
-    B, N, H, D = 2, 70, 3, 64
+def test_combine_merge_matches_formula(device, dtype, D):
+    B, N, H = 2, 70, 3
     g = torch.Generator().manual_seed(1)
     wide = torch.randn(3, B, N, H, 2 * D, generator=g).to(dtype).to(device)
     parts = [wide[i, ..., :D] for i in range(3)]                     # strided views: row pitch 2 D
