@@ -367,5 +367,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return r;
 }
 
+// Programmatic dependent launch.  launch_dependents: the next kernel in the stream, if it was launched
+// with programmatic stream serialization, may start once every CTA of this grid has got here (or left).
+// dependency_wait: returns when the grids this one was serialized behind have completed and their
+// writes are visible.  Both do nothing in a launch without the attribute.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 }  // namespace ptx
 }  // namespace fa
