@@ -44,3 +44,21 @@ def test_main_json_on_gpu(capsys, device):
     res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert res["shape"] == [2, 512, 4, 64] and res["fwd_ms"] > 0 and res["bwd_ms"] > 0
     assert res["fwd_bwd_tflops"] > 0
+
+
+@pytest.mark.gpu
+def test_sequence_parallel_mode_on_one_gpu(capsys, device, monkeypatch):
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    for k, v in (("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", str(port)), ("RANK", "0"), ("WORLD_SIZE", "1"),
+                 ("LOCAL_RANK", "0")):
+        monkeypatch.setenv(k, v)
+    rc = cli.main(["--sequence-parallel", "zigzag", "--batch", "1", "--seq-len", "512", "--heads", "2",
+                   "--head-dim", "64", "--steps", "2", "--warmup", "1", "--json"])
+    assert rc == 0
+    res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert res["n_gpus"] == 1 and res["per_rank"] == 512 and res["layout"] == "zigzag"
+    assert res["ms_per_step"] > 0 and res["fwd_bwd_tflops"] > 0
