@@ -203,3 +203,33 @@ def test_causal_shift_of_the_alignments():
         _causal_shift(True, "bottom_right", 10, 50, object())
     with pytest.raises(ValueError):
         _causal_shift(True, "center", 10, 10, None)
+
+
+def test_combine_operand_checks_need_no_device():
+    """launch_combine refuses malformed operands before it touches the library."""
+    from flash_attention_v100.ops.attention import launch_combine
+    acc = torch.zeros(1, 8, 2, 64)
+    part = torch.zeros(1, 8, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="partial, an output"):
+        launch_combine(acc)
+    with pytest.raises(ValueError, match="fp32"):
+        launch_combine(acc.half(), part)
+    with pytest.raises(ValueError, match="dense within a batch entry"):
+        launch_combine(torch.zeros(1, 8, 2, 128)[..., :64], part)
+    with pytest.raises(ValueError, match="same dtype"):
+        launch_combine(acc, part, out=torch.zeros(1, 8, 2, 64, dtype=torch.float16))
+    with pytest.raises(ValueError, match="lse_acc"):
+        launch_combine(acc, part, lse_acc=torch.zeros(1, 8, 2), lse_part=torch.zeros(1, 2, 8))
+    with pytest.raises(ValueError, match="lse_part"):
+        launch_combine(acc, part, lse_acc=torch.zeros(1, 2, 8), lse_part=torch.zeros(1, 2, 8, dtype=torch.float64))
+
+
+def test_combine_params_struct_matches_the_header():
+    """Field order and size of fa_b200_combine_params as the header declares them (LP64)."""
+    header = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "fa_b200.h")).read()
+    body = header[header.index("typedef struct fa_b200_combine_params {"):header.index("} fa_b200_combine_params;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = re.findall(r"\b(\w+)(?:, (\w+))?(?:, (\w+))?(?:, (\w+))?;", body)
+    declared = [n for group in names for n in group if n]
+    assert declared == [f[0] for f in _cabi.CombineParams._fields_]
+    assert ctypes.sizeof(_cabi.CombineParams) == 8 + 8 + 8 + 32 + 8 + 32 + 4 * 8 + 8 + 3 * 8
