@@ -37,11 +37,14 @@ from typing import Optional, Tuple
 import torch
 
 
-def _scores(q, k, scale, causal, bias=None):
+def _scores(q, k, scale, causal, bias=None, causal_shift=0):
     """(B,H,Nq,Nk) scaled, masked scores; reference __init__.py:36-48.  `bias`
     (broadcastable to (B,H,Nq,Nk)) is added after the scaling and before the
     causal mask, as the reference's test twin does (tests/test_attention.py:48-58)
-    and its forward kernel intends (kernels/forward_kernel.py:171-176)."""
+    and its forward kernel intends (kernels/forward_kernel.py:171-176).
+    `causal_shift` moves the mask's diagonal: key j is hidden iff j > i + shift.
+    0 is the reference's mask; the reference has no other (Nk - Nq gives the
+    bottom-right alignment, which has no counterpart there)."""
     qt = q.transpose(1, 2)
     kt = k.transpose(1, 2)
     hq, hk = qt.shape[1], kt.shape[1]
@@ -53,7 +56,7 @@ def _scores(q, k, scale, causal, bias=None):
     if causal:
         nq, nk = s.shape[-2], s.shape[-1]
         # reference: triu(ones(seq, seq), diagonal=1) -> key j masked iff j > i
-        mask = torch.triu(torch.ones(nq, nk, device=s.device), diagonal=1).bool()
+        mask = torch.triu(torch.ones(nq, nk, device=s.device), diagonal=1 + int(causal_shift)).bool()
         s = s.masked_fill(mask, float("-inf"))
     return s
 
@@ -61,8 +64,8 @@ def _scores(q, k, scale, causal, bias=None):
 def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                       causal: bool = False, scale: Optional[float] = None,
                       dropout_p: float = 0.0, keep_mask: Optional[torch.Tensor] = None,
-                      compute_dtype: torch.dtype = torch.float32, bias: Optional[torch.Tensor] = None
-                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+                      compute_dtype: torch.dtype = torch.float32, bias: Optional[torch.Tensor] = None,
+                      causal_shift: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
     """Dense attention, returns (O (B,Nq,H,D), LSE (B,H,Nq)) in compute_dtype.
 
     Follows reference __init__.py:30-55 step by step; `keep_mask` (B,H,Nq,Nk)
@@ -74,7 +77,7 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     v = v.to(compute_dtype)
     if scale is None:
         scale = q.shape[-1] ** -0.5          # reference __init__.py:32
-    s = _scores(q, k, scale, causal, bias)
+    s = _scores(q, k, scale, causal, bias, causal_shift)
     lse = torch.logsumexp(s, dim=-1)
     p = torch.softmax(s, dim=-1)             # reference __init__.py:50
     if keep_mask is not None:
@@ -87,7 +90,7 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
 
 
 def attention_forward_backward(q, k, v, d_o, *, causal=False, scale=None, dropout_p=0.0,
-                               keep_mask=None, compute_dtype=torch.float32, bias=None):
+                               keep_mask=None, compute_dtype=torch.float32, bias=None, causal_shift=0):
     """(O, LSE, dQ, dK, dV) with gradients from autograd through the restated
     forward (the same route a user of the reference's math path takes).  With a
     `bias` that requires grad, its gradient is left in bias.grad."""
@@ -95,7 +98,8 @@ def attention_forward_backward(q, k, v, d_o, *, causal=False, scale=None, dropou
     k = k.detach().to(compute_dtype).requires_grad_(True)
     v = v.detach().to(compute_dtype).requires_grad_(True)
     o, lse = attention_forward(q, k, v, causal=causal, scale=scale, dropout_p=dropout_p,
-                               keep_mask=keep_mask, compute_dtype=compute_dtype, bias=bias)
+                               keep_mask=keep_mask, compute_dtype=compute_dtype, bias=bias,
+                               causal_shift=causal_shift)
     o.backward(d_o.to(compute_dtype))
     return o.detach(), lse.detach(), q.grad, k.grad, v.grad
 

@@ -152,3 +152,25 @@ def test_host_dropout_mask_matches_oracle_definition(p):
         assert abs((1 - out.mean()) - eff) < 0.03
     else:
         assert out.all()
+
+
+@pytest.mark.parametrize("nq,nk", [(5, 12), (7, 7), (1, 9)])
+def test_causal_shift_equals_the_same_mask_given_as_a_bias(nq, nk):
+    """The shifted diagonal (bottom-right alignment at shift = Nk - Nq) against the reference's own
+    mechanism for arbitrary masks, a 0 / -inf bias; shift 0 is the reference's mask."""
+    import torch
+    from oracle import attention_oracle as ao
+    g = torch.Generator().manual_seed(11)
+    q, d_o = torch.randn(2, nq, 3, 8, generator=g), torch.randn(2, nq, 3, 8, generator=g)
+    k, v = torch.randn(2, nk, 3, 8, generator=g), torch.randn(2, nk, 3, 8, generator=g)
+    shift = nk - nq
+    i, j = torch.arange(nq)[:, None], torch.arange(nk)[None, :]
+    mask = torch.zeros(1, 1, nq, nk).masked_fill_((j > i + shift)[None, None], float("-inf"))
+    a = ao.attention_forward_backward(q, k, v, d_o, causal=True, causal_shift=shift)
+    b = ao.attention_forward_backward(q, k, v, d_o, causal=False, bias=mask)
+    for x, y in zip(a, b):
+        assert torch.allclose(x, y, rtol=1e-6, atol=1e-6)
+    if shift == 0:
+        c = ao.attention_forward_backward(q, k, v, d_o, causal=True)
+        for x, y in zip(a, c):
+            assert torch.equal(x, y)
