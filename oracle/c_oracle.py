@@ -39,7 +39,7 @@ def _p(a, t=ctypes.c_float):
     return a.ctypes.data_as(ctypes.POINTER(t))
 
 
-def forward(q, k, v, causal=False, scale=None, keep=None, dropout_p=0.0):
+def forward(q, k, v, causal=False, scale=None, keep=None, dropout_p=0.0, causal_shift=0):
     """q (B,Nq,H,D), k/v (B,Nk,Hkv,D) numpy -> (o, lse) float32."""
     q, k, v = _f32(q), _f32(k), _f32(v)
     B, Nq, H, D = q.shape
@@ -52,13 +52,13 @@ def forward(q, k, v, causal=False, scale=None, keep=None, dropout_p=0.0):
     if keep is not None:
         keep = np.ascontiguousarray(keep, dtype=np.uint8)
         kp = _p(keep, ctypes.c_uint8)
-    rc = lib().fa_oracle_forward(_p(q), _p(k), _p(v), B, Nq, Nk, H, Hkv, D, int(causal),
+    rc = lib().fa_oracle_forward(_p(q), _p(k), _p(v), B, Nq, Nk, H, Hkv, D, (1 + int(causal_shift)) if causal else 0,
                                  ctypes.c_double(scale), kp, ctypes.c_double(dropout_p), _p(o), _p(lse))
     assert rc == 0
     return o, lse
 
 
-def backward(q, k, v, o, lse, d_o, causal=False, scale=None, keep=None, dropout_p=0.0):
+def backward(q, k, v, o, lse, d_o, causal=False, scale=None, keep=None, dropout_p=0.0, causal_shift=0):
     q, k, v, o, lse, d_o = (_f32(t) for t in (q, k, v, o, lse, d_o))
     B, Nq, H, D = q.shape
     Nk, Hkv = k.shape[1], k.shape[2]
@@ -70,7 +70,7 @@ def backward(q, k, v, o, lse, d_o, causal=False, scale=None, keep=None, dropout_
         keep = np.ascontiguousarray(keep, dtype=np.uint8)
         kp = _p(keep, ctypes.c_uint8)
     rc = lib().fa_oracle_backward(_p(q), _p(k), _p(v), _p(o), _p(lse), _p(d_o), B, Nq, Nk, H, Hkv, D,
-                                  int(causal), ctypes.c_double(scale), kp, ctypes.c_double(dropout_p),
+                                  (1 + int(causal_shift)) if causal else 0, ctypes.c_double(scale), kp, ctypes.c_double(dropout_p),
                                   _p(dq), _p(dk), _p(dv))
     assert rc == 0
     return dq, dk, dv

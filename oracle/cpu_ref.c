@@ -5,7 +5,8 @@
  * shipped package never does.
  *
  * Forward follows the reference's math path, __init__.py:36-54:
- *   scores = (q*scale).k^T  (:41)   causal: j > i -> -inf (:43-48)
+ *   scores = (q*scale).k^T  (:41)   causal: j > i -> -inf (:43-48); `causal` = 1 + shift hides
+ *   j > i + shift instead (shift 0 is the reference's mask, Nk - Nq the bottom-right alignment)
  *   P = softmax(scores) (:50)       O = P.v (:51)
  * on (B, N, H, D) contiguous float inputs (:34-38 transposes are index math
  * here).  Dropout follows the reference's test twin,
@@ -35,7 +36,7 @@ static double score_row(const float* q, const float* k, int b, int h, int hk, in
                         int Nq, int Nk, int H, int Hkv, int D, int causal, double scale, double* s) {
     double mx = -INFINITY;
     for (int j = 0; j < Nk; ++j) {
-        if (causal && j > i) { s[j] = -INFINITY; continue; }
+        if (causal && j > i + (causal - 1)) { s[j] = -INFINITY; continue; }
         double acc = 0.0;
         for (int d = 0; d < D; ++d)
             acc += ((double)q[IDX(b, i, h, d, Nq, H, D)] * scale) * (double)k[IDX(b, j, hk, d, Nk, Hkv, D)];
@@ -104,7 +105,7 @@ int fa_oracle_backward(const float* q, const float* k, const float* v, const flo
                     for (int d = 0; d < D; ++d) dqa[d] = 0.0;
                     const uint8_t* kr = keep ? keep + (((int64_t)b * H + h) * Nq + i) * Nk : NULL;
                     for (int j = 0; j < Nk; ++j) {
-                        if (causal && j > i) continue;
+                        if (causal && j > i + (causal - 1)) continue;
                         double p = exp(s[j] - l);
                         double z = kr ? (kr[j] ? zscale : 0.0) : 1.0;
                         double dp = 0.0;

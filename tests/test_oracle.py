@@ -174,3 +174,17 @@ def test_causal_shift_equals_the_same_mask_given_as_a_bias(nq, nk):
         c = ao.attention_forward_backward(q, k, v, d_o, causal=True)
         for x, y in zip(a, c):
             assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("nq,nk", [(5, 12), (6, 6)])
+def test_c_oracle_causal_shift_equals_the_torch_restatement(nq, nk):
+    g = torch.Generator().manual_seed(12)
+    q, d_o = torch.randn(1, nq, 2, 8, generator=g), torch.randn(1, nq, 2, 8, generator=g)
+    k, v = torch.randn(1, nk, 1, 8, generator=g), torch.randn(1, nk, 1, 8, generator=g)
+    shift = nk - nq
+    ro, rlse, rdq, rdk, rdv = ao.attention_forward_backward(q, k, v, d_o, causal=True, causal_shift=shift)
+    o, lse = c_oracle.forward(q.numpy(), k.numpy(), v.numpy(), causal=True, causal_shift=shift)
+    dq, dk, dv = c_oracle.backward(q.numpy(), k.numpy(), v.numpy(), o, lse, d_o.numpy(), causal=True,
+                                   causal_shift=shift)
+    for got, want in ((o, ro), (lse, rlse), (dq, rdq), (dk, rdk), (dv, rdv)):
+        assert np.allclose(got, want.numpy(), rtol=2e-5, atol=2e-5)
