@@ -1076,8 +1076,9 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         // Only behind the dK/dV kernel of this call, and only while one head's K and V are small
-        // beside L2: measured on B200 (H32 D128 bf16 causal) the overlap takes 1 % off the backward
-        // at N = 4096 and adds 1.5 % at N = 16384, where the two kernels' streams evict each other.
+        // beside L2 (the two kernels stream different heads' tiles at the same time): measured on
+        // B200 (H32 D128 bf16 causal) the overlap takes 1 % off the backward at N = 4096; longer
+        // sequences showed no gain.
         cfg.numAttrs = ((phases & 2) && (int64_t)p.Nk * D * 4 <= (int64_t)4 << 20) ? 1 : 0;
         FA_CUDA_CHECK(cudaLaunchKernelEx(&cfg, k1, mq, mg, mk, mv, mdq, mdq, a));
     }
