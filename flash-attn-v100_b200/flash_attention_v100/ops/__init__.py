@@ -21,6 +21,12 @@ from .memory import (
 )
 
 from .host_pipeline import HostAttentionStep, chunk_bounds, chunk_dropout_offset
+from .sequence_parallel import (
+    flash_attention_v100_sequence_parallel,
+    ring_schedule,
+    zigzag_split,
+    zigzag_merge,
+)
 
 __version__ = "0.1.0"
 
@@ -30,4 +36,5 @@ __all__ = [
     "allocate_attention_workspace", "free_attention_workspace", "estimate_peak_memory_usage",
     "get_memory_statistics", "backward_workspace_bytes",
     "HostAttentionStep", "chunk_bounds", "chunk_dropout_offset",
+    "flash_attention_v100_sequence_parallel", "ring_schedule", "zigzag_split", "zigzag_merge",
 ]
