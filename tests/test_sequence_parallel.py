@@ -154,9 +154,10 @@ def _gloo_rank(rank, world, port, causal, layout, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("causal,layout", [(False, "contiguous"), (True, "contiguous"), (True, "zigzag")])
-def test_distributed_ring_world2_gloo(causal, layout):
-    world, ctx = 2, mp.get_context("spawn")
+@pytest.mark.parametrize("world,causal,layout", [(2, False, "contiguous"), (2, True, "contiguous"),
+                                                 (2, True, "zigzag"), (3, True, "zigzag")])
+def test_distributed_ring_gloo(world, causal, layout):
+    ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
         procs = [ctx.Process(target=_gloo_rank, args=(r, world, port, causal, layout, ret))
