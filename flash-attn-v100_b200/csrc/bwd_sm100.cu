@@ -128,6 +128,7 @@ struct BwdArgs {
     uint32_t drop_thr;
     float inv_keep;
     PhiloxKey key;
+    DropoutOrigin rng;
 };
 
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -506,7 +507,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const int strm_tile = (KS) ? q_tile_of(qi) : it;     // query tile (0) / key tile (1)
             const int col_g0 = strm_tile * kTile + cb;                          // global index of my first column
             const int head_q = (KS) ? head_x * group + hg : head_x;
-            const uint32_t bh = (uint32_t)(b * a.H + head_q);
+            const uint32_t bh = dropout_column(a.rng, b, head_q);
             // key-stationary: -lse*log2(e) and -delta of this step's 128 queries (slot it & 1)
             const float* lse_s = sVec + (it & 1) * 256;
             const float* del_s = lse_s + 128;
@@ -1038,6 +1039,7 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     a.drop_thr = dropout_threshold(p.dropout_p);
     a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
     a.key = philox_make_key(p.seed, p.offset);
+    a.rng = dropout_origin_of(p);
 
     constexpr int kThreads = 128 * kNWG + kExtraThreads;
     const dim3 grid_kv((p.Nk + kTile - 1) / kTile, p.Hkv, p.B);

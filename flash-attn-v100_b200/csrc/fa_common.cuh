@@ -45,6 +45,15 @@ __device__ __forceinline__ int kv_len_of(const int32_t* lens, int b, int Nk) {
     return l < 1 ? 1 : (l > Nk ? Nk : l);
 }
 
+// Origin of the call's (batch, head) columns in the dropout stream (rng_heads = 0: the call is the whole problem).
+static inline DropoutOrigin dropout_origin_of(const fa_b200_params& p) {
+    DropoutOrigin o;
+    o.b0 = p.rng_batch_offset;
+    o.h0 = p.rng_head_offset;
+    o.heads = p.rng_heads > 0 ? p.rng_heads : p.H;
+    return o;
+}
+
 // ---- workspace layout (backward) -------------------------------------------
 // [ delta : B*H*nq_pad fp32 | pad to 256 | lse*log2(e) : B*H*nq_pad fp32 (tensor-core family only)
 //   | pad to 256 | dQ sums : B*H*nq_pad*D fp32 (one-kernel tensor-core backward only) ]

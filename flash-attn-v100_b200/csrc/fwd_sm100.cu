@@ -105,6 +105,7 @@ struct FwdArgs {
     uint32_t drop_thr;
     float inv_keep;
     PhiloxKey key;
+    DropoutOrigin rng;
 };
 
 struct Pair { int pair, h, b; };
@@ -379,7 +380,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 if (n == 0) continue;
                 const int tile = pr.pair * 2 + t;
                 const int i = tile * kBlockM + r;                    // global query row
-                const uint32_t bh = (uint32_t)(pr.b * a.H + pr.h);
+                const uint32_t bh = dropout_column(a.rng, pr.b, pr.h);
                 float m = -INFINITY, l = 0.f;
 
                 for (int j = 0; j < n; ++j) {
@@ -566,6 +567,7 @@ int launch(const fa_b200_params& p) {
     a.drop_thr = dropout_threshold(p.dropout_p);
     a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
     a.key = philox_make_key(p.seed, p.offset);
+    a.rng = dropout_origin_of(p);
     auto kernel = a.drop_thr ? fwd_sm100_kernel<D, BF16, true> : fwd_sm100_kernel<D, BF16, false>;
     FA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     const int sms = sm_count(p.device);

@@ -104,6 +104,13 @@ int validate_common(const fa_b200_params* p, bool backward) {
         return FA_EINVAL;
     }
     if (!(p->scale == p->scale)) { set_error("scale is NaN"); return FA_EINVAL; }
+    if (p->rng_batch_offset < 0 || p->rng_head_offset < 0 || p->rng_heads < 0 ||
+        (p->rng_heads == 0 && (p->rng_batch_offset || p->rng_head_offset)) ||
+        (p->rng_heads > 0 && (int64_t)p->rng_head_offset + p->H > p->rng_heads)) {
+        set_error("dropout stream origin (batch %d, head %d of %d heads) does not hold a call with %d heads",
+                  p->rng_batch_offset, p->rng_head_offset, p->rng_heads, p->H);
+        return FA_EINVAL;
+    }
     if (p->bwd_phases < 0 || p->bwd_phases > 7) { set_error("bwd_phases must be a mask in [0, 7]"); return FA_EINVAL; }
     if (p->B == 0 || p->Nq == 0) return FA_OK;   // empty problem: nothing else to check
     int rc;
@@ -145,6 +152,19 @@ int choose_variant(const fa_b200_params& p, bool backward, int* variant) {
     return FA_OK;
 }
 
+// Zero-fill of dK and dV for a call without queries (shared by both backward entry points).
+int zero_dk_dv(const fa_b200_params* p) {
+    size_t eb = dtype_bytes(p->dtype);
+    for (int b = 0; b < p->B; ++b)
+        for (int j = 0; j < p->Nk; ++j) {
+            FA_CUDA_CHECK(cudaMemset2DAsync((char*)p->dk.ptr + ((int64_t)b * p->dk.stride_b + (int64_t)j * p->dk.stride_n) * eb,
+                                            p->dk.stride_h * eb, 0, p->D * eb, p->Hkv, (cudaStream_t)p->stream));
+            FA_CUDA_CHECK(cudaMemset2DAsync((char*)p->dv.ptr + ((int64_t)b * p->dv.stride_b + (int64_t)j * p->dv.stride_n) * eb,
+                                            p->dv.stride_h * eb, 0, p->D * eb, p->Hkv, (cudaStream_t)p->stream));
+        }
+    return FA_OK;
+}
+
 }  // namespace
 }  // namespace fa
 
@@ -181,6 +201,24 @@ int fa_b200_fwd(const fa_b200_params* p) {
     return variant != FA_B200_VARIANT_SIMT ? sm100_fwd(*p) : simt_fwd(*p);
 }
 
+int fa_b200_copy_rows(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                      size_t row_bytes, size_t rows, int device, void* stream) {
+    if (row_bytes == 0 || rows == 0) return FA_OK;
+    if (!dst || !src) { set_error("copy_rows: null pointer"); return FA_EINVAL; }
+    if (dst_pitch < row_bytes || src_pitch < row_bytes) {
+        set_error("copy_rows: pitch (%zu, %zu) smaller than the row (%zu bytes)", dst_pitch, src_pitch, row_bytes);
+        return FA_EINVAL;
+    }
+    GuardDevice g(device);
+    if (!g.ok) { set_error("cudaSetDevice(%d) failed", device); return FA_ECUDA; }
+    if (dst_pitch == row_bytes && src_pitch == row_bytes)
+        FA_CUDA_CHECK(cudaMemcpyAsync(dst, src, row_bytes * rows, cudaMemcpyDefault, (cudaStream_t)stream));
+    else
+        FA_CUDA_CHECK(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, rows, cudaMemcpyDefault,
+                                        (cudaStream_t)stream));
+    return FA_OK;
+}
+
 size_t fa_b200_bwd_workspace_bytes(const fa_b200_params* p) {
     if (!p || p->struct_bytes != sizeof(fa_b200_params)) return 0;
     if (p->B <= 0 || p->Nq <= 0 || p->H <= 0 || p->Hkv <= 0 || p->D <= 0) return 256;
@@ -214,18 +252,7 @@ int fa_b200_bwd(const fa_b200_params* p) {
     }
     GuardDevice g(p->device);
     if (!g.ok) { set_error("cudaSetDevice(%d) failed", p->device); return FA_ECUDA; }
-    if (p->Nq == 0) {
-        // no queries: dK = dV = 0
-        size_t eb = dtype_bytes(p->dtype);
-        for (int b = 0; b < p->B; ++b)
-            for (int j = 0; j < p->Nk; ++j) {
-                FA_CUDA_CHECK(cudaMemset2DAsync((char*)p->dk.ptr + ((int64_t)b * p->dk.stride_b + (int64_t)j * p->dk.stride_n) * eb,
-                                                p->dk.stride_h * eb, 0, p->D * eb, p->Hkv, (cudaStream_t)p->stream));
-                FA_CUDA_CHECK(cudaMemset2DAsync((char*)p->dv.ptr + ((int64_t)b * p->dv.stride_b + (int64_t)j * p->dv.stride_n) * eb,
-                                                p->dv.stride_h * eb, 0, p->D * eb, p->Hkv, (cudaStream_t)p->stream));
-            }
-        return FA_OK;
-    }
+    if (p->Nq == 0) return zero_dk_dv(p);      // no queries: dK = dV = 0
     return variant != FA_B200_VARIANT_SIMT ? sm100_bwd(*p, ws) : simt_bwd(*p, ws);
 }
 
@@ -239,7 +266,8 @@ int fa_b200_bwd(const fa_b200_params* p) {
 // the scaled log-sum-exp, 8 bytes per padded query row) lives in a fixed array
 // in the library's own device image.  Every GPU that loads the library holds
 // these bytes until the process exits.
-constexpr size_t kStaticScratchBytes = 8u << 20;          // 8 MiB: B*H*ceil128(Nq) <= 1 Mi rows
+constexpr uint64_t kStaticScratchRows = 1u << 20;         // B * H * ceil128(Nq) a call may have
+constexpr size_t kStaticScratchBytes = 8u << 20;          // 8 MiB: two fp32 vectors of that many rows
 static __device__ __align__(256) unsigned char g_bwd_static_scratch[kStaticScratchBytes];
 
 namespace {
@@ -264,24 +292,35 @@ int static_scratch_address(int device, void** out) {
 }  // namespace
 
 int fa_b200_bwd_static(const fa_b200_params* p) {
+    // The size limit comes before everything else, pointers included: it needs the sizes only, and a
+    // call beyond it never gets near a launch whatever its other arguments are.  One limit for every
+    // kernel family (the CUDA-core family would fit twice as many rows; it is held to the same number).
+    if (p && p->struct_bytes == sizeof(fa_b200_params) && p->B > 0 && p->H > 0 && p->Nq > 0) {
+        const uint64_t rows = (uint64_t)p->B * (uint64_t)p->H * (uint64_t)align_up((size_t)p->Nq, 128);
+        if (rows > kStaticScratchRows) {
+            set_error("fa_b200_bwd_static: B*H*(Nq rounded up to 128) = %llu rows, the built-in array serves at most "
+                      "%llu (1048576); use fa_b200_bwd with a workspace",
+                      (unsigned long long)rows, (unsigned long long)kStaticScratchRows);
+            return FA_EWORKSPACE;
+        }
+    }
     int rc = validate_common(p, true);
     if (rc) return rc;
     if (p->B == 0 || (p->Nq == 0 && p->Nk == 0)) return FA_OK;
     if (p->Nk == 0) { set_error("Nk = 0: softmax over an empty key set is undefined"); return FA_EINVAL; }
-    if (p->Nq == 0) { set_error("fa_b200_bwd_static needs at least one query row"); return FA_EINVAL; }
     int variant;
     if ((rc = choose_variant(*p, true, &variant))) return rc;
     // the built-in array is sized for the per-row vectors only: tensor-core calls take the two-pass backward
     if (variant == FA_B200_VARIANT_TCGEN05) variant = FA_B200_VARIANT_TCGEN05_2PASS;
     BwdWorkspace ws = bwd_workspace_layout(*p, variant);
     if (ws.total > kStaticScratchBytes) {
-        set_error("fa_b200_bwd_static: this problem needs %zu bytes of scratch, the built-in array holds %zu "
-                  "(B*H*Nq rounded up to 128 must stay within 1048576 rows); use fa_b200_bwd with a workspace",
-                  ws.total, kStaticScratchBytes);
+        set_error("fa_b200_bwd_static: this problem needs %zu bytes of scratch, the built-in array holds %zu; "
+                  "use fa_b200_bwd with a workspace", ws.total, kStaticScratchBytes);
         return FA_EWORKSPACE;
     }
     GuardDevice g(p->device);
     if (!g.ok) { set_error("cudaSetDevice(%d) failed", p->device); return FA_ECUDA; }
+    if (p->Nq == 0) return zero_dk_dv(p);      // no queries: dK = dV = 0, as fa_b200_bwd does; needs no scratch
     void* scratch = nullptr;
     if ((rc = static_scratch_address(p->device, &scratch))) return rc;
     fa_b200_params q = *p;

@@ -41,6 +41,18 @@ FA_HD PhiloxKey philox_make_key(uint64_t seed, uint64_t offset) {
     return k;
 }
 
+// Which (batch, head) column of the dropout stream a call's local (b, h) is.  A call over a slice of a
+// larger problem (a head or batch shard on another GPU, one chunk of a batch) passes the slice's
+// origin and the whole problem's head count, and so draws exactly the mask the whole call draws.
+struct DropoutOrigin {
+    int32_t b0, h0;    // batch and head index of the call's first column in the whole problem
+    int32_t heads;     // heads of the whole problem
+};
+
+FA_HD uint32_t dropout_column(const DropoutOrigin& o, int b, int h) {
+    return (uint32_t)((b + o.b0) * o.heads + h + o.h0);
+}
+
 FA_HD void philox_mulhilo(uint32_t a, uint32_t b, uint32_t& hi, uint32_t& lo) {
 #if defined(__CUDA_ARCH__)
     lo = a * b;

@@ -42,6 +42,7 @@ struct SimtArgs {
     uint32_t drop_thr;   // 0 = no dropout
     float inv_keep;      // 1 / (1 - effective p)
     PhiloxKey key;
+    DropoutOrigin rng;
 };
 
 template <typename T>
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(SimtArgs a) {
     const int hk = h / (a.H / a.Hkv);
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int m0 = mt * BM;
-    const uint32_t bh = (uint32_t)(b * a.H + h);
+    const uint32_t bh = dropout_column(a.rng, b, h);
     const float* bias_b = a.bias.ptr ? (const float*)a.bias.ptr + (int64_t)b * a.bias.stride_b + (int64_t)h * a.bias.stride_h
                                      : nullptr;
 
@@ -258,7 +259,7 @@ __global__ void __launch_bounds__(NT) simt_bwd_kernel(SimtArgs a) {
     }
 
     for (int h = h_begin; h < h_end; ++h) {
-        const uint32_t bh = (uint32_t)(b * a.H + h);
+        const uint32_t bh = dropout_column(a.rng, b, h);
         const T* qb = (const T*)a.q.ptr + (int64_t)b * a.q.stride_b + (int64_t)h * a.q.stride_h;
         const T* gb = (const T*)a.d_o.ptr + (int64_t)b * a.d_o.stride_b + (int64_t)h * a.d_o.stride_h;
         const float* lse_b = a.lse + ((int64_t)b * a.H + h) * a.Nq;
@@ -455,6 +456,7 @@ SimtArgs make_args(const fa_b200_params& p, float* delta) {
     a.drop_thr = dropout_threshold(p.dropout_p);
     a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
     a.key = philox_make_key(p.seed, p.offset);
+    a.rng = dropout_origin_of(p);
     return a;
 }
 

@@ -261,6 +261,8 @@ def flash_attention_v100(
     validate_inputs: bool = True,
     key_lengths: Optional[torch.Tensor] = None,
     causal_alignment: str = "top_left",
+    dropout_origin: Optional[Tuple[int, int, int]] = None,
+    dropout_stream: Optional[Tuple[int, int]] = None,
 ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
     """Exact attention on (B, N, H, D) tensors; signature of reference interface.py:199-217.
 
@@ -277,6 +279,10 @@ def flash_attention_v100(
         causal_alignment: (not in the reference) "top_left" (the reference's mask: key j visible to
             query i iff j <= i) or "bottom_right" (j <= i + Nk - Nq: the last query sees every key;
             needs Nk >= Nq); the same for Nq == Nk
+        dropout_origin, dropout_stream: (not in the reference) for a call that is one shard of a larger
+            problem, e.g. a rank that received its shard from `scatter_shards`: the shard's (batch offset,
+            head offset, heads of the whole problem) and the whole problem's (seed, offset).  The shard
+            then draws exactly the dropout mask the whole call would draw for its columns
         block_size_m, block_size_n, enable_autotuning, optimization_strategy:
             accepted for source compatibility; tiles come from the static table
         return_softmax_lse: also return the (B, H, Nq) fp32 log-sum-exp
@@ -305,12 +311,13 @@ def flash_attention_v100(
 
     if use_multi and len(manager.devices) > 1:
         result = _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, block_size_n,
-                                    enable_autotuning, return_softmax_lse, manager, key_lengths, shift)
+                                    enable_autotuning, return_softmax_lse, manager, key_lengths, shift,
+                                    dropout_origin, dropout_stream)
     else:
         result = FlashAttentionV100Function.apply(q, k, v, scale, causal, dropout_p, bias, block_size_m,
                                                   block_size_n, enable_autotuning, return_softmax_lse,
                                                   False, True, None, True, "balanced", False, 1, 0, key_lengths,
-                                                  shift)
+                                                  shift, dropout_origin, dropout_stream)
     if profile:
         end.record(torch.cuda.current_stream(q.device))
         end.synchronize()
@@ -337,7 +344,8 @@ def _causal_shift(causal, alignment: str, seq_q: int, seq_k: int, key_lengths) -
 
 
 def _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, block_size_n,
-                       enable_autotuning, return_softmax_lse, manager, key_lengths=None, causal_shift=0):
+                       enable_autotuning, return_softmax_lse, manager, key_lengths=None, causal_shift=0,
+                       dropout_origin=None, dropout_stream=None):
     """Single-process sharding over manager.devices (reference interface.py:351-434).
 
     Shards are planned over heads or batch; each device gets its slice by an
@@ -346,7 +354,14 @@ def _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, bl
     differentiable torch ops around the autograd Function, so backward runs the
     same way in reverse.  Unlike the reference there is no global
     torch.cuda.synchronize(): ordering is by stream events.
+
+    Dropout: one (seed, offset) is drawn for the whole call and every shard indexes the stream by its
+    columns' place in the whole problem, so the mask does not depend on how the call was split.
     """
+    from .ops.attention import next_dropout_stream
+    if dropout_p > 0.0 and dropout_stream is None:
+        dropout_stream = next_dropout_stream()
+    b_base, h_base, h_total = dropout_origin if dropout_origin is not None else (0, 0, q.shape[2])
     devices = manager.devices
     group = q.shape[2] // k.shape[2]
     _, shards = manager.plan_shards(q.shape[0], q.shape[2], k.shape[2], len(devices))
@@ -377,7 +392,8 @@ def _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, bl
             ll = key_lengths[shard[0]:shard[1]].to(dev, non_blocking=True) if key_lengths is not None else None
             res = FlashAttentionV100Function.apply(ql, kl, vl, scale, causal, dropout_p, bl, block_size_m,
                                                    block_size_n, enable_autotuning, return_softmax_lse,
-                                                   False, True, None, True, "balanced", False, 1, 0, ll, causal_shift)
+                                                   False, True, None, True, "balanced", False, 1, 0, ll, causal_shift,
+                                                   (b_base + shard[0], h_base + shard[2], h_total), dropout_stream)
             o_l, lse_l = res if return_softmax_lse else (res, None)
             outs.append((shard, o_l.to(home, non_blocking=True)))
             if lse_l is not None:

@@ -14,6 +14,7 @@ import threading
 _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG_DIR, "lib", "libfa_b200.so")
 
+ABI_VERSION = 2
 FA_B200_F16, FA_B200_BF16, FA_B200_F32 = 0, 1, 2
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_TCGEN05, VARIANT_TCGEN05_2PASS = 0, 1, 2, 3
 VARIANT_NAMES = {VARIANT_AUTO: "auto", VARIANT_SIMT: "simt", VARIANT_TCGEN05: "tcgen05",
@@ -25,6 +26,7 @@ EXPORTS = (
     "fa_b200_fwd", "fa_b200_bwd", "fa_b200_bwd_static", "fa_b200_bwd_workspace_bytes", "fa_b200_tile_config",
     "fa_b200_dropout_mask_host", "fa_b200_dropout_mask_device", "fa_b200_dropout_effective_p",
     "fa_b200_philox4x32_10", "fa_b200_strerror", "fa_b200_last_error", "fa_b200_version", "fa_b200_combine",
+    "fa_b200_copy_rows",
 )
 
 
@@ -50,6 +52,8 @@ class Params(ctypes.Structure):
         ("scale", ctypes.c_float), ("dropout_p", ctypes.c_float),
         ("bwd_phases", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
         ("bias", Tensor4), ("d_scores", ctypes.c_void_p), ("kv_lengths", ctypes.c_void_p),
+        ("rng_batch_offset", ctypes.c_int32), ("rng_head_offset", ctypes.c_int32), ("rng_heads", ctypes.c_int32),
+        ("reserved0", ctypes.c_int32),
     ]
 
 
@@ -107,6 +111,9 @@ def load():
         lib.fa_b200_bwd_workspace_bytes.restype = ctypes.c_size_t
         lib.fa_b200_combine.argtypes = [ctypes.POINTER(CombineParams)]
         lib.fa_b200_combine.restype = ctypes.c_int
+        lib.fa_b200_copy_rows.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t,
+                                          ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+        lib.fa_b200_copy_rows.restype = ctypes.c_int
         lib.fa_b200_tile_config.argtypes = [ctypes.c_int] * 4 + [ctypes.POINTER(Tile)]
         lib.fa_b200_tile_config.restype = ctypes.c_int
         lib.fa_b200_dropout_mask_host.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float] + \
@@ -125,7 +132,7 @@ def load():
         lib.fa_b200_last_error.restype = ctypes.c_char_p
         lib.fa_b200_version.argtypes = []
         lib.fa_b200_version.restype = ctypes.c_int
-        if lib.fa_b200_version() != 1:
+        if lib.fa_b200_version() != ABI_VERSION:
             raise FlashAttentionLibraryError("ABI version mismatch")
         _lib = lib
     return _lib

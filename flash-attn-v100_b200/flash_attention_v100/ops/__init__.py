@@ -20,7 +20,7 @@ from .memory import (
     backward_workspace_bytes,
 )
 
-from .host_pipeline import HostAttentionStep, chunk_bounds, chunk_dropout_offset
+from .host_pipeline import HostAttentionStep, chunk_bounds, plan_chunks
 from .sequence_parallel import (
     flash_attention_v100_sequence_parallel,
     ring_schedule,
@@ -35,6 +35,6 @@ __all__ = [
     "compare_with_pytorch_attention", "set_dropout_seed", "kernel_variant",
     "allocate_attention_workspace", "free_attention_workspace", "estimate_peak_memory_usage",
     "get_memory_statistics", "backward_workspace_bytes",
-    "HostAttentionStep", "chunk_bounds", "chunk_dropout_offset",
+    "HostAttentionStep", "chunk_bounds", "plan_chunks",
     "flash_attention_v100_sequence_parallel", "ring_schedule", "zigzag_split", "zigzag_merge",
 ]

@@ -126,7 +126,8 @@ def _lengths_operand(key_lengths: Optional[torch.Tensor], q: torch.Tensor):
     return kl.data_ptr(), kl
 
 
-def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift=0) -> _cabi.Params:
+def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift=0,
+                 dropout_origin=None) -> _cabi.Params:
     p = _cabi.Params()
     p.struct_bytes = ctypes.sizeof(_cabi.Params)
     p.q, p.k, p.v, p.o = _tensor4(q), _tensor4(k), _tensor4(v), _tensor4(o)
@@ -143,11 +144,14 @@ def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal
     p.seed, p.offset = int(seed), int(offset)
     p.stream = torch.cuda.current_stream(q.device).cuda_stream or None
     p.status_word = _status_word(q.device).data_ptr()
+    if dropout_origin is not None:
+        # the call is a slice of a larger problem: (batch offset, head offset, heads of the whole)
+        p.rng_batch_offset, p.rng_head_offset, p.rng_heads = (int(x) for x in dropout_origin)
     return p
 
 
 def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None, bias=None,
-                   key_lengths=None, causal_shift=0):
+                   key_lengths=None, causal_shift=0, dropout_origin=None):
     """o, lse <- fa_b200_fwd.  Counterpart of flash_attention_forward_triton_enhanced
     (kernels/forward_kernel.py:246-387); returns (o, lse).  `out=(o, lse)` writes into
     caller-owned buffers (o like q, lse (B, H, Nq) fp32 contiguous) instead of allocating."""
@@ -156,7 +160,7 @@ def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=
     else:
         o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
-    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift)
+    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift, dropout_origin)
     p.bias, _keep = _bias_operand(bias)        # scores = scale * q.k + bias (CUDA-core kernels)
     p.kv_lengths, _keep_len = _lengths_operand(key_lengths, q)
     rc = _cabi.load().fa_b200_fwd(ctypes.byref(p))
@@ -165,7 +169,8 @@ def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=
 
 
 def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None,
-                    workspace=None, bias=None, d_scores=None, key_lengths=None, causal_shift=0):
+                    workspace=None, bias=None, d_scores=None, key_lengths=None, causal_shift=0,
+                    dropout_origin=None):
     """dq, dk, dv <- fa_b200_bwd.  Counterpart of
     flash_attention_backward_triton_enhanced (kernels/backward_kernel.py:208-318).
     `out=(dq, dk, dv)` and `workspace` (uint8, at least fa_b200_bwd_workspace_bytes)
@@ -177,7 +182,7 @@ def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, 
         dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
         dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
-    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift)
+    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift, dropout_origin)
     p.d_o, p.dq, p.dk, p.dv = _tensor4(d_o), _tensor4(dq), _tensor4(dk), _tensor4(dv)
     p.bias, _keep = _bias_operand(bias)
     p.kv_lengths, _keep_len = _lengths_operand(key_lengths, q)
@@ -253,21 +258,27 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
                 num_checkpoints: Optional[int] = None, memory_efficient: bool = True,
                 performance_mode: str = "balanced", enable_multi_gpu: bool = False,
                 world_size: int = 1, rank: int = 0, key_lengths: Optional[torch.Tensor] = None,
-                causal_shift: int = 0) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
+                causal_shift: int = 0, dropout_origin: Optional[Tuple[int, int, int]] = None,
+                dropout_stream: Optional[Tuple[int, int]] = None
+                ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
         # block sizes, autotuning, checkpointing, mixed precision and the
         # multi-GPU arguments are accepted for source compatibility: tiles come
         # from the static table, the backward always recomputes P, and sharding
         # over GPUs happens above this op (interface.py).
         q, k, v, scale = validate_inputs(q, k, v, scale, bias, dropout_p)
+        # dropout_origin / dropout_stream (after the reference's parameters): a call that is one shard of
+        # a larger problem passes the shard's (batch offset, head offset, heads of the whole) and the
+        # whole call's (seed, offset), and draws exactly the mask the whole call draws
         seed = offset = 0
         if dropout_p > 0.0:
-            seed, offset = _next_dropout_stream()
+            seed, offset = dropout_stream if dropout_stream is not None else _next_dropout_stream()
         # key_lengths (one int per batch entry, after the reference's 19 parameters): batch entry b
         # attends to its first key_lengths[b] keys only
         # causal_shift: key j is visible to query i iff j <= i + causal_shift (0: the reference's top-left
         # alignment; Nk - Nq: bottom-right)
         o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias, key_lengths=key_lengths,
-                                causal_shift=causal_shift)
+                                causal_shift=causal_shift, dropout_origin=dropout_origin)
+        ctx.dropout_origin = dropout_origin
         ctx.save_for_backward(q, k, v, o, lse, *([bias] if bias is not None else []))
         ctx.key_lengths = key_lengths
         ctx.causal_shift = int(causal_shift)
@@ -291,13 +302,14 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
                                    device=q.device)
         dq, dk, dv = launch_backward(grad_output, q, k, v, o, lse, ctx.scale, ctx.causal,
                                      ctx.dropout_p, ctx.seed, ctx.offset, bias=bias, d_scores=d_scores,
-                                     key_lengths=ctx.key_lengths, causal_shift=ctx.causal_shift)
+                                     key_lengths=ctx.key_lengths, causal_shift=ctx.causal_shift,
+                                     dropout_origin=ctx.dropout_origin)
         if d_scores is not None:
             dims = [i for i in range(4) if bias.shape[i] == 1 and d_scores.shape[i] != 1]
             grad_bias = (d_scores.sum(dim=dims, keepdim=True) if dims else d_scores).to(bias.dtype)
         return (dq if ctx.needs_input_grad[0] else None,
                 dk if ctx.needs_input_grad[1] else None,
-                dv if ctx.needs_input_grad[2] else None, None, None, None, grad_bias) + (None,) * 14
+                dv if ctx.needs_input_grad[2] else None, None, None, None, grad_bias) + (None,) * 16
 
 
 def flash_attention_forward_enhanced(q, k, v, scale: Optional[float] = None, causal: bool = False,
@@ -312,7 +324,7 @@ def flash_attention_forward_enhanced(q, k, v, scale: Optional[float] = None, cau
         seed, offset = kwargs.get("dropout_stream") or _next_dropout_stream()
     with torch.no_grad():
         o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias,
-                                key_lengths=kwargs.get("key_lengths"))
+                                key_lengths=kwargs.get("key_lengths"), dropout_origin=kwargs.get("dropout_origin"))
     return (o, lse) if kwargs.get("return_softmax_lse", False) else o
 
 
@@ -330,7 +342,7 @@ def flash_attention_backward_enhanced(grad_output, q, k, v, output, lse, max_val
         return launch_backward(grad_output, q, k, v, _last_dim_contiguous(output), lse.contiguous(),
                                scale, causal, kwargs.get("dropout_p", 0.0), seed, offset,
                                bias=kwargs.get("bias"), d_scores=kwargs.get("d_scores"),
-                               key_lengths=kwargs.get("key_lengths"))
+                               key_lengths=kwargs.get("key_lengths"), dropout_origin=kwargs.get("dropout_origin"))
 
 
 def compare_with_pytorch_attention_enhanced(q, k, v, causal: bool = False,
@@ -387,8 +399,14 @@ flash_attention_forward = flash_attention_forward_enhanced
 flash_attention_backward = flash_attention_backward_enhanced
 compare_with_pytorch_attention = compare_with_pytorch_attention_enhanced
 
+def next_dropout_stream() -> Tuple[int, int]:
+    """(seed, offset) the next dropout call would use; advances the counter.  A caller that splits one
+    problem into several calls draws it once and hands it to every part (`dropout_stream=`)."""
+    return _next_dropout_stream()
+
+
 __all__ = [
-    "EnhancedFlashAttentionV100Function", "flash_attention_forward_enhanced",
+    "EnhancedFlashAttentionV100Function", "next_dropout_stream", "flash_attention_forward_enhanced",
     "flash_attention_backward_enhanced", "compare_with_pytorch_attention_enhanced",
     "gradient_checkpointing_mode", "mixed_precision_mode", "FlashAttentionV100Function",
     "flash_attention_forward", "flash_attention_backward", "compare_with_pytorch_attention",

@@ -1,38 +1,47 @@
 """Forward + backward with every operand in pinned host memory.
 
 The reference keeps its tensors on the device and has no counterpart of this
-module; its multi-GPU manager splits a call along the batch dimension
-(interface.py:228-263), and the same split is used here in time instead of in
-space: the batch is cut into chunks and three CUDA streams work on different
-chunks at once,
+module; its multi-GPU manager splits a call over heads or batch entries
+(interface.py:228-263, :382-434), and the same split is used here in time
+instead of in space: the (batch x heads) grid is cut into chunks and three CUDA
+streams work on different chunks at once,
 
     copy-in stream   q, k, v, d_o of chunk c        (host -> device)
     compute stream   fa_b200_fwd, fa_b200_bwd on c  (through the C ABI)
     copy-out stream  o, dq, dk, dv of chunk c       (device -> host)
 
-so that PCIe carries data in both directions while the kernels run.  Chunks
-are whole batch entries (contiguous in the (B, N, H, D) layout), the device
-buffers are allocated once, and successive calls overlap too: the copy-in of a
-call starts while the copy-out of the previous one drains.
+so that PCIe carries data in both directions while the kernels run.  A chunk is
+a range of heads of one batch entry (or whole batch entries): in the
+(B, N, H, D) layout that is N rows of (h1 - h0) * D elements with a pitch of
+H * D, which one strided copy per tensor moves (fa_b200_copy_rows), and which the
+kernels consume in place as a strided view.  Small chunks shorten what cannot
+overlap, the copy-in of the first chunk and the copy-out of the last one, and
+let a batch of one overlap at all.  The device buffers are allocated once, and
+successive calls overlap too: the copy-in of a call starts while the copy-out of
+the previous one drains.
 
-Dropout: chunk c uses the stream (seed, offset + (c << 40)), so the mask of a
-chunked call differs from the mask of one call over the whole batch but is a
-pure function of (seed, offset, chunking).
+Dropout: every chunk uses the call's (seed, offset) and indexes the stream by
+its columns' place in the whole problem, so a chunked call draws exactly the
+mask of one call over the whole batch, however it is chunked.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from . import attention as _ops
+from ..kernels import _cabi
 
 _IN = ("q", "k", "v", "d_o")
 _OUT = ("o", "dq", "dk", "dv")
 
+Chunk = Tuple[int, int, int, int]     # (b0, b1, h0, h1): half-open batch and query-head ranges
+
 
 def chunk_bounds(batch: int, chunks: int) -> List[Tuple[int, int]]:
-    """[begin, end) batch ranges of `chunks` near-equal chunks (fewer if batch is smaller)."""
+    """[begin, end) ranges of `chunks` near-equal parts of `batch` items (fewer if batch is smaller)."""
     if batch < 0 or chunks < 1:
         raise ValueError("batch must be non-negative and chunks positive")
     n = max(1, min(chunks, batch))
@@ -45,9 +54,29 @@ def chunk_bounds(batch: int, chunks: int) -> List[Tuple[int, int]]:
     return out
 
 
-def chunk_dropout_offset(offset: int, chunk: int) -> int:
-    """Dropout stream offset of chunk `chunk` of a call made with `offset`."""
-    return (int(offset) + (int(chunk) << 40)) & 0xFFFFFFFFFFFFFFFF
+def plan_chunks(batch: int, heads: int, heads_kv: int, chunks: Optional[int] = None,
+                min_columns: int = 16, target: int = 16) -> List[Chunk]:
+    """Cut the (batch x heads) grid into chunks, batch-major.
+
+    `chunks=None` aims at `target` chunks of at least `min_columns` (batch, head) columns each (fewer
+    columns leave SMs idle in the kernels; fewer chunks expose more of the first copy-in and the last
+    copy-out).  Up to `batch` chunks are whole batch entries; beyond that every batch entry is cut
+    into head groups, at multiples of the K/V group size H / Hkv so that a chunk owns its K/V heads.
+    """
+    if batch <= 0:
+        return [(0, 0, 0, heads)]
+    if chunks is None:
+        chunks = max(1, min(target, (batch * heads) // max(1, min_columns)))
+    chunks = max(1, int(chunks))
+    if chunks <= batch:
+        return [(b, e, 0, heads) for b, e in chunk_bounds(batch, chunks)]
+    group = heads // heads_kv
+    per_entry = min(heads_kv, -(-chunks // batch))           # head groups per batch entry
+    out = []
+    for b in range(batch):
+        for k0, k1 in chunk_bounds(heads_kv, per_entry):
+            out.append((b, b + 1, k0 * group, k1 * group))
+    return out
 
 
 class HostAttentionStep:
@@ -75,28 +104,53 @@ class HostAttentionStep:
         self.q_shape, self.k_shape, self.dtype = (B, Nq, H, D), (B, Nk, Hkv, D), dtype
         self.causal, self.dropout_p = bool(causal), float(dropout_p)
         self.scale = float(D ** -0.5 if scale is None else scale)
-        self.bounds = chunk_bounds(B, B if chunks is None else int(chunks))
+        self.chunks: List[Chunk] = plan_chunks(B, H, Hkv, chunks)
+        self.bounds = self.chunks               # (b0, b1, h0, h1) per chunk
+        self._group = H // Hkv
         dev = self.device
         with torch.cuda.device(dev):
             self._dev: Dict[str, torch.Tensor] = {}
             for n in _IN + _OUT:
                 shape = self.k_shape if n in ("k", "v", "dk", "dv") else self.q_shape
                 self._dev[n] = torch.empty(shape, dtype=dtype, device=dev)
-            self._lse = torch.empty(B, H, Nq, dtype=torch.float32, device=dev)
-            self._ws = [self._workspace(e - b) for b, e in self.bounds]
+            # the log-sum-exp stays on the device: one dense (b, h, Nq) buffer per chunk
+            self._lse = [torch.empty(b1 - b0, h1 - h0, Nq, dtype=torch.float32, device=dev)
+                         for b0, b1, h0, h1 in self.chunks]
+            self._ws = [self._workspace(b1 - b0, h1 - h0) for b0, b1, h0, h1 in self.chunks]
             self._s_in, self._s_run, self._s_out = (torch.cuda.Stream(dev) for _ in range(3))
-            n = len(self.bounds)
+            n = len(self.chunks)
             ev = lambda: [torch.cuda.Event() for _ in range(n)]
             self._ev_qkv, self._ev_do, self._ev_fwd, self._ev_bwd, self._ev_out = ev(), ev(), ev(), ev(), ev()
             self._ev_done = torch.cuda.Event()
         self._calls = 0
 
-    def _workspace(self, batch: int) -> torch.Tensor:
+    def _workspace(self, batch: int, heads: int) -> torch.Tensor:
         from .memory import backward_workspace_bytes
-        _, Nq, H, D = self.q_shape
-        _, Nk, Hkv, _ = self.k_shape
-        n = backward_workspace_bytes(batch, Nq, Nk, H, D, self.dtype, num_heads_kv=Hkv) if batch else 0
+        _, Nq, _, D = self.q_shape
+        _, Nk, _, _ = self.k_shape
+        n = backward_workspace_bytes(batch, Nq, Nk, heads, D, self.dtype,
+                                     num_heads_kv=heads // self._group) if batch and heads else 0
         return torch.empty(max(n, 1), dtype=torch.uint8, device=self.device)
+
+    def _copy(self, dst: torch.Tensor, src: torch.Tensor, stream: "torch.cuda.Stream") -> None:
+        """dst <- src for two (b, N, h, D) views of the same shape (one in pinned host memory, one on
+        the device), as one strided copy per batch entry on `stream`."""
+        if dst.numel() == 0:
+            return
+        es = dst.element_size()
+        b, n, h, d = dst.shape
+        lib = _cabi.load()
+        whole = all(t.stride(2) == d and t.stride(1) == h * d for t in (dst, src))
+        if whole and dst.stride(0) == n * h * d and src.stride(0) == n * h * d:
+            views = [(dst, src, 1, b * n * h * d * es)]                    # contiguous: one flat copy
+        else:
+            views = [(dst[i], src[i], n, h * d * es) for i in range(b)]    # N rows of h * D elements each
+        for dv, sv, rows, row_bytes in views:
+            dp = row_bytes if rows == 1 else dv.stride(0) * es
+            sp = row_bytes if rows == 1 else sv.stride(0) * es
+            rc = lib.fa_b200_copy_rows(dv.data_ptr(), dp, sv.data_ptr(), sp, row_bytes, rows,
+                                       self.device.index or 0, stream.cuda_stream)
+            _cabi.raise_for_status(rc, "fa_b200_copy_rows")
 
     @property
     def h2d_bytes(self) -> int:
@@ -125,37 +179,43 @@ class HostAttentionStep:
         caller = torch.cuda.current_stream(self.device)
         self._s_in.wait_stream(caller)
         first = self._calls == 0
-        for c, (b, e) in enumerate(self.bounds):
-            if e == b:
+        g = self._group
+        for c, (b, e, h0, h1) in enumerate(self.chunks):
+            if e == b or h1 == h0:
                 continue
+            qs = (slice(b, e), slice(None), slice(h0, h1))               # the chunk's query heads
+            ks = (slice(b, e), slice(None), slice(h0 // g, h1 // g))     # ... and its K/V heads
+            sl = lambda n: ks if n in ("k", "v", "dk", "dv") else qs
             with torch.cuda.stream(self._s_in):
                 if not first:
                     self._s_in.wait_event(self._ev_bwd[c])      # previous call still reads chunk c's inputs
                 for n in ("q", "k", "v"):
-                    d[n][b:e].copy_(host_in[n][b:e], non_blocking=True)
+                    self._copy(d[n][sl(n)], host_in[n][sl(n)], self._s_in)
                 self._ev_qkv[c].record(self._s_in)
-                d["d_o"][b:e].copy_(host_in["d_o"][b:e], non_blocking=True)
+                self._copy(d["d_o"][qs], host_in["d_o"][qs], self._s_in)
                 self._ev_do[c].record(self._s_in)
             with torch.cuda.stream(self._s_run):
                 if not first:
                     self._s_run.wait_event(self._ev_out[c])     # previous results of chunk c copied out
                 self._s_run.wait_event(self._ev_qkv[c])
-                off = chunk_dropout_offset(offset, c) if self.dropout_p > 0 else 0
-                sd = int(seed) if self.dropout_p > 0 else 0
-                _ops.launch_forward(d["q"][b:e], d["k"][b:e], d["v"][b:e], self.scale, self.causal,
-                                    self.dropout_p, sd, off, out=(d["o"][b:e], self._lse[b:e]))
+                sd, off = (int(seed), int(offset)) if self.dropout_p > 0 else (0, 0)
+                origin = (b, h0, self.q_shape[2])               # this chunk's place in the whole problem
+                lse_c = self._lse[c]
+                _ops.launch_forward(d["q"][qs], d["k"][ks], d["v"][ks], self.scale, self.causal,
+                                    self.dropout_p, sd, off, out=(d["o"][qs], lse_c), dropout_origin=origin)
                 self._ev_fwd[c].record(self._s_run)
                 self._s_run.wait_event(self._ev_do[c])
-                _ops.launch_backward(d["d_o"][b:e], d["q"][b:e], d["k"][b:e], d["v"][b:e], d["o"][b:e],
-                                     self._lse[b:e], self.scale, self.causal, self.dropout_p, sd, off,
-                                     out=(d["dq"][b:e], d["dk"][b:e], d["dv"][b:e]), workspace=self._ws[c])
+                _ops.launch_backward(d["d_o"][qs], d["q"][qs], d["k"][ks], d["v"][ks], d["o"][qs],
+                                     lse_c, self.scale, self.causal, self.dropout_p, sd, off,
+                                     out=(d["dq"][qs], d["dk"][ks], d["dv"][ks]), workspace=self._ws[c],
+                                     dropout_origin=origin)
                 self._ev_bwd[c].record(self._s_run)
             with torch.cuda.stream(self._s_out):
                 self._s_out.wait_event(self._ev_fwd[c])
-                host_out["o"][b:e].copy_(d["o"][b:e], non_blocking=True)
+                self._copy(host_out["o"][qs], d["o"][qs], self._s_out)
                 self._s_out.wait_event(self._ev_bwd[c])
                 for n in ("dq", "dk", "dv"):
-                    host_out[n][b:e].copy_(d[n][b:e], non_blocking=True)
+                    self._copy(host_out[n][sl(n)], d[n][sl(n)], self._s_out)
                 self._ev_out[c].record(self._s_out)
         self._ev_done.record(self._s_out)
         caller.wait_event(self._ev_done)
@@ -167,4 +227,4 @@ class HostAttentionStep:
         _ops.check_status(self.device)
 
 
-__all__ = ["HostAttentionStep", "chunk_bounds", "chunk_dropout_offset"]
+__all__ = ["HostAttentionStep", "chunk_bounds", "plan_chunks"]

@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define FA_B200_ABI_VERSION 1
+#define FA_B200_ABI_VERSION 2
 
 typedef enum fa_b200_dtype {
     FA_B200_F16  = 0,
@@ -128,6 +128,14 @@ typedef struct fa_b200_params {
        in the reference, which expresses padding as a dense -inf bias (examples/basic_usage.py:243-248);
        here whole key blocks beyond the count are skipped, on every kernel family. */
     const int32_t* kv_lengths;
+    /* Dropout stream of a call over a slice of a larger problem (a head or batch shard, one chunk of a
+       batch).  The mask of column (b, h) is indexed by (b + rng_batch_offset) * rng_heads + h +
+       rng_head_offset; rng_heads = 0 means H (the call is the whole problem, offsets then are 0).  A
+       sharded or chunked call that passes its slice's origin and the whole problem's head count draws
+       exactly the mask the whole call draws.  The reference has no replayable stream at all
+       (kernels/forward_kernel.py:198-203). */
+    int32_t        rng_batch_offset, rng_head_offset, rng_heads;
+    int32_t        reserved0;
 } fa_b200_params;
 
 /* Static tile choice for a (D, dtype, causal) key; replaces the reference's
@@ -161,8 +169,13 @@ int fa_b200_bwd(const fa_b200_params* p);
  * scaled log-sum-exp) is an 8 MiB array built into the library's device image,
  * which every GPU that loads the library keeps until the process exits.
  *
- *  - Limit: B * H * (Nq rounded up to 128) <= 1048576 rows; larger problems
- *    return FA_EWORKSPACE and must use fa_b200_bwd.
+ *  - Limit: B * H * (Nq rounded up to 128) <= 1048576 rows, the same for every
+ *    kernel family; larger problems return FA_EWORKSPACE (checked before any
+ *    other argument) and must use fa_b200_bwd.
+ *  - Nq == 0 zero-fills dk and dv, as fa_b200_bwd does (no scratch is touched).
+ *  - Tensor-core calls are served by the two-pass backward (the array holds the
+ *    per-row vectors only), so dq, dk and dv are bit-reproducible; they equal
+ *    fa_b200_bwd's bit for bit when that is asked for the same variant.
  *  - The first call on each device looks the array's device address up
  *    (cudaGetSymbolAddress, with that device current).  Make that first call
  *    outside any stream capture.
@@ -214,6 +227,19 @@ typedef struct fa_b200_combine_params {
 } fa_b200_combine_params;
 
 int fa_b200_combine(const fa_b200_combine_params* p);
+
+/*
+ * One strided copy between host and device memory on `stream`: `rows` rows of
+ * `row_bytes` bytes, `src_pitch` / `dst_pitch` bytes from one row to the next
+ * (cudaMemcpy2DAsync; the direction is inferred from the pointers).  With it a
+ * head slice [b, :, h0:h1, :] of a (B, N, H, D) tensor in pinned host memory
+ * moves to or from the device in one request: rows of (h1-h0)*D elements, pitch
+ * H*D elements.  No counterpart in the reference, whose tensors never leave
+ * the device; used by the host-operand pipeline.  Host memory must be pinned
+ * for the copy to be asynchronous.
+ */
+int fa_b200_copy_rows(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                      size_t row_bytes, size_t rows, int device, void* stream);
 
 /* Bytes of scratch fa_b200_bwd needs for these sizes (delta, fp32 dQ
  * accumulator, ...).  Counterpart of the 'delta' entry of

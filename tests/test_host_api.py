@@ -146,7 +146,7 @@ def test_public_signatures_match_the_reference():
         "q", "k", "v", "causal", "scale", "dropout_p", "bias", "block_size_m", "block_size_n",
         "enable_autotuning", "return_softmax_lse", "optimization_strategy", "enable_multi_gpu",
         "enable_profiling", "fallback_on_error", "validate_inputs",     # reference interface.py:199-217
-        "key_lengths", "causal_alignment"]                                                   # this build's addition, last and optional
+        "key_lengths", "causal_alignment", "dropout_origin", "dropout_stream"]   # this build's additions, last and optional
     assert sig.parameters["causal"].default is False and sig.parameters["dropout_p"].default == 0.0
     fwd = inspect.signature(fa.FlashAttentionV100Function.forward)
     assert list(fwd.parameters)[1:] == [
@@ -154,7 +154,7 @@ def test_public_signatures_match_the_reference():
         "enable_autotuning", "return_softmax_lse", "enable_gradient_checkpointing",
         "enable_mixed_precision", "num_checkpoints", "memory_efficient", "performance_mode",
         "enable_multi_gpu", "world_size", "rank",                          # reference ops/attention.py:50-72
-        "key_lengths", "causal_shift"]                                                     # addition, after the reference's 19
+        "key_lengths", "causal_shift", "dropout_origin", "dropout_stream"]   # additions, after the reference's 19
     mgr = inspect.signature(fa.FlashAttentionV100Manager.__init__)
     assert list(mgr.parameters)[1:] == ["enable_multi_gpu", "optimization_strategy", "enable_profiling"]
     assert fa.SUPPORTED_DTYPES == {torch.float16, torch.bfloat16, torch.float32}

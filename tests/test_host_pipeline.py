@@ -21,11 +21,25 @@ def test_chunk_bounds_cover_the_batch():
         hp.chunk_bounds(4, 0)
 
 
-def test_chunk_dropout_offsets_are_distinct_streams():
-    offs = {hp.chunk_dropout_offset(7, c) for c in range(16)}
-    assert len(offs) == 16
-    assert hp.chunk_dropout_offset(7, 0) == 7
-    assert all((o >> 32) != 0 for o in offs if o != 7)      # the chunk index lands in the key word
+def test_plan_chunks_cover_the_grid_once():
+    for batch, heads, hkv in ((4, 32, 32), (1, 32, 8), (3, 4, 2), (32, 16, 16), (2, 6, 3), (1, 1, 1)):
+        group = heads // hkv
+        for chunks in (None, 1, 2, 3, 8, 16, 64):
+            plan = hp.plan_chunks(batch, heads, hkv, chunks)
+            seen = set()
+            for b0, b1, h0, h1 in plan:
+                assert 0 <= b0 < b1 <= batch and 0 <= h0 < h1 <= heads
+                assert h0 % group == 0 and h1 % group == 0          # a chunk owns whole K/V heads
+                cols = {(b, h) for b in range(b0, b1) for h in range(h0, h1)}
+                assert not (cols & seen)
+                seen |= cols
+            assert len(seen) == batch * heads
+            if chunks is not None and chunks <= batch:
+                assert len(plan) == chunks
+    # a batch of one is cut along heads, so its copies can overlap its kernels
+    assert len(hp.plan_chunks(1, 32, 32)) > 1
+    # the default keeps at least 16 columns per chunk
+    assert all((b1 - b0) * (h1 - h0) >= 16 for b0, b1, h0, h1 in hp.plan_chunks(4, 32, 32))
 
 
 def test_needs_cuda():
@@ -41,9 +55,11 @@ def _pinned(shape, dtype, seed):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("chunks", [None, 2, 1])
+@pytest.mark.parametrize("chunks", [None, 2, 1, 6])
 @pytest.mark.parametrize("dropout_p", [0.0, 0.25])
-def test_host_step_matches_single_calls(chunks, dropout_p):
+def test_host_step_matches_one_call_over_the_whole_problem(chunks, dropout_p):
+    """However the step is chunked (whole batch entries, or head groups of a batch entry), its results
+    equal one forward and one backward call over the whole problem, dropout mask included."""
     dev = torch.device("cuda", 0)
     B, N, H, Hkv, D, dt = 3, 320, 4, 2, 128, torch.bfloat16
     host = {"q": _pinned((B, N, H, D), dt, 1), "k": _pinned((B, N, Hkv, D), dt, 2),
@@ -52,22 +68,21 @@ def test_host_step_matches_single_calls(chunks, dropout_p):
            for n in ("o", "dq", "dk", "dv")}
     step = fa.HostAttentionStep(host["q"].shape, host["k"].shape, dt, dev, causal=True, dropout_p=dropout_p,
                                 chunks=chunks)
-    seed, offset = 0x5EED, 3
+    if chunks == 6:
+        assert len(step.chunks) == 6 and step.chunks[0] == (0, 1, 0, 2)
+    seed, offset = (0x5EED, 3) if dropout_p > 0 else (0, 0)
+    d = {n: t.to(dev) for n, t in host.items()}
+    o, lse = ops.launch_forward(d["q"], d["k"], d["v"], step.scale, True, dropout_p, seed, offset)
+    dq, dk, dv = ops.launch_backward(d["d_o"], d["q"], d["k"], d["v"], o, lse, step.scale, True, dropout_p,
+                                     seed, offset)
     for rep in range(2):                       # the second call reuses buffers while the first drains
         for t in out.values():
             t.fill_(float("nan"))
         step(host, out, seed, offset)
         step.synchronize()
-        for c, (b, e) in enumerate(step.bounds):
-            d = {n: t[b:e].to(dev) for n, t in host.items()}
-            off = hp.chunk_dropout_offset(offset, c) if dropout_p > 0 else 0
-            sd = seed if dropout_p > 0 else 0
-            o, lse = ops.launch_forward(d["q"], d["k"], d["v"], step.scale, True, dropout_p, sd, off)
-            dq, dk, dv = ops.launch_backward(d["d_o"], d["q"], d["k"], d["v"], o, lse, step.scale, True,
-                                             dropout_p, sd, off)
-            for name, ref in (("o", o), ("dk", dk), ("dv", dv)):
-                assert torch.equal(out[name][b:e], ref.cpu()), (name, c, rep)
-            assert_same_dq(out["dq"][b:e], dq.cpu(), dq_is_bit_reproducible("auto", dt, D, dropout_p))
+        for name, ref in (("o", o), ("dk", dk), ("dv", dv)):
+            assert torch.equal(out[name], ref.cpu()), (name, rep)
+        assert_same_dq(out["dq"], dq.cpu(), dq_is_bit_reproducible("auto", dt, D, dropout_p))
 
 
 @pytest.mark.gpu
