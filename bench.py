@@ -2,10 +2,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3]
 
-N > 1 is launched with torch.distributed.run (one rank per GPU); the (batch x
-heads) grid has no exchange step, so every rank runs an independent shard of
-the same shape (weak scaling) and NCCL is used only for the barrier and the
-max-over-ranks reduction of the timings.  Rank 0 prints ONE JSON line.
+N > 1 is launched with torch.distributed.run (one rank per GPU).  The workload
+is then split over the ranks the way the package's shard planner splits it
+(heads when they divide, else batch): the ONE problem, e.g. cfg3's 128
+(batch, head) columns as 16 / 8 / 4 heads per GPU at 2 / 4 / 8 GPUs, with every
+rank's shard resident on its GPU (strong scaling).  The (batch x heads) grid has
+no exchange step, so NCCL is used only for the barrier and the max-over-ranks
+reduction of the timings.  Rank 0 prints ONE JSON line.  `--replicas` instead
+gives every rank the whole workload (weak scaling).
 
 A step is one forward + backward pass of the workload (default: B4 N4096 H32
 D128 bf16 causal, the Llama-7B-like layer) through the public API.  `value` is
@@ -122,9 +126,9 @@ NCU_DRAM_BYTES_PER_BATCH = {"fwd": 111.5e6, "bwd_dkdv": 175.9e6, "bwd_dq": 155.3
 
 def ncu_traffic(kernel: str, w):
     """DRAM bytes per launch for the default workload's shape family, else None."""
-    if (w.N, w.H, w.D, w.causal) != (4096, 32, 128, True) or kernel not in NCU_DRAM_BYTES_PER_BATCH:
+    if (w.N, w.D, w.causal) != (4096, 128, True) or kernel not in NCU_DRAM_BYTES_PER_BATCH:
         return None
-    return NCU_DRAM_BYTES_PER_BATCH[kernel] * w.B
+    return NCU_DRAM_BYTES_PER_BATCH[kernel] * w.B * w.H / 32.0
 
 
 def time_steps(fn, steps: int, device, world: int):
@@ -197,7 +201,46 @@ def run_reference(args, w):
 
 
 # ----------------------------------------------------------------------------- GPU side
-def run_ours(args, w):
+def shard_of(w, world: int, rank: int, replicas: bool):
+    """This rank's part of the workload: (local workload, dropout origin, description).  With more
+    than one rank the problem is split by the package's planner, heads first, then batch."""
+    if world == 1 or replicas:
+        return w, None, ("the whole workload" if world == 1 else "replicas: every rank runs the whole workload")
+    from flash_attention_v100.interface import plan_shards
+    kind, shards = plan_shards(w.B, w.H, world)
+    b0, b1, h0, h1 = shards[rank]
+    sizes = sorted({(s[1] - s[0], s[3] - s[2]) for s in shards})
+    what = "%s: %s (batch, heads) per rank" % (kind, ", ".join("%dx%d" % x for x in sizes))
+    local = w.shrink(B=b1 - b0, H=h1 - h0)
+    return local, (b0, h0, w.H), what
+
+
+def bind_to_gpu_numa_node(index: int):
+    """Pin this process to the CPUs of the NUMA node its GPU hangs off, before any pinned host
+    memory is allocated (first touch then places the buffers on that node).  Returns a description
+    of what was done; does nothing when the topology cannot be read."""
+    try:
+        props = torch.cuda.get_device_properties(index)
+        bdf = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        with open("/sys/bus/pci/devices/%s/numa_node" % bdf) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return {"numa_node": None, "bound": False}
+        with open("/sys/devices/system/node/node%d/cpulist" % node) as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return {"numa_node": node, "bound": False}
+        os.sched_setaffinity(0, cpus)
+        return {"numa_node": node, "bound": True, "cpus": len(cpus)}
+    except (OSError, ValueError, AttributeError):
+        return {"numa_node": None, "bound": False}
+
+
+def run_ours(args, whole):
     import flash_attention_v100 as fa
     from flash_attention_v100.kernels import _cabi
     from flash_attention_v100.ops import attention as ops
@@ -210,11 +253,13 @@ def run_ours(args, w):
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    numa = bind_to_gpu_numa_node(local) if world > 1 else {"numa_node": None, "bound": False}
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     _cabi.load()
 
-    host = make_inputs(w, seed=w.seed + rank, pin=True)              # pinned host copies
+    w, origin, split = shard_of(whole, world, rank, args.replicas)
+    host = make_inputs(w, seed=w.seed + rank, pin=True)              # pinned host copies of this rank's shard
     dev = {n: t.to(device, non_blocking=True) for n, t in host.items()}
     torch.cuda.synchronize(device)
     stream = (DROPOUT_SEED, DROPOUT_OFFSET)
@@ -225,7 +270,8 @@ def run_ours(args, w):
         if w.dropout_p > 0:
             fa.set_dropout_seed(*stream)
         o = fa.flash_attention_v100(q, k, v, causal=w.causal, scale=w.scale, dropout_p=w.dropout_p,
-                                    enable_multi_gpu=False)
+                                    enable_multi_gpu=False, dropout_origin=origin,
+                                    dropout_stream=stream if origin is not None else None)
         o.backward(dev["d_o"])
         q.grad = k.grad = v.grad = None
         return o
@@ -331,8 +377,16 @@ def run_ours(args, w):
         "per_kernel_tflops_counted": {n: a * unit_gemm / (ms * 1e-3) / 1e12 for n, (ms, a, _) in kernels.items()},
     }
 
-    total_flops = (w.fwd_flops() + w.bwd_flops()) * world
+    # strong scaling: the ranks together ran the one workload; replicas: each ran all of it
+    total_flops = (whole.fwd_flops() + whole.bwd_flops()) * (world if args.replicas else 1)
     value = total_flops / (ms_step * 1e-3) / 1e12
+    host_gbs_rank = (host_step.h2d_bytes + host_step.d2h_bytes) / (ms_e2e * 1e-3) / 1e9   # both directions
+    host_gbs = torch.tensor([host_gbs_rank], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(host_gbs, op=dist.ReduceOp.SUM)
+    bound = torch.tensor([1.0 if numa.get("bound") else 0.0], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(bound, op=dist.ReduceOp.SUM)
     e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
     tb = w.tensor_bytes()
     fwd_tf = w.fwd_flops() / (kern_ms["fwd"] * 1e-3) / 1e12
@@ -348,12 +402,13 @@ def run_ours(args, w):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None,
+            "scaling": "weak" if (args.replicas and world > 1) else "strong", "vs_baseline": None,
             "dtype": {torch.bfloat16: "bf16", torch.float16: "f16", torch.float32: "f32"}[w.dtype],
             "data": "synthetic",
             "config": {
-                "workload": w.name, "B": w.B, "N": w.N, "H": w.H, "D": w.D, "causal": w.causal,
-                "dropout_p": w.dropout_p, "per_gpu": "every rank runs this shape (its own seeded shard)",
+                "workload": whole.name, "B": whole.B, "N": whole.N, "H": whole.H, "D": whole.D,
+                "causal": whole.causal, "dropout_p": whole.dropout_p,
+                "split": split, "per_gpu": "B%d H%d of the workload, resident on the GPU" % (w.B, w.H),
                 "parallelism": f"(batch x heads) shards, {world} rank(s), no data-path collective",
                 "l2": ("not flushed: q, k, v, o, dO, dQ, dK, dV are %.0f MB each (working set %.0f MB), %s the 126 MB L2"
                        % (tb / 1e6, 8 * tb / 1e6, "larger than" if tb > 126 * 2 ** 20 else
@@ -367,12 +422,14 @@ def run_ours(args, w):
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": host_step.h2d_bytes, "d2h_bytes_per_step": host_step.d2h_bytes,
-                    "api": "HostAttentionStep: %d batch chunks, copies and kernels on three streams"
-                           % len(host_step.bounds),
-                    "single_stream_ms_per_step": ms_e2e_serial},
+                    "api": "HostAttentionStep: %d (batch, head-group) chunks, copies and kernels on three streams"
+                           % len(host_step.chunks),
+                    "single_stream_ms_per_step": ms_e2e_serial,
+                    "host_gbs_per_rank": host_gbs_rank, "host_gbs_all_ranks": float(host_gbs.item()),
+                    "ranks_bound_to_gpu_numa_node": int(bound.item())},
             "gpu_launches": 4 * args.steps,     # per step: 1 forward + 3 backward kernels of this library
             "clocks": clock_info,
-            "status_word": int(status.item()),
+            "status_word": int(status[0]),
         }
         print(json.dumps(line))
     if world > 1:
@@ -388,6 +445,8 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", default="cfg3")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--replicas", action="store_true",
+                    help="N > 1: every rank runs the whole workload (weak scaling) instead of its shard of it")
     ap.add_argument("--batch", type=int, default=None, help="override the workload's batch (small profiling cases)")
     ap.add_argument("--heads", type=int, default=None, help="override the workload's head count")
     args = ap.parse_args()

@@ -47,7 +47,8 @@
 //                    step's last MMA, so it gets three stages where shared memory allows and its
 //                    next load overlaps a whole step; W gets two), and in the key-stationary
 //                    kernels the step's -lse / -delta rows into a two-slot ring
-//   warps 18-19      idle (registers are granted per four warps)
+//   warps 18-19      bf16 inputs: convert the streamed tiles to fp16 in place as they land (all MMAs run
+//                    f16 x f16, with P and dS rounded to fp16; see "number formats" below); else idle
 //
 // TMEM columns: T1 [0,128)  T2 [128,256)  ACC1 [256,256+D)  ACC2 [384,384+D).
 // MODE 1 has no ACC2 and uses [384,512) as a second S buffer: S(i+1) is computed
@@ -56,6 +57,8 @@
 #include "fa_common.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
+#include "tile_config.cuh"
+#include <stdlib.h>
 #include <type_traits>
 
 namespace fa {
@@ -65,7 +68,7 @@ using namespace ptx;
 
 constexpr int kTile = 128;
 constexpr int kBoxBytes = 128 * 128;
-constexpr int kNWG = 4;                  // elementwise warpgroups per CTA (each owns 128 / kNWG columns)
+constexpr int kNWG = tile::kBwdWarpgroups;   // elementwise warpgroups per CTA (each owns 128 / kNWG columns)
 constexpr int kExtraThreads = 128;       // MMA warp + TMA warp + two idle warps: registers are granted per
                                          // four warps, so dropping the idle pair would free none
 constexpr float kLog2e = 1.4426950408889634f;
@@ -82,8 +85,8 @@ struct BwdCfg {
     static constexpr int kTileBytes = kNBox * kBoxBytes;
     static constexpr bool kFused = (MODE == 2);
     static constexpr bool kMasks = DROP && MODE != 1;            // masks are built in shared memory when keys are rows
-    static constexpr int kUStages = (D == 64) ? 4 : (kMasks ? 2 : 3);
-    static constexpr int kWStages = (D == 64) ? 3 : 2;
+    static constexpr int kUStages = tile::bwd_u_stages(D, kMasks);
+    static constexpr int kWStages = tile::bwd_w_stages(D);
     static constexpr int kMaskBytes = 2 * 128 * 8 * 2;          // two buffers of 128 x 8 uint16 keep masks
     static constexpr int kXYFull = 0;
     static constexpr int kUFull = 1;                             // [kUStages]
@@ -103,25 +106,34 @@ struct BwdCfg {
     static constexpr int kDsHalf = kPHalf + 1;                   // first half of each dS slice stored
     static constexpr int kVFull = kDsHalf + 1;                   // [2] key-stationary: -lse, -delta rows of a step landed
     static constexpr int kVEmpty = kVFull + 2;                   // [2] ... and read (one arrival per elementwise warp)
-    static constexpr int kNumBars = kVEmpty + 2;
+    // bf16 inputs: tiles converted to fp16 in place (arrivals: one per converting warp)
+    static constexpr int kXYConv = kVEmpty + 2;                  // stationary tiles (elementwise warps)
+    static constexpr int kUConv = kXYConv + 1;                   // [kUStages] streamed U (the two spare warps)
+    static constexpr int kWConv = kUConv + kUStages;             // [kWStages] streamed W, key-stationary kernels only
+    static constexpr int kNumBars = kWConv + kWStages;
     static constexpr int kVecBytes = (MODE != 1) ? 2 * 1024 : 0; // two slots of lse[128] | delta[128]
     static constexpr int kDsBytes = 128 * 128 * 2;               // fused kernel: dS^T tile for the dQ MMA
     // bytes used from the 1024-aligned base: X, Y, U ring, W ring, [dS], [vectors], barriers, TMEM slot + flag, [masks]
     static constexpr int kUsedBytes = (2 + kUStages + kWStages) * kTileBytes + (kFused ? kDsBytes : 0) + kVecBytes +
                                       kNumBars * 8 + 64 + (kMasks ? kMaskBytes : 0);
     static constexpr int kMaxSmem = 232448;                      // 227 KB: the most one CTA can ask for
+    static_assert(128 * kNWG + 128 == 32 * tile::kBwdWarps, "thread count and table disagree");
     static_assert(kUsedBytes <= kMaxSmem, "shared-memory plan does not fit");
     // what the launch asks for: room to align the base when it fits (the kernel checks what it got)
     static constexpr int kSmemBytes = kUsedBytes + 1024 <= kMaxSmem ? kUsedBytes + 1024 : kMaxSmem;
 };
 
 struct BwdArgs {
-    const float* lse2;     // [B*H][nq_pad]  -lse * log2(e), -inf in the padding
+    const float* lse2;     // [B*H][nq_pad]  kPShift - lse * log2(e), -inf in the padding
     const float* delta;    // [B*H][nq_pad]  -delta, 0 in the padding
+    const float* ranges;   // [B*Hkv][2]     max |dO| over the column's query heads, max |V|
+    const float* erow;     // [B*H][nq_pad]  row exponents e_i of the fp16 dO copy (row form only)
     float* dq_acc;         // fused kernel: fp32 dQ sums, [B*H][nq_pad/128] tiles of [D/4][128 rows][4]
     const int32_t* kv_len; // optional per-batch key counts
     int32_t* status;
     int B, Nq, Nk, H, Hkv, nq_pad;
+    int wait_limit_ms;             // limit of one mbarrier wait (0: the default)
+    int cols_per_group;            // CTA order: (batch, head) columns per group, see cta_work()
     int causal;
     int shift;                     // key j is visible to query i iff j <= i + shift
     float scale, scale_log2;
@@ -138,16 +150,104 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
         : "memory");
 }
 
+// ---- number formats of the two operands the threads hand to the MMAs -----------------------------
+// P and dS are written to tensor memory as fp16 whatever the input dtype (with bf16 they would carry
+// a 2^-9 rounding into dV, dK and dQ at full size; see sm100_ptx.cuh), so both are scaled into
+// fp16's range by powers of two that the epilogue takes out again:
+//   P'  = P * 2^kPShift                      P <= 1, so P' <= 2^14 and P down to 2^-28 keeps 11 bits
+//   dS' = P (dP o Z - delta) * 2^g           g from a bound: |dP o Z - delta| <= 2 D max|dO| max|V| / (1-p)
+// and, for bf16 inputs, dO is normalised while it is converted to fp16: dO' = dO * 2^-eO, max|dO'| < 2^15,
+// so gradients of any magnitude (bf16 training runs with dO ~ 1e-8) use fp16's range.  max|dO| and max|V|
+// are taken per (batch, K/V head) column by the preprocess launch, so a column's result does not depend
+// on which other columns the call holds.
+constexpr float kPShift = 14.0f;
+
+struct BwdScales {
+    float tt_mul;     // dP (as the MMA delivers it) * tt_mul
+    float nd_mul;     // the staged -delta vector * nd_mul
+    float l_add;      // added to the staged lse vector (key-stationary kernels)
+    float acc1_mul;   // dK or dQ  = ACC1 * acc1_mul  (scale * 2^-g)
+    float acc2_mul;   // dV        = ACC2 * acc2_mul
+    float do_mul;     // inline conversion: dO' = dO * do_mul
+};
+// smallest k with m < 2^k (0 for m == 0; NaN and infinity count as the largest finite exponent)
+__host__ __device__ __forceinline__ int log2_bound_bits(uint32_t bits) {
+    bits &= 0x7FFFFFFFu;
+    if (bits == 0u) return 0;
+    int e = (int)(bits >> 23);
+    if (e == 0) return -126;
+    if (e > 254) e = 254;
+    return e - 127 + 1;
+}
+__device__ __forceinline__ int log2_bound(float m) { return log2_bound_bits(__float_as_uint(m)); }
+__device__ __forceinline__ float pow2i(int e) {
+    e = e < -126 ? -126 : (e > 127 ? 127 : e);
+    return __uint_as_float((uint32_t)(e + 127) << 23);
+}
+// How dO reaches the key-stationary kernels' MMAs, which decides where its normalisation sits:
+//   kDoAsIs     fp16 inputs: dO is used as it is
+//   kDoInline   bf16, converted tile by tile inside the kernel: one factor 2^-e_col for the whole column
+//   kDoRowCopy  bf16, converted once by the preprocess launch into an fp16 copy, every row by its own
+//               2^-e_i (the column's maximum is not known while the copy is written); the staged vectors
+//               hold  lse' = kPShift - lse*log2(e) + e_i  and  -delta * 2^-e_i,  and P carries 2^(e_i - e_col)
+// With e_col = (bound of the column's max |dO|) - 15 the constants below are the same in the last two
+// forms except for l_add and nd_mul.  The query-stationary kernel multiplies the bf16 dO itself
+// (kDoAsIs arithmetic; it undoes e_i in its per-row scalars when the vectors are in the row form).
+enum DoForm { kDoAsIs = 0, kDoInline = 1, kDoRowCopy = 2 };
+__device__ __forceinline__ BwdScales make_scales(const float* rng, int D, float inv_keep, float scale, DoForm form) {
+    const int k_do = log2_bound(rng[0]), k_v = log2_bound(rng[1]);
+    const int e_col = form == kDoAsIs ? 0 : k_do - 15;
+    const int g = 15 - (k_do + k_v + (D > 64 ? 8 : 7) + log2_bound(inv_keep));
+    BwdScales sc;
+    sc.tt_mul = pow2i(g - (int)kPShift + e_col);
+    sc.nd_mul = pow2i(g - (int)kPShift + (form == kDoRowCopy ? e_col : 0));
+    sc.l_add = form == kDoRowCopy ? (float)(-e_col) : 0.f;
+    sc.acc1_mul = scale * pow2i(-g);
+    sc.acc2_mul = inv_keep * pow2i(e_col - (int)kPShift);
+    sc.do_mul = pow2i(-e_col);
+    return sc;
+}
+
+// Which (tile, head, batch) a CTA works on.  The grid is (tiles, heads, batch) and CTAs start in the
+// order of their linear index.  Under a causal mask tiles cost between 1 and `tiles` steps, so the
+// order decides how evenly the SMs finish: the (batch, head) columns are taken in groups of
+// `cols_per_group`, and within a group all columns' most expensive tile comes first, then the next
+// one, ... (longest first).  A group is sized so that its Q, K, V and dO stay in L2 while its CTAs
+// run; the cheap tiles that end one group fill the SMs beside the expensive ones that start the next.
+struct CtaWork { int tile_rank, head, b; };
+__device__ __forceinline__ CtaWork cta_work(int cols_per_group) {
+    const int X = (int)gridDim.x, Y = (int)gridDim.y, cols = Y * (int)gridDim.z;
+    const int L = (int)blockIdx.x + X * ((int)blockIdx.y + Y * (int)blockIdx.z);
+    const int G = cols_per_group < 1 ? 1 : cols_per_group;
+    const int grp = L / (G * X), r = L - grp * (G * X);
+    const int gcols = (cols - grp * G) < G ? (cols - grp * G) : G;
+    const int col = grp * G + r % gcols;
+    CtaWork w;
+    w.tile_rank = r / gcols;
+    w.head = col % Y;
+    w.b = col / Y;
+    return w;
+}
+
 // MODE 0: dK, dV (key-stationary).  MODE 1: dQ (query-stationary).
-template <int D, bool BF16, int MODE, int NWG, bool DROP>
+// INLINE (bf16 inputs only): the streamed tiles arrive as bf16 and the two spare warps convert them;
+// otherwise bf16 calls stream the fp16 copies the preprocess launch (Q, dO) and the dK/dV kernel (K:
+// map_aux, a by-product of its stationary tile) have written to the workspace.
+template <int D, bool BF16, int MODE, int NWG, bool DROP, bool INLINE>
 __global__ void __launch_bounds__(128 * NWG + kExtraThreads, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                  const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_out1, const __grid_constant__ CUtensorMap map_out2,
-                 const BwdArgs a) {
+                 const __grid_constant__ CUtensorMap map_aux, const BwdArgs a) {
     using Cfg = BwdCfg<D, MODE, DROP>;
     constexpr bool KS = (MODE != 1);        // key-stationary: K, V stay, query tiles stream
     constexpr bool FUSED = (MODE == 2);     // key-stationary and dQ too
+    constexpr bool CONV = BF16;             // every MMA runs f16 x f16: bf16 tiles are converted
+    constexpr bool STREAM_CONV = CONV && INLINE;             // ... the streamed ones by the spare warps
+    constexpr bool XY_CONV = CONV && (KS || INLINE);         // ... the stationary ones by the elementwise warps
+    constexpr bool ROWFORM = CONV && !INLINE;                // staged vectors are in the row form (see DoForm)
+    constexpr bool K_COPY = ROWFORM && MODE == 0;            // this kernel writes the fp16 copy of K
+    static_assert(BF16 || !INLINE, "inline conversion is a bf16 variant");
     constexpr int UST = Cfg::kUStages, WST = Cfg::kWStages;
     constexpr int TILE = Cfg::kTileBytes;
 
@@ -168,13 +268,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         uint32_t dyn;
         asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
         if ((uint32_t)(smem - smem_raw) + (uint32_t)Cfg::kUsedBytes > dyn) {
-            if (threadIdx.x == 0 && a.status) atomicExch(a.status, 8);
+            if (threadIdx.x == 0) report_status(a.status, 8);
             return;
         }
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z;
+    const CtaWork cw = cta_work(a.cols_per_group);
+    const int b = cw.b;
     const int group = a.H / a.Hkv;
     const int nq_tiles = (a.Nq + kTile - 1) / kTile;
 
@@ -182,16 +283,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const int nk = kv_len_of(a.kv_len, b, a.Nk);    // keys this batch entry attends to
     int tile, head_x, it0, n_per_head, n_iter;
     if (KS) {
-        tile = blockIdx.x;                          // key tile
-        head_x = blockIdx.y;                        // kv head
+        tile = cw.tile_rank;                        // key tile: the first one sees the most query tiles
+        head_x = cw.head;                           // kv head
         // first query tile that sees this key tile: query i sees key j iff j <= i + shift
         it0 = a.causal ? (tile * kTile > a.shift ? (tile * kTile - a.shift) / kTile : 0) : 0;
         n_per_head = nq_tiles > it0 ? nq_tiles - it0 : 0;
         if (tile * kTile >= nk) n_per_head = 0;     // a tile of padding keys: dK = dV = 0
         n_iter = n_per_head * group;
     } else {
-        tile = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;   // query tile, heavy first
-        head_x = blockIdx.y;                        // query head
+        tile = a.causal ? (int)gridDim.x - 1 - cw.tile_rank : cw.tile_rank;     // query tile, heavy first
+        head_x = cw.head;                           // query head
         it0 = 0;
         int kv_end = nk;
         if (a.causal && tile * kTile + kTile + a.shift < kv_end) kv_end = tile * kTile + kTile + a.shift;
@@ -215,10 +316,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         for (int i = 0; i < Cfg::kNumBars; ++i) {
             const bool wide = (i == Cfg::kPReady || i == Cfg::kDsReady || i == Cfg::kMask || i == Cfg::kEpi ||
                                i == Cfg::kDqRead || i == Cfg::kPHalf || i == Cfg::kDsHalf ||
-                               i == Cfg::kVEmpty || i == Cfg::kVEmpty + 1);
-            mbar_init(&bars[i], wide ? 4u * NWG : 1u);    // one arrival per elementwise warp
+                               i == Cfg::kVEmpty || i == Cfg::kVEmpty + 1 || i == Cfg::kXYConv);
+            const bool conv2 = i >= Cfg::kUConv;          // the two converting warps
+            mbar_init(&bars[i], wide ? 4u * NWG : (conv2 ? 2u : 1u));    // one arrival per elementwise warp
         }
-        *abort_flag = 0u;
+        wait_control_init(abort_flag, a.wait_limit_ms);
         fence_mbar_init();
     }
     constexpr int kMmaWarp = 4 * NWG, kTmaWarp = 4 * NWG + 1;
@@ -235,6 +337,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         prefetch_tensormap(&map_u); prefetch_tensormap(&map_w);
         prefetch_tensormap(&map_out1);
         if (KS) prefetch_tensormap(&map_out2);
+        if (K_COPY) prefetch_tensormap(&map_aux);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -244,6 +347,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     // fused kernel: the per-step dQ tile has columns of its own when D = 64 and shares T2's when D = 128
     constexpr bool kDqAliasesT2 = (D > 64);
     const uint32_t tDq = kDqAliasesT2 ? tT2 : tmem + 448u;
+    const BwdScales sc = make_scales(a.ranges + 2 * ((int64_t)b * a.Hkv + head_kv), D, a.inv_keep, a.scale,
+                                     !(CONV && KS) ? kDoAsIs : (INLINE ? kDoInline : kDoRowCopy));
 
     if (warp >= kMmaWarp) {
       // No setmaxnreg in this kernel: with the launch allocation of 96 registers per thread no role
@@ -322,8 +427,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       } else if (warp == kMmaWarp) {
         // ---------------------------------------------------------------- MMA issuer
         if (elect_one() && n_iter > 0) {
-            constexpr uint32_t idesc_t = make_idesc_f16(BF16, BF16, kTile, kTile, false, false);
-            constexpr uint32_t idesc_acc = make_idesc_f16(BF16, BF16, kTile, D, false, true);
+            // operand formats: converted tiles, P and dS are fp16; the query-stationary kernel's dP keeps
+            // its two bf16 tiles (dO_i, V_j) as they are
+            constexpr bool T1_BF16 = BF16 && !CONV, T2_BF16 = BF16 && !(CONV && KS);
+            constexpr uint32_t idesc_t1 = make_idesc_f16(T1_BF16, T1_BF16, kTile, kTile, false, false);
+            constexpr uint32_t idesc_t2 = make_idesc_f16(T2_BF16, T2_BF16, kTile, kTile, false, false);
+            constexpr uint32_t idesc_acc = make_idesc_f16(false, false, kTile, D, false, true);
+            constexpr int kUReady = STREAM_CONV ? Cfg::kUConv : Cfg::kUFull;
+            constexpr int kWReady = (STREAM_CONV && KS) ? Cfg::kWConv : Cfg::kWFull;
+            constexpr int kXYReady = XY_CONV ? Cfg::kXYConv : Cfg::kXYFull;
             const uint32_t sX_u = smem_u32(sX), sY_u = smem_u32(sY), sU_u = smem_u32(sU), sW_u = smem_u32(sW);
 
             // Descriptors differ only in the 16-byte-granular start address held in their low
@@ -331,7 +443,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             // single issuing thread's instruction count per MMA small.
             const uint64_t dk_major = make_smem_desc_sw128(0, 0, 1024);            // K-major operand
             const uint64_t dmn_major = make_smem_desc_sw128(0, kBoxBytes, 1024);   // MN-major operand
-            auto issue_t = [&](uint32_t d_tmem, uint32_t stat_u, uint32_t strm_u) {
+            auto issue_t = [&](uint32_t d_tmem, uint32_t stat_u, uint32_t strm_u, uint32_t idesc_t) {
                 const uint64_t a0 = dk_major + (uint64_t)(stat_u >> 4), b0 = dk_major + (uint64_t)(strm_u >> 4);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -365,7 +477,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             };
 
             // fused kernel: the step's dQ tile (fresh accumulation) from two shared-memory operands
-            constexpr uint32_t idesc_dq = make_idesc_f16(BF16, BF16, kTile, D, true, true);
+            constexpr uint32_t idesc_dq = make_idesc_f16(false, false, kTile, D, true, true);
             const uint32_t sDs_u = smem_u32(sDs);
             auto issue_dq = [&]() {
                 const uint64_t a0 = dmn_major + (uint64_t)(sDs_u >> 4), b0 = dmn_major + (uint64_t)(sX_u >> 4);
@@ -375,14 +487,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                                kk > 0);
             };
 
-            bool ok = mbar_wait(&bars[Cfg::kXYFull], 0u, abort_flag);
-            if (ok) ok = mbar_wait(&bars[Cfg::kUFull + 0], 0u, abort_flag);
-            if (ok) ok = mbar_wait(&bars[Cfg::kWFull + 0], 0u, abort_flag);
+            bool ok = mbar_wait(&bars[kXYReady], 0u, abort_flag);
+            if (ok) ok = mbar_wait(&bars[kUReady + 0], 0u, abort_flag);
+            if (ok) ok = mbar_wait(&bars[kWReady + 0], 0u, abort_flag);
             if (ok) {
                 tc_fence_after_sync();
-                issue_t(tT1, sX_u, sU_u);
+                issue_t(tT1, sX_u, sU_u, idesc_t1);
                 mma_commit(&bars[Cfg::kT1Full]);
-                issue_t(tT2, sY_u, sW_u);
+                issue_t(tT2, sY_u, sW_u, idesc_t2);
                 mma_commit(&bars[Cfg::kT2Full]);
                 if (!KS) mma_commit(&bars[Cfg::kWEmpty + 0]);        // MODE 1: V_j is read by dP(j) only
             }
@@ -396,7 +508,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 const uint32_t cur_u = sU_u + us * TILE, nxt_u = sU_u + nus * TILE;
                 const uint32_t cur_w = sW_u + ws * TILE, nxt_w = sW_u + nws * TILE;
                 const bool more = it + 1 < n_iter;
-                if (more) { ok = mbar_wait(&bars[Cfg::kUFull + nus], nuph & 1u, abort_flag); if (!ok) break; }
+                if (more) { ok = mbar_wait(&bars[kUReady + nus], nuph & 1u, abort_flag); if (!ok) break; }
                 if (KS) {
                     ok = mbar_wait(&bars[Cfg::kPHalf], (uint32_t)it & 1u, abort_flag);
                     if (!ok) break;
@@ -407,13 +519,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     tc_fence_after_sync();
                     issue_acc_half(tAcc2, tT1, cur_w, it > 0, 1);
                     mma_commit(&bars[Cfg::kWEmpty + ws]);                        // dO_i: dP^T(i) earlier, dV(i) last
-                    if (more) { issue_t(tT1, sX_u, nxt_u); mma_commit(&bars[Cfg::kT1Full]); }
+                    if (more) { issue_t(tT1, sX_u, nxt_u, idesc_t1); mma_commit(&bars[Cfg::kT1Full]); }
                 } else if (more) {
                     // dQ needs no second accumulator, so S is double-buffered in its columns: S(it+1)
                     // goes to the buffer S(it-1) left, which phase A(it-1) finished reading before the
                     // dS(it-1) hand-off this thread waited for in the previous step
                     tc_fence_after_sync();
-                    issue_t(((it + 1) & 1) ? tAcc2 : tT1, sX_u, nxt_u);
+                    issue_t(((it + 1) & 1) ? tAcc2 : tT1, sX_u, nxt_u, idesc_t1);
                     // a barrier per buffer: its previous phase, S(it-1), was observed by every warp
                     // before the dS(it-1) hand-off, so this completion cannot lap a waiter
                     mma_commit(&bars[Cfg::kT1Full + ((it + 1) & 1)]);
@@ -447,10 +559,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     }
                 }
                 if (more) {
-                    ok = mbar_wait(&bars[Cfg::kWFull + nws], nwph & 1u, abort_flag);
+                    ok = mbar_wait(&bars[kWReady + nws], nwph & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_t(tT2, sY_u, nxt_w);
+                    issue_t(tT2, sY_u, nxt_w, idesc_t2);
                     mma_commit(&bars[Cfg::kT2Full]);
                     if (!KS) mma_commit(&bars[Cfg::kWEmpty + nws]);
                 }
@@ -459,6 +571,31 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             if (ok) mma_commit(&bars[Cfg::kAccDone]);
         }
         __syncwarp();
+      } else if (STREAM_CONV) {
+        // ---------------------------------------------------------------- warps 18-19: streamed tiles -> fp16
+        // the producer's walk; a tile is touched between its arrival (U_full / W_full) and its first
+        // reader (the MMAs wait for U_conv / W_conv).  dO tiles are normalised on the way.
+        const int ct = (warp - kTmaWarp - 1) * 32 + lane;
+        int us = 0, ws = 0;
+        uint32_t uph = 0, wph = 0;
+        for (int it = 0; it < n_iter; ++it) {
+            bool ok = mbar_wait(&bars[Cfg::kUFull + us], uph & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            convert_tile_bf16_to_f16<false>(sU + us * TILE, TILE, ct, 64, 1.f);
+            fence_proxy_async_smem();
+            mbar_arrive_warp(&bars[Cfg::kUConv + us]);
+            if (KS) {
+                ok = mbar_wait(&bars[Cfg::kWFull + ws], wph & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                convert_tile_bf16_to_f16<true>(sW + ws * TILE, TILE, ct, 64, sc.do_mul);
+                fence_proxy_async_smem();
+                mbar_arrive_warp(&bars[Cfg::kWConv + ws]);
+            }
+            if (++us == UST) { us = 0; ++uph; }
+            if (++ws == WST) { ws = 0; ++wph; }
+        }
       }
     } else {
         // ---------------------------------------------------------------- P / dS and epilogue
@@ -475,8 +612,37 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const int64_t off = ((int64_t)b * a.H + head_x) * a.nq_pad + row_g;
             my_nlse2 = a.lse2[off];
             my_ndelta = a.delta[off];
+            if (ROWFORM) {
+                // the vectors are staged for the key-stationary kernels: take the row exponent out again
+                const int e_i = (int)a.erow[off];
+                my_nlse2 -= (float)e_i;            // -inf in the padding stays -inf
+                my_ndelta *= pow2i(e_i);
+            }
         }
+        // dS' = P' o (dP * tt_mul o Z + (-delta) * nd_mul): see "number formats" above
+        const uint64_t ttm2 = f2_pack(sc.tt_mul, sc.tt_mul), ndm2 = f2_pack(sc.nd_mul, sc.nd_mul);
+        const float zk = a.inv_keep * sc.tt_mul;
+        const uint64_t ladd2 = f2_pack(sc.l_add, sc.l_add);
+        my_ndelta *= sc.nd_mul;
         bool ok = true;
+        if (XY_CONV && n_iter > 0) {
+            // the stationary tiles, once per CTA: K_j and V_j, or Q_i (dO_i is only ever multiplied
+            // with the bf16 V_j tiles and stays as it is)
+            ok = mbar_wait(&bars[Cfg::kXYFull], 0u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                convert_tile_bf16_to_f16<false>(sX, (KS ? 2 : 1) * TILE, tid, 128 * NWG, 1.f);   // Y follows X
+                fence_proxy_async_smem();
+                mbar_arrive_warp(&bars[Cfg::kXYConv]);
+                if (K_COPY && tid == 0 && mbar_wait(&bars[Cfg::kXYConv], 0u, abort_flag)) {
+                    // the fp16 K tile is what the dQ kernel streams: keep a copy (rows beyond Nk are clipped)
+#pragma unroll
+                    for (int bx = 0; bx < Cfg::kNBox; ++bx)
+                        tma_store_4d(&map_aux, sX + bx * kBoxBytes, bx * 64, head_x, tile * kTile, b);
+                    tma_store_commit();       // read out before the kernel ends: the epilogue waits for all groups
+                }
+            }
+        }
 
         // fused kernel: add the dQ tile of step `jt` (queries on the TMEM lanes, my D / NWG columns)
         // to the fp32 sums in global memory; the order of additions across CTAs is not fixed
@@ -590,7 +756,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                 for (int jj = 0; jj < 2; ++jj) {
                     const int j = 2 * hf + jj;
-                    const uint64_t L = *reinterpret_cast<const uint64_t*>(lse_s + cb + 8 * j + 2 * lq);
+                    uint64_t L = *reinterpret_cast<const uint64_t*>(lse_s + cb + 8 * j + 2 * lq);
+                    if (ROWFORM) L = f2_add(L, ladd2);
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -633,7 +800,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                                 if (!(kw & 1u)) z0 = 0.f;
                                 if (!(kw & 2u)) z1 = 0.f;
                             }
-                            pk[h][2 * jj + k] = pack2<BF16>(z0, z1);
+                            pk[h][2 * jj + k] = pack2<false>(z0, z1);
                         }
                 if (hf == 1) {
                     tmem_wait_st();                                 // the first half's stores were issued a half-phase ago
@@ -662,7 +829,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                     for (int jj = 0; jj < 2; ++jj) {
                         const int j = 2 * hf + jj;
-                        const uint64_t nd = *reinterpret_cast<const uint64_t*>(del_s + cb + 8 * j + 2 * lq);
+                        const uint64_t nd = f2_mul(*reinterpret_cast<const uint64_t*>(del_s + cb + 8 * j + 2 * lq), ndm2);
 #pragma unroll
                         for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -672,13 +839,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                                 uint64_t tt;
                                 if (drop) {
                                     const uint32_t kw = kbits >> (16 * h + i0);
-                                    tt = f2_fma(dp, f2_pack((kw & 1u) ? a.inv_keep : 0.f, (kw & 2u) ? a.inv_keep : 0.f), nd);
+                                    tt = f2_fma(dp, f2_pack((kw & 1u) ? zk : 0.f, (kw & 2u) ? zk : 0.f), nd);
                                 } else {
-                                    tt = f2_add(dp, nd);
+                                    tt = f2_fma(dp, ttm2, nd);
                                 }
                                 float d0, d1;
                                 f2_unpack(f2_mul(f2_pack(__uint_as_float(pf[h][i0]), __uint_as_float(pf[h][i0 + 1])), tt), d0, d1);
-                                pk[h][2 * jj + k] = pack2<BF16>(d0, d1);
+                                pk[h][2 * jj + k] = pack2<false>(d0, d1);
                             }
                     }
                     if (hf == 1) {
@@ -724,7 +891,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 for (int hf = 0; hf < 2; ++hf) {
 #pragma unroll
                     for (int c4 = hf * (CPT / 8); c4 < (hf + 1) * (CPT / 8); ++c4) {
-                        const ulonglong2 L = l2[c4];
+                        ulonglong2 L = l2[c4];
+                        if (ROWFORM) { L.x = f2_add(L.x, ladd2); L.y = f2_add(L.y, ladd2); }
                         float x0, x1, x2, x3;
                         f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 0), PF(c4 * 4 + 1)), sc2, L.x), x0, x1);
                         f2_unpack(f2_fma(f2_pack(PF(c4 * 4 + 2), PF(c4 * 4 + 3)), sc2, L.y), x2, x3);
@@ -752,7 +920,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             if (!((kb[c >> 5] >> (c & 31)) & 1u)) x0 = 0.f;
                             if (!((kb[(c + 1) >> 5] >> ((c + 1) & 31)) & 1u)) x1 = 0.f;
                         }
-                        pk[e] = pack2<BF16>(x0, x1);
+                        pk[e] = pack2<false>(x0, x1);
                     }
                     if (hf == 1) {
                         // the first half's store was issued a half-phase ago
@@ -820,7 +988,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                     for (int c4 = hf * (CPT / 8); c4 < (hf + 1) * (CPT / 8); ++c4) {
                         ulonglong2 nd;
-                        if (KS) nd = d2[c4];
+                        if (KS) { nd = d2[c4]; nd.x = f2_mul(nd.x, ndm2); nd.y = f2_mul(nd.y, ndm2); }
                         else { nd.x = my_nd2; nd.y = my_nd2; }
                         const int c = c4 * 4;
                         uint64_t dpa = f2_pack(__uint_as_float(dr[c >> 5][c & 31]), __uint_as_float(dr[c >> 5][(c + 1) & 31]));
@@ -828,19 +996,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         uint64_t ta, tb;
                         if (drop) {
                             const uint32_t kw = kb[c >> 5] >> (c & 31);
-                            const uint64_t za = f2_pack((kw & 1u) ? a.inv_keep : 0.f, (kw & 2u) ? a.inv_keep : 0.f);
-                            const uint64_t zb = f2_pack((kw & 4u) ? a.inv_keep : 0.f, (kw & 8u) ? a.inv_keep : 0.f);
+                            const uint64_t za = f2_pack((kw & 1u) ? zk : 0.f, (kw & 2u) ? zk : 0.f);
+                            const uint64_t zb = f2_pack((kw & 4u) ? zk : 0.f, (kw & 8u) ? zk : 0.f);
                             ta = f2_fma(dpa, za, nd.x);
                             tb = f2_fma(dpb, zb, nd.y);
                         } else {
-                            ta = f2_add(dpa, nd.x);
-                            tb = f2_add(dpb, nd.y);
+                            ta = f2_fma(dpa, ttm2, nd.x);
+                            tb = f2_fma(dpb, ttm2, nd.y);
                         }
                         float d0, d1, d2v, d3;
                         f2_unpack(f2_mul(f2_pack(PF(c), PF(c + 1)), ta), d0, d1);
                         f2_unpack(f2_mul(f2_pack(PF(c + 2), PF(c + 3)), tb), d2v, d3);
-                        pk[(c4 - hf * (CPT / 8)) * 2 + 0] = pack2<BF16>(d0, d1);
-                        pk[(c4 - hf * (CPT / 8)) * 2 + 1] = pack2<BF16>(d2v, d3);
+                        pk[(c4 - hf * (CPT / 8)) * 2 + 0] = pack2<false>(d0, d1);
+                        pk[(c4 - hf * (CPT / 8)) * 2 + 1] = pack2<false>(d2v, d3);
                     }
                     if (hf == 1) {
                         tmem_wait_st();
@@ -885,7 +1053,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
             for (int o = 0; o < kOuts; ++o) {
                 const uint32_t tacc = (o == 0 ? tAcc1 : tAcc2) + lane_off + (uint32_t)(wg * kCols);
-                const float mul = (o == 0) ? a.scale : a.inv_keep;
+                const float mul = (o == 0) ? sc.acc1_mul : sc.acc2_mul;
                 uint8_t* stage = sU + o * TILE;                // the U ring is idle once all MMAs completed
 #pragma unroll
                 for (int c0 = 0; c0 < kCols; c0 += 32) {
@@ -928,52 +1096,148 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
     }
 
+    if (K_COPY && threadIdx.x == 0) tma_store_wait_read<0>();   // the K copy's source tile (also when unwinding)
     tc_fence_before_sync();
     __syncthreads();
     if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
-    if (threadIdx.x == 0 && *abort_flag && a.status) atomicExch(a.status, 2 + MODE);
+    if (threadIdx.x == 0 && *abort_flag) report_status(a.status, 2 + MODE);
     // the end of this grid must still mean the end of the dK/dV grid before it in the stream
     if (MODE == 1) grid_dependency_wait();
 }
 
-// negated delta and negated scaled lse (the main kernels add them).  D / 8 lanes share one
-// (b, h, padded query row), 16 bytes of O and dO each, so a warp covers 256 / D rows.
-template <typename T, int D>
+// Largest magnitude among the eight 16-bit values of a 16-byte piece, folded into a running maximum
+// of magnitude bit patterns (two per word; for fp16 and bf16 alike a larger magnitude is a larger
+// unsigned pattern).
+__device__ __forceinline__ uint32_t absmax16_acc(uint32_t m, const uint4& v) {
+    asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(v.x & 0x7FFF7FFFu));
+    asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(v.y & 0x7FFF7FFFu));
+    asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(v.z & 0x7FFF7FFFu));
+    asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(v.w & 0x7FFF7FFFu));
+    return m;
+}
+// Block-wide maximum of those patterns, as a float, folded into *slot (an fp32 bit pattern; for
+// non-negative floats the unsigned order is the numeric order, so atomicMax on the bits is exact).
+template <typename T>
+__device__ __forceinline__ void absmax16_commit(uint32_t m, float* slot, uint32_t* red) {
+    m = max(m & 0xFFFFu, m >> 16);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = max(m, red[w]);
+        const unsigned short bits = (unsigned short)m;
+        const float f = to_f32<T>(*reinterpret_cast<const T*>(&bits));
+        atomicMax(reinterpret_cast<uint32_t*>(slot), __float_as_uint(f));
+    }
+}
+
+// Preprocess launch.  Blocks [0, n_row_blocks): negated delta and the shifted, negated, scaled lse (the
+// main kernels add them), and max |dO| of the block's column.  D / 8 lanes share one (b, h, padded query
+// row), 16 bytes of O and dO each, so a warp covers 256 / D rows; a block's rows lie in one (b, h).
+// Blocks beyond: max |V| over a slab of one (b, K/V head) column's visible keys.
+// ranges[(b * Hkv + hk) * 2 + {0, 1}] = max |dO| over the K/V head's query heads, max |V|; zeroed before.
+// COPIES (bf16): also the fp16 copies the main kernels stream, dense (B, Nq, H, D): Q as it is, dO row
+// by row normalised to max < 2^15 by 2^-e_i, with e_i kept in `erow` and folded into the two vectors
+// (lse' = kPShift - lse*log2(e) + e_i, -delta * 2^-e_i: the "row form" of make_scales).
+struct PreprocessCopies {
+    const void* o_lo; int64_t l_sb, l_sn, l_sh;     // optional residual of O (any dtype)
+    const void* q; int64_t q_sb, q_sn, q_sh;
+    uint16_t* q16; uint16_t* do16; float* erow;
+};
+template <typename T, int D, bool COPIES>
 __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
-                      float* __restrict__ lse2, float* __restrict__ delta, int B, int Nq, int H, int nq_pad,
-                      int64_t o_sb, int64_t o_sn, int64_t o_sh, int64_t g_sb, int64_t g_sn, int64_t g_sh) {
+                      float* __restrict__ lse2, float* __restrict__ delta, float* __restrict__ ranges,
+                      int B, int Nq, int H, int Hkv, int nq_pad,
+                      int64_t o_sb, int64_t o_sn, int64_t o_sh, int64_t g_sb, int64_t g_sn, int64_t g_sh,
+                      const T* __restrict__ v, int64_t v_sb, int64_t v_sn, int64_t v_sh, int Nk,
+                      const int32_t* __restrict__ kv_len, int n_row_blocks, int v_slabs, const PreprocessCopies cp) {
     constexpr int LPR = D / 8;                 // lanes per row
     constexpr int RPW = 32 / LPR;              // rows per warp
+    constexpr int kVRows = 256;                // keys per slab of the V scan
+    __shared__ uint32_t red[8];
     const int lane = threadIdx.x & 31, sub = lane % LPR;
+    if ((int)blockIdx.x >= n_row_blocks) {
+        const int vb = (int)blockIdx.x - n_row_blocks;
+        const int slab = vb % v_slabs, col = vb / v_slabs;          // col = b * Hkv + hk
+        const int hk = col % Hkv, b = col / Hkv;
+        const int nk = kv_len_of(kv_len, b, Nk);
+        uint32_t m = 0u;
+        const int j_end = min(nk, (slab + 1) * kVRows);
+        for (int j = slab * kVRows + (int)(threadIdx.x / LPR); j < j_end; j += 256 / LPR)
+            m = absmax16_acc(m, *reinterpret_cast<const uint4*>(v + b * v_sb + (int64_t)j * v_sn + hk * v_sh + sub * 8));
+        absmax16_commit<T>(m, ranges + 2 * (int64_t)col + 1, red);
+        return;
+    }
     const int64_t row = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + lane / LPR;
     const bool live = row < (int64_t)B * H * nq_pad;
     const int i = live ? (int)(row % nq_pad) : 0;
     const int64_t bh = live ? row / nq_pad : 0;
     const int h = (int)(bh % H), b = (int)(bh / H);
     float s = 0.f;
+    uint32_t m = 0u;
     if (live && i < Nq) {
         const uint4 vo = *reinterpret_cast<const uint4*>(o + b * o_sb + i * o_sn + h * o_sh + sub * 8);
         const uint4 vg = *reinterpret_cast<const uint4*>(d_o + b * g_sb + i * g_sn + h * g_sh + sub * 8);
         const T* eo = reinterpret_cast<const T*>(&vo);
         const T* eg = reinterpret_cast<const T*>(&vg);
+        if (cp.o_lo) {
+            // delta from the output as the forward computed it, not as 16 bits hold it
+            const uint4 vl = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(cp.o_lo) + b * cp.l_sb +
+                                                             i * cp.l_sn + h * cp.l_sh + sub * 8);
+            const T* el = reinterpret_cast<const T*>(&vl);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(eo[e]), to_f32<T>(eg[e]), s);
+            for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(eo[e]) + to_f32<T>(el[e]), to_f32<T>(eg[e]), s);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(eo[e]), to_f32<T>(eg[e]), s);
+        }
+        m = absmax16_acc(m, vg);
     }
 #pragma unroll
     for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (live && sub == 0) {
-        if (i < Nq) { delta[row] = -s; lse2[row] = -lse[bh * Nq + i] * kLog2e; }
-        else        { delta[row] = 0.f; lse2[row] = -INFINITY; }
+    int e_i = 0;
+    if (COPIES) {
+        // the row's largest |dO| (a bf16 bit pattern) over the lanes that share the row
+        uint32_t mr = max(m & 0xFFFFu, m >> 16);
+#pragma unroll
+        for (int off = LPR / 2; off > 0; off >>= 1) mr = max(mr, __shfl_xor_sync(0xffffffffu, mr, off));
+        e_i = log2_bound_bits(mr << 16) - 15;
+        if (live && i < Nq) {
+            const int64_t at = (((int64_t)b * Nq + i) * H + h) * D + sub * 8;
+            const uint64_t mul2 = f2_pack(pow2i(-e_i), pow2i(-e_i));
+            const T* qp = reinterpret_cast<const T*>(cp.q);
+            const uint4 vq = *reinterpret_cast<const uint4*>(qp + b * cp.q_sb + i * cp.q_sn + h * cp.q_sh + sub * 8);
+            const uint4 vg = *reinterpret_cast<const uint4*>(d_o + b * g_sb + i * g_sn + h * g_sh + sub * 8);
+            *reinterpret_cast<uint4*>(cp.q16 + at) = make_uint4(bf16x2_to_f16x2(vq.x), bf16x2_to_f16x2(vq.y),
+                                                                bf16x2_to_f16x2(vq.z), bf16x2_to_f16x2(vq.w));
+            *reinterpret_cast<uint4*>(cp.do16 + at) = make_uint4(bf16x2_to_f16x2(vg.x, mul2), bf16x2_to_f16x2(vg.y, mul2),
+                                                                 bf16x2_to_f16x2(vg.z, mul2), bf16x2_to_f16x2(vg.w, mul2));
+        }
     }
+    if (live && sub == 0) {
+        if (i < Nq) { delta[row] = -s * pow2i(-e_i); lse2[row] = kPShift - lse[bh * Nq + i] * kLog2e + (float)e_i; }
+        else        { delta[row] = 0.f; lse2[row] = -INFINITY; }
+        if (COPIES) cp.erow[row] = (i < Nq) ? (float)e_i : 0.f;
+    }
+    // the block's first row decides the column (all its rows share it: 128 is a multiple of the rows per block)
+    const int64_t row0 = (int64_t)blockIdx.x * 8 * RPW;
+    const int64_t bh0 = row0 / nq_pad;
+    const int group = H / Hkv;
+    const int64_t col0 = (bh0 / H) * Hkv + (bh0 % H) / group;
+    absmax16_commit<T>(m, ranges + 2 * col0, red);
 }
 
 // fused backward: fp32 dQ sums (tiles of [D/4][128 rows][4]) * scale -> dQ in the call's dtype and layout
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
-bwd_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, int Nq, int H, int n_tiles, float scale,
-                      int64_t sb, int64_t sn, int64_t sh) {
+bwd_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, int Nq, int H, int n_tiles, float scale_in,
+                      int64_t sb, int64_t sn, int64_t sh, const float* __restrict__ ranges, int Hkv, float inv_keep) {
     const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    // the sums carry the column's dS scaling (see "number formats"): the same constant the dK epilogue uses
+    const float scale = make_scales(ranges + 2 * ((int64_t)b * Hkv + h / (H / Hkv)), D, inv_keep, scale_in,
+                                    kDoAsIs).acc1_mul;     // acc1_mul does not depend on dO's form
     const float* src = acc + (((int64_t)b * H + h) * n_tiles + tile) * (int64_t)(kTile * D);
     const int row = threadIdx.x & 127;
     const int i = tile * kTile + row;
@@ -992,34 +1256,58 @@ bwd_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, int Nq,
     }
 }
 
-template <int D, bool BF16>
+// INLINE: bf16 call without room for the fp16 copies (the workspace-free entry point): the main kernels
+// convert their tiles themselves.
+template <int D, bool BF16, bool INLINE>
 int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
     const CUtensorMapDataType dt = BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    constexpr bool COPIES = BF16 && !INLINE;
     cudaStream_t st = (cudaStream_t)p.stream;
     const int nq_pad = (int)align_up((size_t)p.Nq, 128);
-    float* delta = (float*)((char*)p.workspace + ws.delta_off);
-    float* lse2 = (float*)((char*)p.workspace + ws.lse2_off);
+    char* wsp = (char*)p.workspace;
+    float* delta = (float*)(wsp + ws.delta_off);
+    float* lse2 = (float*)(wsp + ws.lse2_off);
+    float* ranges = (float*)(wsp + ws.rng_off);
+    if (COPIES && (ws.q16_bytes == 0 || ws.do16_bytes == 0)) { set_error("workspace layout lacks the fp16 copies"); return FA_EWORKSPACE; }
 
     const bool fused = ws.dq_bytes > 0;
-    float* dq_acc = fused ? (float*)((char*)p.workspace + ws.dq_off) : nullptr;
+    float* dq_acc = fused ? (float*)(wsp + ws.dq_off) : nullptr;
     const bool drop = dropout_threshold(p.dropout_p) != 0u;
 
     const int phases = p.bwd_phases ? p.bwd_phases : 7;
     if (phases & 1) {
         if (fused) FA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, ws.dq_bytes, st));
+        FA_CUDA_CHECK(cudaMemsetAsync(ranges, 0, ws.rng_bytes, st));
         const int64_t rows = (int64_t)p.B * p.H * nq_pad;
         constexpr int kRowsPerBlock = 8 * (256 / D);
-        bwd_preprocess_kernel<T, D><<<(unsigned)((rows + kRowsPerBlock - 1) / kRowsPerBlock), 256, 0, st>>>(
-            (const T*)p.o.ptr, (const T*)p.d_o.ptr, p.lse, lse2, delta, p.B, p.Nq, p.H, nq_pad,
-            p.o.stride_b, p.o.stride_n, p.o.stride_h, p.d_o.stride_b, p.d_o.stride_n, p.d_o.stride_h);
+        const int n_row_blocks = (int)((rows + kRowsPerBlock - 1) / kRowsPerBlock);
+        const int v_slabs = (p.Nk + 255) / 256;
+        const int64_t n_blocks = (int64_t)n_row_blocks + (int64_t)p.B * p.Hkv * v_slabs;
+        if (rows + kRowsPerBlock > 0x7fffffff || n_blocks > 0x7fffffff) { set_error("problem too large for the preprocess grid"); return FA_EUNSUPPORTED; }
+        PreprocessCopies cp = {};
+        cp.o_lo = p.o_lo.ptr; cp.l_sb = p.o_lo.stride_b; cp.l_sn = p.o_lo.stride_n; cp.l_sh = p.o_lo.stride_h;
+        if (COPIES) {
+            cp.q = p.q.ptr; cp.q_sb = p.q.stride_b; cp.q_sn = p.q.stride_n; cp.q_sh = p.q.stride_h;
+            cp.q16 = (uint16_t*)(wsp + ws.q16_off); cp.do16 = (uint16_t*)(wsp + ws.do16_off);
+            cp.erow = (float*)(wsp + ws.erow_off);
+        }
+        bwd_preprocess_kernel<T, D, COPIES><<<(unsigned)n_blocks, 256, 0, st>>>(
+            (const T*)p.o.ptr, (const T*)p.d_o.ptr, p.lse, lse2, delta, ranges, p.B, p.Nq, p.H, p.Hkv, nq_pad,
+            p.o.stride_b, p.o.stride_n, p.o.stride_h, p.d_o.stride_b, p.d_o.stride_n, p.d_o.stride_h,
+            (const T*)p.v.ptr, p.v.stride_b, p.v.stride_n, p.v.stride_h, p.Nk, p.kv_lengths, n_row_blocks, v_slabs, cp);
         FA_CUDA_CHECK(cudaGetLastError());
     }
 
-    CUtensorMap mq, mk, mv, mg, mdq, mdk, mdv;
+    CUtensorMap mq, mk, mv, mg, mdq, mdk, mdv, mq16, mg16, mk16;
     int r;
     auto mk_map = [&](CUtensorMap* m, const fa_b200_tensor& t, int N, int H) {
-        return make_tmap_bnhd(m, t.ptr, dt, 2, p.B, N, H, D, t.stride_b, t.stride_n, t.stride_h, 128, 64, true);
+        return cached_tmap_bnhd(m, t.ptr, dt, 2, p.B, N, H, D, t.stride_b, t.stride_n, t.stride_h, 128, 64, true);
+    };
+    // a dense fp16 (B, N, H, D) copy in the workspace
+    auto mk_copy = [&](CUtensorMap* m, size_t off, int N, int H) {
+        return cached_tmap_bnhd(m, wsp + off, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.B, N, H, D, (int64_t)N * H * D,
+                                (int64_t)H * D, (int64_t)D, 128, 64, true);
     };
     if ((r = mk_map(&mq, p.q, p.Nq, p.H)) || (r = mk_map(&mk, p.k, p.Nk, p.Hkv)) ||
         (r = mk_map(&mv, p.v, p.Nk, p.Hkv)) || (r = mk_map(&mg, p.d_o, p.Nq, p.H)) ||
@@ -1028,10 +1316,25 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
         set_error("cuTensorMapEncodeTiled failed (%d)", r);
         return FA_ECUDA;
     }
+    mq16 = mq; mg16 = mg; mk16 = mk;
+    if (COPIES) {
+        if ((r = mk_copy(&mq16, ws.q16_off, p.Nq, p.H)) || (r = mk_copy(&mg16, ws.do16_off, p.Nq, p.H)) ||
+            (ws.k16_bytes && (r = mk_copy(&mk16, ws.k16_off, p.Nk, p.Hkv)))) {
+            set_error("cuTensorMapEncodeTiled failed (%d)", r);
+            return FA_ECUDA;
+        }
+    }
     BwdArgs a;
-    a.lse2 = lse2; a.delta = delta; a.dq_acc = dq_acc; a.status = p.status_word;
+    a.lse2 = lse2; a.delta = delta; a.ranges = ranges; a.dq_acc = dq_acc; a.status = p.status_word; a.wait_limit_ms = p.wait_limit_ms;
+    a.erow = COPIES ? (const float*)(wsp + ws.erow_off) : nullptr;
     a.kv_len = p.kv_lengths;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv; a.nq_pad = nq_pad;
+    {
+        // columns whose Q, K, V and dO (16-bit) fit the budget
+        const int64_t col_bytes = 2 * ((int64_t)p.Nq + p.Nk) * D * 2;
+        const int64_t g = (int64_t)tile::kBwdGroupBytes / (col_bytes > 0 ? col_bytes : 1);
+        a.cols_per_group = (int)(g < 1 ? 1 : (g > 65535 ? 65535 : g));
+    }
     a.causal = p.causal;
     a.shift = p.causal ? p.causal_shift : 0;
     a.scale = p.scale;
@@ -1041,33 +1344,39 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     a.key = philox_make_key(p.seed, p.offset);
     a.rng = dropout_origin_of(p);
 
+    static std::mutex smem_mu;             // per (D, dtype, INLINE) instance of this function
+    static uint64_t smem_done[6] = {};     // [kernel mode and dropout flag] -> devices whose limit is set
     constexpr int kThreads = 128 * kNWG + kExtraThreads;
     const dim3 grid_kv((p.Nk + kTile - 1) / kTile, p.Hkv, p.B);
     const dim3 grid_q((p.Nq + kTile - 1) / kTile, p.H, p.B);
     if constexpr (D == 64) if (fused) {
         // one key-stationary kernel for dK, dV and the fp32 dQ sums, then the conversion of dQ
-        auto k2 = drop ? bwd_sm100_kernel<D, BF16, 2, kNWG, true> : bwd_sm100_kernel<D, BF16, 2, kNWG, false>;
+        auto k2 = drop ? bwd_sm100_kernel<D, BF16, 2, kNWG, true, INLINE> : bwd_sm100_kernel<D, BF16, 2, kNWG, false, INLINE>;
         const int smem2 = drop ? BwdCfg<D, 2, true>::kSmemBytes : BwdCfg<D, 2, false>::kSmemBytes;
-        FA_CUDA_CHECK(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
+        FA_CUDA_CHECK(set_smem_limit_once(k2, smem2, p.device, &smem_done[drop ? 5 : 4], &smem_mu));
         if (phases & 2) {
-            k2<<<grid_kv, kThreads, smem2, st>>>(mk, mv, mq, mg, mdk, mdv, a);
+            k2<<<grid_kv, kThreads, smem2, st>>>(mk, mv, mq16, mg16, mdk, mdv, mdk, a);
             FA_CUDA_CHECK(cudaGetLastError());
         }
         if (phases & 4) {
             bwd_dq_convert_kernel<T, D><<<grid_q, 256, 0, st>>>(dq_acc, (T*)p.dq.ptr, p.Nq, p.H, nq_pad / kTile, p.scale,
-                                                               p.dq.stride_b, p.dq.stride_n, p.dq.stride_h);
+                                                               p.dq.stride_b, p.dq.stride_n, p.dq.stride_h, ranges, p.Hkv,
+                                                               a.inv_keep);
             FA_CUDA_CHECK(cudaGetLastError());
         }
         return FA_OK;
     }
-    auto k0 = drop ? bwd_sm100_kernel<D, BF16, 0, kNWG, true> : bwd_sm100_kernel<D, BF16, 0, kNWG, false>;
-    auto k1 = drop ? bwd_sm100_kernel<D, BF16, 1, kNWG, true> : bwd_sm100_kernel<D, BF16, 1, kNWG, false>;
+    if (COPIES && ws.k16_bytes == 0) { set_error("workspace layout lacks the fp16 copy of K"); return FA_EWORKSPACE; }
+    auto k0 = drop ? bwd_sm100_kernel<D, BF16, 0, kNWG, true, INLINE> : bwd_sm100_kernel<D, BF16, 0, kNWG, false, INLINE>;
+    auto k1 = drop ? bwd_sm100_kernel<D, BF16, 1, kNWG, true, INLINE> : bwd_sm100_kernel<D, BF16, 1, kNWG, false, INLINE>;
     const int smem0 = drop ? BwdCfg<D, 0, true>::kSmemBytes : BwdCfg<D, 0, false>::kSmemBytes;
     const int smem1 = drop ? BwdCfg<D, 1, true>::kSmemBytes : BwdCfg<D, 1, false>::kSmemBytes;
-    FA_CUDA_CHECK(cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, smem0));
-    FA_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
+    FA_CUDA_CHECK(set_smem_limit_once(k0, smem0, p.device, &smem_done[drop ? 1 : 0], &smem_mu));
+    FA_CUDA_CHECK(set_smem_limit_once(k1, smem1, p.device, &smem_done[drop ? 3 : 2], &smem_mu));
     if (phases & 2) {
-        k0<<<grid_kv, kThreads, smem0, st>>>(mk, mv, mq, mg, mdk, mdv, a);
+        // stationary K_j, V_j; streamed Q_i, dO_i (bf16 with copies: their fp16 copies; the kernel leaves
+        // the fp16 copy of K behind for the dQ kernel)
+        k0<<<grid_kv, kThreads, smem0, st>>>(mk, mv, mq16, mg16, mdk, mdv, mk16, a);
         FA_CUDA_CHECK(cudaGetLastError());
     }
     if (phases & 4) {
@@ -1079,10 +1388,12 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
         cfg.attrs = attr;
         // Only behind the dK/dV kernel of this call, and only while one head's K and V are small
         // beside L2 (the two kernels stream different heads' tiles at the same time): measured on
-        // B200 (H32 D128 bf16 causal) the overlap takes 1 % off the backward at N = 4096; longer
-        // sequences showed no gain.
-        cfg.numAttrs = ((phases & 2) && (int64_t)p.Nk * D * 4 <= (int64_t)4 << 20) ? 1 : 0;
-        FA_CUDA_CHECK(cudaLaunchKernelEx(&cfg, k1, mq, mg, mk, mv, mdq, mdq, a));
+        // B200 (H32 D128 causal) the overlap takes 1 % off the backward at N = 4096; longer
+        // sequences showed no gain.  Never with the fp16 copies: the dQ kernel streams the copy of K
+        // that the dK/dV kernel is still writing.
+        cfg.numAttrs = (!COPIES && (phases & 2) && (int64_t)p.Nk * D * 4 <= (int64_t)tile::kBwdOverlapMaxKvBytes) ? 1 : 0;
+        // stationary Q_i (its fp16 copy), dO_i; streamed K_j (its fp16 copy), V_j
+        FA_CUDA_CHECK(cudaLaunchKernelEx(&cfg, k1, mq16, mg, mk16, mv, mdq, mdq, mdq, a));
     }
     return FA_OK;
 }
@@ -1094,12 +1405,15 @@ bool sm100_bwd_fused_supported(const fa_b200_params& p) {
     // to share dP^T's columns, which serialises the step, and the fp32 additions (64 KB per step)
     // cost more than recomputing S and dP in a second kernel: measured on B200 (B4 N4096 H32
     // causal) 2.12 ms against 1.95 ms for the two kernels.
-    return p.D == 64;
+    return tile::bwd_one_kernel(p.D);
 }
 
 int sm100_bwd(const fa_b200_params& p, const BwdWorkspace& ws) {
-    if (p.dtype == FA_B200_BF16) return p.D == 128 ? launch<128, true>(p, ws) : launch<64, true>(p, ws);
-    return p.D == 128 ? launch<128, false>(p, ws) : launch<64, false>(p, ws);
+    if (p.dtype == FA_B200_BF16) {
+        if (ws.q16_bytes == 0) return p.D == 128 ? launch<128, true, true>(p, ws) : launch<64, true, true>(p, ws);
+        return p.D == 128 ? launch<128, true, false>(p, ws) : launch<64, true, false>(p, ws);
+    }
+    return p.D == 128 ? launch<128, false, false>(p, ws) : launch<64, false, false>(p, ws);
 }
 
 }  // namespace fa

@@ -55,16 +55,27 @@ static inline DropoutOrigin dropout_origin_of(const fa_b200_params& p) {
 }
 
 // ---- workspace layout (backward) -------------------------------------------
-// [ delta : B*H*nq_pad fp32 | pad to 256 | lse*log2(e) : B*H*nq_pad fp32 (tensor-core family only)
-//   | pad to 256 | dQ sums : B*H*nq_pad*D fp32 (one-kernel tensor-core backward only) ]
-// nq_pad = Nq rounded up to 128; the CUDA-core family indexes delta unpadded.
+// [ delta : B*H*nq_pad fp32 | lse*log2(e) : B*H*nq_pad fp32 | ranges : B*Hkv x {max|dO|, max|V|} fp32
+//   | row exponents of dO : B*H*nq_pad fp32 | fp16 copies of Q, dO (B*Nq*H*D each) and K (B*Nk*Hkv*D)
+//   | dQ sums : B*H*nq_pad*D fp32 ]
+// every region starts on a 256-byte boundary.  delta alone serves the CUDA-core family (which
+// indexes it unpadded); lse and ranges belong to the tensor-core family; the row exponents and
+// the fp16 copies to its bf16 calls (tcgen05.mma wants one format for both operands, see
+// sm100_ptx.cuh) unless `inline_conversion` is asked for, which converts the tiles inside the main
+// kernels instead and needs no copies; the dQ sums to the one-kernel backward.
+// nq_pad = Nq rounded up to 128.
 struct BwdWorkspace {
     size_t delta_off, delta_bytes;
     size_t lse2_off, lse2_bytes;
+    size_t rng_off, rng_bytes;
+    size_t erow_off, erow_bytes;
+    size_t q16_off, q16_bytes;
+    size_t do16_off, do16_bytes;
+    size_t k16_off, k16_bytes;
     size_t dq_off, dq_bytes;
     size_t total;
 };
-BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant);
+BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant, bool inline_conversion = false);
 
 // ---- kernel families ---------------------------------------------------------
 // CUDA-core tiles (simt_kernels.cu)

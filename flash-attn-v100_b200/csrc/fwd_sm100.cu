@@ -24,13 +24,15 @@
 //               is in TMEM (the threads are still computing the second)
 //   warps 0-3   softmax + epilogue of tile 0, one thread per query row (TMEM lane)
 //   warps 4-7   softmax + epilogue of tile 1
-//   warps 10-11 idle (they complete the third warpgroup for setmaxnreg)
+//   warps 10-11 bf16 inputs: convert each V_j tile to fp16 in place as it lands, so that PV runs
+//               f16 x f16 with P rounded to fp16 instead of bf16 (see sm100_ptx.cuh); fp16 inputs: idle
+//               (the two warps complete the third warpgroup for setmaxnreg)
 //
 // Online softmax in the log2 domain with scale*log2(e) folded into one FMA.
 // The running maximum is only refreshed when it grows by more than 2^8 (warp
 // vote), so the O accumulator in TMEM is rescaled rarely; the final division
-// by the row sum makes the result exact either way.  P is rounded to the input
-// dtype and written over S in TMEM; dropout zeroes P entries (the 1/(1-p)
+// by the row sum makes the result exact either way.  P is rounded to fp16 (whatever
+// the input dtype) and written over S in TMEM; dropout zeroes P entries (the 1/(1-p)
 // factor is applied once to O), the row sum uses the undropped P.
 //
 // TMEM columns: S0/P0 [0,128)  S1/P1 [128,256)  O0 [256,256+D)  O1 [384,384+D).
@@ -42,6 +44,7 @@
 #include "fa_common.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
+#include "tile_config.cuh"
 #include <type_traits>
 
 namespace fa {
@@ -49,31 +52,31 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kBlockM = 128;        // query rows per tile
-constexpr int kBlockN = 128;        // key rows per block
-constexpr int kThreads = 384;       // 2 softmax warpgroups + 1 warpgroup holding the MMA and TMA warps
+constexpr int kBlockM = tile::kBlockM;      // query rows per tile
+constexpr int kBlockN = tile::kBlockN;      // key rows per block
+constexpr int kThreads = 32 * tile::kFwdWarps;   // 2 softmax warpgroups + 1 warpgroup holding the MMA, TMA and converting warps
 constexpr int kBoxBytes = 128 * 128;   // one TMA box: 128 rows x 64 16-bit elements
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr float kRescaleThreshold = 8.0f;   // log2 units
+constexpr float kRescaleThreshold = tile::kFwdRescaleLog2;   // log2 units
 // Share of the exponentials evaluated by the FMA-pipe polynomial instead of the special-function
-// unit: in kPolyCount of every kPolyPeriod groups of four, two.  Measured on B200 (B4 N4096 H32 D128
-// causal forward): 0 % 0.559 ms, 25 % 0.544 ms, 50 % 0.563 ms.
-constexpr int kPolyPeriod = 2, kPolyCount = 1;
+// unit: in kPolyCount of every kPolyPeriod groups of four, two (tile_config.cuh has the measurements).
+constexpr int kPolyPeriod = tile::kFwdPolyPeriod, kPolyCount = tile::kFwdPolyCount;
 // The first 64 keys of P are handed to the MMA warp after this many of the second half's 64
 // exponentials (a multiple of 4), when their tcgen05.st has had time to complete.
-constexpr int kHalfSignalAt = 16;
+constexpr int kHalfSignalAt = tile::kFwdHalfSignalAt;
 // Register split after setmaxnreg.  The pool is what the CTA was launched with, 168 registers for
 // each of its 384 threads, not the whole file: a split that asks for more makes
 // setmaxnreg.inc wait for ever.
-constexpr int kRegsSoftmax = 208, kRegsOther = 88;   // measured best of 224/56, 216/72, 208/88, 200/104
+constexpr int kRegsSoftmax = tile::kFwdRegsSoftmax, kRegsOther = tile::kFwdRegsOther;
 static_assert(256 * kRegsSoftmax + 128 * kRegsOther <= 168 * kThreads, "register split exceeds the CTA's allocation");
+static_assert(tile::kFwdQTilesPerCta == 2, "the kernel is written for two query tiles per work item");
 
 template <int D>
 struct FwdCfg {
     static constexpr int kNBox = D / 64;
     static constexpr int kTileBytes = kNBox * kBoxBytes;
-    static constexpr int kStages = (D == 128) ? 2 : 4;
+    static constexpr int kStages = tile::fwd_kv_stages(D);
     // barrier slots
     static constexpr int kQFull = 0;                       // [2]
     static constexpr int kQEmpty = 2;                      // [2] last S MMA of the pair has read Q_t
@@ -85,13 +88,16 @@ struct FwdCfg {
     static constexpr int kPFull = kSFull + 2;              // [2] one arrival per warp of the warpgroup
     static constexpr int kODone = kPFull + 2;              // [2]
     static constexpr int kPHalf = kODone + 2;              // [2] first 64 keys of P_t stored (one arrival per warp)
-    static constexpr int kNumBars = kPHalf + 2;
+    static constexpr int kVConv = kPHalf + 2;              // [kStages] V_j converted to fp16 (one arrival per converting warp)
+    static constexpr int kNumBars = kVConv + kStages;
     static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + kNumBars * 8 + 64 + 1024;
 };
 
 struct FwdArgs {
     void* o;                       // (B, Nq, H, D) output, element strides below
     int64_t o_sb, o_sn, o_sh;
+    void* o_lo;                    // optional residual of the output (what rounding O to 16 bits dropped)
+    int64_t l_sb, l_sn, l_sh;
     float* lse;
     int32_t* status;
     const int32_t* kv_len;         // optional per-batch key counts
@@ -101,6 +107,7 @@ struct FwdArgs {
     int n_pairs;                   // ceil(Nq / 256)
     int items_per_head;            // causal: ceil(n_pairs / 2) mirrored items; else n_pairs
     int n_items;                   // items_per_head * B * H
+    int wait_limit_ms;             // limit of one mbarrier wait (0: the default)
     float scale_log2;              // scale * log2(e)
     uint32_t drop_thr;
     float inv_keep;
@@ -136,6 +143,10 @@ __device__ __forceinline__ int num_blocks(const FwdArgs& a, int pair, int t, int
     return (row0 < a.Nq) ? (kv_end + kBlockN - 1) / kBlockN : 0;
 }
 
+// P is stored as 2^(S c - m + kPShift): with the lazily refreshed maximum P <= 2^8, so the shifted value
+// stays below 2^14 in fp16 and entries down to 2^-20 of the row's largest keep full precision.
+constexpr float kPShift = 6.0f;
+
 template <int D, bool BF16, bool DROP>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -143,9 +154,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     using Cfg = FwdCfg<D>;
     constexpr int ST = Cfg::kStages;
     constexpr int TILE = Cfg::kTileBytes;
-    // P is rounded to the input dtype: tcgen05.mma kind::f16 wants A and B in one
-    // format (an fp16 A next to a bf16 B raises an illegal-instruction fault).
-    constexpr bool P_BF16 = BF16;
+    // tcgen05.mma kind::f16 wants A and B in one format (an fp16 A next to a bf16 B raises an
+    // illegal-instruction fault).  P is always fp16; a bf16 V tile is converted to fp16 in shared memory.
+    constexpr bool CONV = BF16;
+    constexpr bool P_BF16 = false;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -162,9 +174,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kNumBars; ++i) {
             const bool wg_bar = (i >= Cfg::kPFull && i < Cfg::kPFull + 2) || (i >= Cfg::kPHalf && i < Cfg::kPHalf + 2);
-            mbar_init(&bars[i], wg_bar ? 4u : 1u);
+            const bool conv_bar = (i >= Cfg::kVConv && i < Cfg::kVConv + ST);
+            mbar_init(&bars[i], wg_bar ? 4u : (conv_bar ? 2u : 1u));
         }
-        *abort_flag = 0u;
+        wait_control_init(abort_flag, a.wait_limit_ms);
         fence_mbar_init();
     }
     if (warp == 8) {
@@ -255,7 +268,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         // ------------------------------------------------------------ MMA issuer
         if (elect_one()) {
             constexpr uint32_t idesc_s = make_idesc_f16(BF16, BF16, kBlockM, kBlockN, false, false);
-            constexpr uint32_t idesc_pv = make_idesc_f16(P_BF16, BF16, kBlockM, D, false, true);
+            constexpr uint32_t idesc_pv = make_idesc_f16(false, false, kBlockM, D, false, true);   // P, V: fp16
             const uint32_t sQ_u = smem_u32(sQ), sK_u = smem_u32(sK), sV_u = smem_u32(sV);
 
             // Descriptors differ only in the 16-byte-granular start address held in their low
@@ -320,7 +333,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         const int ks = (kvc + j + 1) % ST;
                         const uint32_t kph = (uint32_t)((kvc + j + 1) / ST) & 1u;
                         bool k_ready = false;
-                        ok = mbar_wait(&bars[Cfg::kVFull + vs], vph, abort_flag);
+                        ok = mbar_wait(&bars[(CONV ? Cfg::kVConv : Cfg::kVFull) + vs], vph, abort_flag);
                         if (!ok) break;
 #pragma unroll
                         for (int t = 0; t < 2; ++t) {
@@ -357,7 +370,32 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
         }
         __syncwarp();
-      }   // warps 10-11 idle: they complete the third warpgroup
+      } else if (CONV) {
+        // ------------------------------------------------------------ warps 10-11: V_j bf16 -> fp16
+        // the same walk as the producer's; a tile is touched between its arrival (V_full) and its
+        // first reader (the PV MMAs wait for V_conv instead of V_full)
+        const int ct = (warp - 10) * 32 + lane;
+        int kvc = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < a.n_items && ok; w += gridDim.x) {
+            for (int u = 0; u < 2 && ok; ++u) {
+                Pair pr;
+                if (!decode_work(a, w, u, pr)) continue;
+                const int nk = kv_len_of(a.kv_len, pr.b, a.Nk);
+                const int n0 = num_blocks(a, pr.pair, 0, nk), n1 = num_blocks(a, pr.pair, 1, nk);
+                const int nmax = n0 > n1 ? n0 : n1;
+                for (int j = 0; j < nmax; ++j, ++kvc) {
+                    const int sidx = kvc % ST;
+                    ok = mbar_wait(&bars[Cfg::kVFull + sidx], (uint32_t)(kvc / ST) & 1u, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    convert_tile_bf16_to_f16<false>(sV + sidx * TILE, TILE, ct, 64, 1.f);
+                    fence_proxy_async_smem();           // generic-proxy writes -> visible to the MMA's reads
+                    mbar_arrive_warp(&bars[Cfg::kVConv + sidx]);
+                }
+            }
+        }
+      }   // fp16 inputs: warps 10-11 idle, they complete the third warpgroup
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         // ------------------------------------------------------------ softmax + epilogue
@@ -437,7 +475,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     // dropout P is packed to 16 bits as it is produced and each 64-key half is
                     // stored to TMEM as soon as it is complete, so conversion and store latency
                     // overlap the exponentials of the other half.
-                    const uint64_t c2 = f2_pack(a.scale_log2, a.scale_log2), nm2 = f2_pack(-m, -m);
+                    const uint64_t c2 = f2_pack(a.scale_log2, a.scale_log2), nm2 = f2_pack(kPShift - m, kPShift - m);
                     uint64_t la = 0ull, lb = 0ull;             // {0.f, 0.f}
 #pragma unroll
                     for (int c0 = 0; c0 < 2; ++c0) {
@@ -507,6 +545,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const float inv = a.inv_keep / l;
                 T16* orow = reinterpret_cast<T16*>(a.o) + (int64_t)pr.b * a.o_sb + (int64_t)i * a.o_sn +
                             (int64_t)pr.h * a.o_sh;
+                T16* lrow = a.o_lo ? reinterpret_cast<T16*>(a.o_lo) + (int64_t)pr.b * a.l_sb + (int64_t)i * a.l_sn +
+                                         (int64_t)pr.h * a.l_sh : nullptr;
 #pragma unroll
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t orr[32];
@@ -521,10 +561,23 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             v4.z = pack2<BF16>(__uint_as_float(orr[g * 8 + 4]) * inv, __uint_as_float(orr[g * 8 + 5]) * inv);
                             v4.w = pack2<BF16>(__uint_as_float(orr[g * 8 + 6]) * inv, __uint_as_float(orr[g * 8 + 7]) * inv);
                             *reinterpret_cast<uint4*>(orow + c0 + g * 8) = v4;
+                            if (lrow) {
+                                // residual: the exact value minus what was just stored, rounded once more
+                                const uint32_t hi[4] = {v4.x, v4.y, v4.z, v4.w};
+                                uint32_t lo[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    float h0, h1;
+                                    unpack2<BF16>(hi[e], h0, h1);
+                                    lo[e] = pack2<BF16>(__uint_as_float(orr[g * 8 + 2 * e]) * inv - h0,
+                                                        __uint_as_float(orr[g * 8 + 2 * e + 1]) * inv - h1);
+                                }
+                                *reinterpret_cast<uint4*>(lrow + c0 + g * 8) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                            }
                         }
                     }
                 }
-                if (i < a.Nq) a.lse[((int64_t)pr.b * a.H + pr.h) * a.Nq + i] = kLn2 * (m + log2f(l));
+                if (i < a.Nq) a.lse[((int64_t)pr.b * a.H + pr.h) * a.Nq + i] = kLn2 * ((m - kPShift) + log2f(l));
                 // the O_t reads above are complete (wait::ld); the next pair's first PV_t MMA waits for
                 // this warpgroup's next P_t, so it cannot overwrite O_t earlier
             }
@@ -534,7 +587,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 8) tmem_dealloc(tmem, 512);
-    if (threadIdx.x == 0 && *abort_flag && a.status) atomicExch(a.status, 1);
+    if (threadIdx.x == 0 && *abort_flag) report_status(a.status, 1);
 }
 
 template <int D, bool BF16>
@@ -543,17 +596,20 @@ int launch(const fa_b200_params& p) {
     const CUtensorMapDataType dt = BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap mq, mk, mv;
     int r;
-    if ((r = make_tmap_bnhd(&mq, p.q.ptr, dt, 2, p.B, p.Nq, p.H, D, p.q.stride_b, p.q.stride_n, p.q.stride_h, 128, 64, true)) ||
-        (r = make_tmap_bnhd(&mk, p.k.ptr, dt, 2, p.B, p.Nk, p.Hkv, D, p.k.stride_b, p.k.stride_n, p.k.stride_h, 128, 64, true)) ||
-        (r = make_tmap_bnhd(&mv, p.v.ptr, dt, 2, p.B, p.Nk, p.Hkv, D, p.v.stride_b, p.v.stride_n, p.v.stride_h, 128, 64, true))) {
+    if ((r = cached_tmap_bnhd(&mq, p.q.ptr, dt, 2, p.B, p.Nq, p.H, D, p.q.stride_b, p.q.stride_n, p.q.stride_h, 128, 64, true)) ||
+        (r = cached_tmap_bnhd(&mk, p.k.ptr, dt, 2, p.B, p.Nk, p.Hkv, D, p.k.stride_b, p.k.stride_n, p.k.stride_h, 128, 64, true)) ||
+        (r = cached_tmap_bnhd(&mv, p.v.ptr, dt, 2, p.B, p.Nk, p.Hkv, D, p.v.stride_b, p.v.stride_n, p.v.stride_h, 128, 64, true))) {
         set_error("cuTensorMapEncodeTiled failed (%d)", r);
         return FA_ECUDA;
     }
     FwdArgs a;
     a.o = p.o.ptr;
     a.o_sb = p.o.stride_b; a.o_sn = p.o.stride_n; a.o_sh = p.o.stride_h;
+    a.o_lo = p.o_lo.ptr;
+    a.l_sb = p.o_lo.stride_b; a.l_sn = p.o_lo.stride_n; a.l_sh = p.o_lo.stride_h;
     a.lse = p.lse;
     a.status = p.status_word;
+    a.wait_limit_ms = p.wait_limit_ms;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv;
     a.kv_len = p.kv_lengths;
     a.causal = p.causal;
@@ -569,7 +625,11 @@ int launch(const fa_b200_params& p) {
     a.key = philox_make_key(p.seed, p.offset);
     a.rng = dropout_origin_of(p);
     auto kernel = a.drop_thr ? fwd_sm100_kernel<D, BF16, true> : fwd_sm100_kernel<D, BF16, false>;
-    FA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    {
+        static std::mutex mu;
+        static uint64_t done[2] = {0, 0};
+        FA_CUDA_CHECK(set_smem_limit_once(kernel, Cfg::kSmemBytes, p.device, &done[a.drop_thr ? 1 : 0], &mu));
+    }
     const int sms = sm_count(p.device);
     if (sms <= 0) { set_error("cannot read the SM count of device %d", p.device); return FA_ECUDA; }
     const int grid = a.n_items < sms ? a.n_items : sms;     // one persistent CTA per SM
@@ -597,6 +657,7 @@ bool sm100_supports(const fa_b200_params& p, bool backward, const char** why) {
     if (p.B > 65535 || p.H > 65535) { *why = "batch and heads must be below 65536"; return false; }
     if (!tensor_ok(p.q, p.B, p.Nq, p.H) || !tensor_ok(p.k, p.B, p.Nk, p.Hkv) ||
         !tensor_ok(p.v, p.B, p.Nk, p.Hkv) || !tensor_ok(p.o, p.B, p.Nq, p.H) ||
+        (p.o_lo.ptr && !tensor_ok(p.o_lo, p.B, p.Nq, p.H)) ||
         (backward && (!tensor_ok(p.d_o, p.B, p.Nq, p.H) || !tensor_ok(p.dq, p.B, p.Nq, p.H) ||
                       !tensor_ok(p.dk, p.B, p.Nk, p.Hkv) || !tensor_ok(p.dv, p.B, p.Nk, p.Hkv)))) {
         *why = "tensors must be 16-byte aligned with strides that are multiples of 8 elements";

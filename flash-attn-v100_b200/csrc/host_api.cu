@@ -4,6 +4,8 @@
 // scans and no device synchronisation (the reference's launchers do both:
 // utils.py:227-254, kernels/forward_kernel.py:308-313).
 #include "fa_common.cuh"
+#include "sm100_ptx.cuh"
+#include "tile_config.cuh"
 #include <stdarg.h>
 #include <string.h>
 #include <mutex>
@@ -19,19 +21,26 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
-BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant) {
+BwdWorkspace bwd_workspace_layout(const fa_b200_params& p, int variant, bool inline_conversion) {
     BwdWorkspace w;
+    memset(&w, 0, sizeof(w));
     const size_t nq_pad = align_up((size_t)p.Nq, 128);
-    w.delta_off = 0;
-    w.delta_bytes = (size_t)p.B * p.H * nq_pad * sizeof(float);
-    w.lse2_off = align_up(w.delta_bytes, 256);
     const bool tc = (variant == FA_B200_VARIANT_TCGEN05 || variant == FA_B200_VARIANT_TCGEN05_2PASS);
-    w.lse2_bytes = tc ? w.delta_bytes : 0;
-    w.dq_off = align_up(w.lse2_off + w.lse2_bytes, 256);
-    w.dq_bytes = (variant == FA_B200_VARIANT_TCGEN05 && sm100_bwd_fused_supported(p))
-                     ? (size_t)p.B * p.H * nq_pad * (size_t)p.D * sizeof(float) : 0;
-    w.total = w.dq_bytes ? w.dq_off + w.dq_bytes : w.lse2_off + w.lse2_bytes;
-    if (w.total == 0) w.total = 256;
+    const bool copies = tc && p.dtype == FA_B200_BF16 && !inline_conversion;
+    const bool one_kernel = (variant == FA_B200_VARIANT_TCGEN05 && sm100_bwd_fused_supported(p));
+    size_t at = 0;
+    auto region = [&](size_t* off, size_t* bytes, size_t n) { *off = at; *bytes = n; at = align_up(at + n, 256); };
+    const size_t rows = (size_t)p.B * p.H * nq_pad * sizeof(float);
+    region(&w.delta_off, &w.delta_bytes, rows);
+    region(&w.lse2_off, &w.lse2_bytes, tc ? rows : 0);
+    region(&w.rng_off, &w.rng_bytes, tc ? (size_t)p.B * p.Hkv * 2 * sizeof(float) : 0);
+    region(&w.erow_off, &w.erow_bytes, copies ? rows : 0);
+    region(&w.q16_off, &w.q16_bytes, copies ? (size_t)p.B * p.Nq * p.H * p.D * 2 : 0);
+    region(&w.do16_off, &w.do16_bytes, copies ? (size_t)p.B * p.Nq * p.H * p.D * 2 : 0);
+    // the K copy feeds the dQ kernel only: the one-kernel backward has none
+    region(&w.k16_off, &w.k16_bytes, (copies && !one_kernel) ? (size_t)p.B * p.Nk * p.Hkv * p.D * 2 : 0);
+    region(&w.dq_off, &w.dq_bytes, one_kernel ? (size_t)p.B * p.H * nq_pad * (size_t)p.D * sizeof(float) : 0);
+    w.total = at ? at : 256;
     return w;
 }
 
@@ -111,6 +120,7 @@ int validate_common(const fa_b200_params* p, bool backward) {
                   p->rng_batch_offset, p->rng_head_offset, p->rng_heads, p->H);
         return FA_EINVAL;
     }
+    if (p->wait_limit_ms < 0) { set_error("wait_limit_ms must not be negative"); return FA_EINVAL; }
     if (p->bwd_phases < 0 || p->bwd_phases > 7) { set_error("bwd_phases must be a mask in [0, 7]"); return FA_EINVAL; }
     if (p->B == 0 || p->Nq == 0) return FA_OK;   // empty problem: nothing else to check
     int rc;
@@ -130,6 +140,51 @@ int validate_common(const fa_b200_params* p, bool backward) {
         }
     }
     return FA_OK;
+}
+
+// A status word in pinned host memory is read here, on entry to the next call, without any
+// synchronisation: the kernels write it with a system-wide store when a bounded wait gives up.
+// Returns the code an earlier call left (and clears it), 0 when there is none or when the word
+// lives in device memory (which only the caller can read, after synchronising).
+int take_host_status(int32_t* word) {
+    if (!word) return 0;
+    static thread_local int32_t* last_word = nullptr;
+    static thread_local volatile int32_t* last_host = nullptr;
+    if (word != last_word) {
+        cudaPointerAttributes attr;
+        volatile int32_t* host = nullptr;
+        if (cudaPointerGetAttributes(&attr, word) == cudaSuccess && attr.type == cudaMemoryTypeHost)
+            host = (volatile int32_t*)attr.hostPointer;
+        else
+            (void)cudaGetLastError();          // not a CUDA allocation: leave no sticky error behind
+        last_word = word;
+        last_host = host;
+    }
+    if (!last_host) return 0;
+    const int code = *last_host;
+    if (code != 0) *last_host = 0;
+    return code;
+}
+
+int refuse_after_timeout(const fa_b200_params* p, const char* what) {
+    const int code = take_host_status(p->status_word);
+    if (code == 0) return FA_OK;
+    set_error("%s: an earlier call's device-side wait ran out (status %d: 1 forward, 2 dK/dV, 3 dQ, 4 one-kernel "
+              "backward, 8 shared memory, 9 self-test); its results are invalid.  The word has been cleared", what, code);
+    return FA_ETIMEOUT;
+}
+
+// Self-test of the bounded wait: one thread waits on an mbarrier that nobody ever arrives at.
+__global__ void wait_timeout_selftest_kernel(int32_t* status, int limit_ms) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t ctl[2];
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1u);
+        ptx::wait_control_init(ctl, limit_ms);
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !ptx::mbar_wait(&bar, 0u, ctl)) ptx::report_status(status, 9);
 }
 
 // Kernel family for a call: an explicit request is honoured or refused, AUTO
@@ -184,14 +239,25 @@ const char* fa_b200_strerror(int status) {
         case FA_EALIGN:       return "pointer or stride not aligned as the kernel requires";
         case FA_EWORKSPACE:   return "workspace missing or too small";
         case FA_ECUDA:        return "CUDA call failed";
-        case FA_ETIMEOUT:     return "bounded device-side wait ran out";
+        case FA_ETIMEOUT:     return "a bounded device-side wait of an earlier call ran out";
         default:              return "unknown status";
     }
+}
+
+int fa_b200_selftest_wait_timeout(int32_t* status_word, int limit_ms, int device, void* stream) {
+    if (!status_word) { set_error("status_word is null"); return FA_EINVAL; }
+    if (limit_ms < 1 || limit_ms > 1000) { set_error("limit_ms must be in [1, 1000]"); return FA_EINVAL; }
+    GuardDevice g(device);
+    if (!g.ok) { set_error("cudaSetDevice(%d) failed", device); return FA_ECUDA; }
+    wait_timeout_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status_word, limit_ms);
+    FA_CUDA_CHECK(cudaGetLastError());
+    return FA_OK;
 }
 
 int fa_b200_fwd(const fa_b200_params* p) {
     int rc = validate_common(p, false);
     if (rc) return rc;
+    if ((rc = refuse_after_timeout(p, "fa_b200_fwd"))) return rc;
     if (p->B == 0 || p->Nq == 0) return FA_OK;
     if (p->Nk == 0) { set_error("Nk = 0: softmax over an empty key set is undefined"); return FA_EINVAL; }
     int variant;
@@ -236,6 +302,7 @@ size_t fa_b200_bwd_workspace_bytes(const fa_b200_params* p) {
 int fa_b200_bwd(const fa_b200_params* p) {
     int rc = validate_common(p, true);
     if (rc) return rc;
+    if ((rc = refuse_after_timeout(p, "fa_b200_bwd"))) return rc;
     if (p->B == 0 || (p->Nq == 0 && p->Nk == 0)) return FA_OK;
     if (p->Nk == 0) { set_error("Nk = 0: softmax over an empty key set is undefined"); return FA_EINVAL; }
     int variant;
@@ -267,7 +334,8 @@ int fa_b200_bwd(const fa_b200_params* p) {
 // in the library's own device image.  Every GPU that loads the library holds
 // these bytes until the process exits.
 constexpr uint64_t kStaticScratchRows = 1u << 20;         // B * H * ceil128(Nq) a call may have
-constexpr size_t kStaticScratchBytes = 8u << 20;          // 8 MiB: two fp32 vectors of that many rows
+// two fp32 vectors of that many rows (8 MiB) + the per-column ranges (at most rows / 128 columns) + alignment
+constexpr size_t kStaticScratchBytes = (8u << 20) + (kStaticScratchRows / 128) * 8 + 512;
 static __device__ __align__(256) unsigned char g_bwd_static_scratch[kStaticScratchBytes];
 
 namespace {
@@ -306,13 +374,14 @@ int fa_b200_bwd_static(const fa_b200_params* p) {
     }
     int rc = validate_common(p, true);
     if (rc) return rc;
+    if ((rc = refuse_after_timeout(p, "fa_b200_bwd_static"))) return rc;
     if (p->B == 0 || (p->Nq == 0 && p->Nk == 0)) return FA_OK;
     if (p->Nk == 0) { set_error("Nk = 0: softmax over an empty key set is undefined"); return FA_EINVAL; }
     int variant;
     if ((rc = choose_variant(*p, true, &variant))) return rc;
     // the built-in array is sized for the per-row vectors only: tensor-core calls take the two-pass backward
     if (variant == FA_B200_VARIANT_TCGEN05) variant = FA_B200_VARIANT_TCGEN05_2PASS;
-    BwdWorkspace ws = bwd_workspace_layout(*p, variant);
+    BwdWorkspace ws = bwd_workspace_layout(*p, variant, /*inline_conversion=*/true);
     if (ws.total > kStaticScratchBytes) {
         set_error("fa_b200_bwd_static: this problem needs %zu bytes of scratch, the built-in array holds %zu; "
                   "use fa_b200_bwd with a workspace", ws.total, kStaticScratchBytes);
@@ -331,20 +400,26 @@ int fa_b200_bwd_static(const fa_b200_params* p) {
     return variant != FA_B200_VARIANT_SIMT ? sm100_bwd(q, ws) : simt_bwd(q, ws);
 }
 
-// Static tile table.  Tensor-core rows hold the tile shapes the sm_100a
-// kernels are compiled for; everything else is served by 64x64 CUDA-core tiles.
+// Static tile table.  Tensor-core rows report the constants the sm_100a kernels are compiled from
+// (tile_config.cuh); everything else is served by 64x64 CUDA-core tiles.  The same tiles serve both
+// masks: `causal` is part of the reference's lookup key (config.py:288-348) and changes no row here.
 int fa_b200_tile_config(int D, int dtype, int causal, int backward, fa_b200_tile* out) {
     if (!out) { set_error("out is null"); return FA_EINVAL; }
     if (D <= 0 || D > 128) { set_error("no tile for D=%d", D); return FA_EUNSUPPORTED; }
     (void)causal;
+    memset(out, 0, sizeof(*out));
     bool tc = (dtype == FA_B200_F16 || dtype == FA_B200_BF16) && (D == 64 || D == 128);
     if (tc) {
         out->variant = FA_B200_VARIANT_TCGEN05;
-        out->block_m = 128;
-        out->block_n = 128;
-        out->q_tiles_per_cta = backward ? 1 : 2;
-        out->kv_stages = backward ? 1 : (D == 64 ? 3 : 2);
-        out->num_warps = backward ? 20 : 12;
+        out->block_m = tile::kBlockM;
+        out->block_n = tile::kBlockN;
+        out->q_tiles_per_cta = backward ? 1 : tile::kFwdQTilesPerCta;
+        out->kv_stages = backward ? tile::bwd_u_stages(D, false) : tile::fwd_kv_stages(D);
+        out->w_stages = backward ? tile::bwd_w_stages(D) : 0;
+        out->num_warps = backward ? tile::kBwdWarps : tile::kFwdWarps;
+        out->regs_softmax = backward ? 0 : tile::kFwdRegsSoftmax;
+        out->regs_other = backward ? 0 : tile::kFwdRegsOther;
+        out->one_kernel_backward = backward && tile::bwd_one_kernel(D) ? 1 : 0;
     } else {
         out->variant = FA_B200_VARIANT_SIMT;
         out->block_m = 64;

@@ -30,6 +30,7 @@ constexpr int MAXC = 8;      // output columns per thread: D <= 16*MAXC = 128
 
 struct SimtArgs {
     fa_b200_tensor q, k, v, o, d_o, dq, dk, dv;
+    fa_b200_tensor o_lo;   // optional residual of o (forward: written; backward: added to o for delta)
     fa_b200_tensor bias;   // fp32 (B, H, Nq, Nk) with broadcast strides; ptr = nullptr: none
     float* d_scores;       // optional dense (B, H, Nq, Nk) gradient of the scores
     const int32_t* kv_len; // optional per-batch key counts
@@ -193,7 +194,14 @@ __global__ void __launch_bounds__(NT) simt_fwd_kernel(SimtArgs a) {
 #pragma unroll
             for (int c = 0; c < MAXC; ++c) {
                 int col = tx + 16 * c;
-                if (col < D) ob[(int64_t)i * a.o.stride_n + col] = from_f32<T>(oacc[r][c] * inv);
+                if (col < D) {
+                    const float x = oacc[r][c] * inv;
+                    const T hi = from_f32<T>(x);
+                    ob[(int64_t)i * a.o.stride_n + col] = hi;
+                    if (a.o_lo.ptr)
+                        ((T*)a.o_lo.ptr)[(int64_t)b * a.o_lo.stride_b + (int64_t)i * a.o_lo.stride_n +
+                                         (int64_t)h * a.o_lo.stride_h + col] = from_f32<T>(x - to_f32<T>(hi));
+                }
             }
         }
     }
@@ -214,7 +222,12 @@ __global__ void __launch_bounds__(256) simt_delta_kernel(SimtArgs a) {
     const T* o = (const T*)a.o.ptr + (int64_t)b * a.o.stride_b + (int64_t)i * a.o.stride_n + (int64_t)h * a.o.stride_h;
     const T* g = (const T*)a.d_o.ptr + (int64_t)b * a.d_o.stride_b + (int64_t)i * a.d_o.stride_n + (int64_t)h * a.d_o.stride_h;
     float s = 0.f;
-    for (int d = lane; d < a.D; d += 32) s = fmaf(to_f32<T>(o[d]), to_f32<T>(g[d]), s);
+    if (a.o_lo.ptr) {
+        const T* l = (const T*)a.o_lo.ptr + (int64_t)b * a.o_lo.stride_b + (int64_t)i * a.o_lo.stride_n + (int64_t)h * a.o_lo.stride_h;
+        for (int d = lane; d < a.D; d += 32) s = fmaf(to_f32<T>(o[d]) + to_f32<T>(l[d]), to_f32<T>(g[d]), s);
+    } else {
+        for (int d = lane; d < a.D; d += 32) s = fmaf(to_f32<T>(o[d]), to_f32<T>(g[d]), s);
+    }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
     if (lane == 0) a.delta[row] = s;
@@ -449,6 +462,7 @@ __global__ void dropout_mask_kernel(PhiloxKey key, uint32_t thr, int H, int Nq, 
 SimtArgs make_args(const fa_b200_params& p, float* delta) {
     SimtArgs a;
     a.q = p.q; a.k = p.k; a.v = p.v; a.o = p.o; a.d_o = p.d_o; a.dq = p.dq; a.dk = p.dk; a.dv = p.dv;
+    a.o_lo = p.o_lo;
     a.lse = p.lse; a.delta = delta;
     a.bias = p.bias; a.d_scores = p.d_scores; a.kv_len = p.kv_lengths;
     a.B = p.B; a.Nq = p.Nq; a.Nk = p.Nk; a.H = p.H; a.Hkv = p.Hkv; a.D = p.D;

@@ -65,11 +65,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Wall-clock limit of one wait.  The longest legitimate wait inside a CTA is
-// one pipeline step (microseconds); two seconds means a protocol error.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// one pipeline step (microseconds); the default of two seconds means a protocol
+// error.  The caller may pass a shorter one (fa_b200_params.wait_limit_ms).
+constexpr uint32_t kDefaultWaitLimitUs = 2000000u;
 
-// Wait for the phase with the given parity.  `abort_flag` is a shared-memory
-// word any thread of the CTA may raise; a raised flag ends every wait.
+// The CTA's wait control block in shared memory: word 0 is the abort flag any
+// thread may raise (a raised flag ends every wait), word 1 the limit of one wait
+// in microseconds.
+__device__ __forceinline__ void wait_control_init(volatile uint32_t* abort_flag, int limit_ms) {
+    abort_flag[0] = 0u;
+    abort_flag[1] = limit_ms > 0 ? (uint32_t)limit_ms * 1000u : kDefaultWaitLimitUs;
+}
+
+// Set the caller's status word (device memory, or pinned host memory the host reads without
+// synchronising): a plain store made visible system-wide; nothing is read back.
+__device__ __forceinline__ void report_status(int32_t* status, int32_t code) {
+    if (status) {
+        *reinterpret_cast<volatile int32_t*>(status) = code;
+        __threadfence_system();
+    }
+}
+
+// Wait for the phase with the given parity; false when the wait ran out or the flag was raised.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
@@ -77,9 +94,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0) {
-            if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
-                *abort_flag = 1u;
+            if (abort_flag[0]) return false;
+            if (globaltimer_ns() - t0 > (uint64_t)abort_flag[1] * 1000ull) {
+                abort_flag[0] = 1u;
                 return false;
             }
         }
@@ -365,6 +382,61 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     if (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     else      asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
+}
+
+// ---- bf16 -> fp16 in shared memory ---------------------------------------------------------------
+// tcgen05.mma kind::f16 wants both operands in one 16-bit format.  A product whose A operand is a
+// probability (or dS) tile rounded to bf16 carries that rounding, 2^-9 relative, into the result
+// at full size, because with zero-mean V / K / Q / dO the terms add like a random walk; rounded
+// to fp16 (2^-12) it does not.  So for bf16 inputs the B operand tile is converted in place, as it
+// sits in shared memory after the TMA load, and the MMA runs f16 x f16.  The conversion is exact
+// for 2^-17 <= |x| < 65520 (bf16 has 8 significant bits, fp16 11; below 2^-14 fp16 is subnormal
+// with a spacing of 2^-24), it saturates beyond and loses bits below; `mul` (a power of two) moves
+// a tensor whose values lie elsewhere into that range first.
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t x) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;"
+        : "=r"(r) : "f"(__uint_as_float(x & 0xFFFF0000u)), "f"(__uint_as_float(x << 16)));
+    return r;
+}
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t x, uint64_t mul2) {
+    float lo, hi;
+    f2_unpack(f2_mul(f2_pack(__uint_as_float(x << 16), __uint_as_float(x & 0xFFFF0000u)), mul2), lo, hi);
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// Convert `bytes` (a multiple of 16 * nthreads * 4) of bf16 at `tile` to fp16 in place; thread `t` of
+// `nthreads` takes 16-byte pieces t, t + nthreads, ...  Element-wise, so the tile's swizzle is irrelevant.
+template <bool SCALED>
+__device__ __forceinline__ void convert_tile_bf16_to_f16(uint8_t* tile, int bytes, int t, int nthreads, float mul) {
+    uint4* p = reinterpret_cast<uint4*>(tile) + t;
+    const uint64_t m2 = f2_pack(mul, mul);
+    const int n = bytes / (16 * nthreads);
+#pragma unroll 4
+    for (int i = 0; i < n; ++i) {
+        uint4 v = p[i * nthreads];
+        if (SCALED) {
+            v.x = bf16x2_to_f16x2(v.x, m2); v.y = bf16x2_to_f16x2(v.y, m2);
+            v.z = bf16x2_to_f16x2(v.z, m2); v.w = bf16x2_to_f16x2(v.w, m2);
+        } else {
+            v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y);
+            v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w);
+        }
+        p[i * nthreads] = v;
+    }
+}
+
+// packed 16-bit pair -> two floats (`lo` from bits 0-15)
+template <bool BF16>
+__device__ __forceinline__ void unpack2(uint32_t v, float& lo, float& hi) {
+    if (BF16) {
+        lo = __uint_as_float(v << 16);
+        hi = __uint_as_float(v & 0xFFFF0000u);
+    } else {
+        asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}"
+            : "=f"(lo), "=f"(hi) : "r"(v));
+    }
 }
 
 // Programmatic dependent launch.  launch_dependents: the next kernel in the stream, if it was launched

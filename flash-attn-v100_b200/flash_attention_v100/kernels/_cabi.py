@@ -26,7 +26,7 @@ EXPORTS = (
     "fa_b200_fwd", "fa_b200_bwd", "fa_b200_bwd_static", "fa_b200_bwd_workspace_bytes", "fa_b200_tile_config",
     "fa_b200_dropout_mask_host", "fa_b200_dropout_mask_device", "fa_b200_dropout_effective_p",
     "fa_b200_philox4x32_10", "fa_b200_strerror", "fa_b200_last_error", "fa_b200_version", "fa_b200_combine",
-    "fa_b200_copy_rows",
+    "fa_b200_copy_rows", "fa_b200_selftest_wait_timeout",
 )
 
 
@@ -53,7 +53,8 @@ class Params(ctypes.Structure):
         ("bwd_phases", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
         ("bias", Tensor4), ("d_scores", ctypes.c_void_p), ("kv_lengths", ctypes.c_void_p),
         ("rng_batch_offset", ctypes.c_int32), ("rng_head_offset", ctypes.c_int32), ("rng_heads", ctypes.c_int32),
-        ("reserved0", ctypes.c_int32),
+        ("wait_limit_ms", ctypes.c_int32),
+        ("o_lo", Tensor4),
     ]
 
 
@@ -72,7 +73,8 @@ class CombineParams(ctypes.Structure):
 class Tile(ctypes.Structure):
     _fields_ = [("variant", ctypes.c_int32), ("block_m", ctypes.c_int32), ("block_n", ctypes.c_int32),
                 ("q_tiles_per_cta", ctypes.c_int32), ("kv_stages", ctypes.c_int32),
-                ("num_warps", ctypes.c_int32)]
+                ("num_warps", ctypes.c_int32), ("w_stages", ctypes.c_int32), ("regs_softmax", ctypes.c_int32),
+                ("regs_other", ctypes.c_int32), ("one_kernel_backward", ctypes.c_int32)]
 
 
 _lib = None
@@ -114,6 +116,8 @@ def load():
         lib.fa_b200_copy_rows.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t,
                                           ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         lib.fa_b200_copy_rows.restype = ctypes.c_int
+        lib.fa_b200_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        lib.fa_b200_selftest_wait_timeout.restype = ctypes.c_int
         lib.fa_b200_tile_config.argtypes = [ctypes.c_int] * 4 + [ctypes.POINTER(Tile)]
         lib.fa_b200_tile_config.restype = ctypes.c_int
         lib.fa_b200_dropout_mask_host.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float] + \

@@ -2,8 +2,10 @@
 
 Replaces the reference's run-time tuner (kernels/autotuning.py:118-1018,
 never reached from its call path) and the seq-len buckets of
-config.get_enhanced_config (config.py:288-348).  The table itself lives in the
-shared library (fa_b200_tile_config) so that the host launcher and Python agree.
+config.get_enhanced_config (config.py:288-348).  The table lives in the shared
+library: fa_b200_tile_config reports the constants of csrc/tile_config.cuh, the
+header the kernels themselves are compiled from, so what this module returns is
+what runs.
 """
 from __future__ import annotations
 
@@ -37,4 +39,6 @@ def lookup(head_dim: int, dtype: torch.dtype = torch.bfloat16, causal: bool = Fa
         "BLOCK_M": t.block_m, "BLOCK_N": t.block_n, "BLOCK_K": int(head_dim),
         "NUM_STAGES": t.kv_stages, "NUM_WARPS": t.num_warps,
         "Q_TILES_PER_CTA": t.q_tiles_per_cta, "VARIANT": _cabi.VARIANT_NAMES[t.variant],
+        "W_STAGES": t.w_stages, "REGS_SOFTMAX": t.regs_softmax, "REGS_OTHER": t.regs_other,
+        "ONE_KERNEL_BACKWARD": bool(t.one_kernel_backward),
     }

@@ -60,24 +60,30 @@ def kernel_variant(name: str):
         _variant_override.value = old
 
 
-# One int32 per device that kernels set non-zero when a bounded device-side
-# wait gives up (a protocol error, never expected).  Reading it synchronises,
-# so it is only read on request.
+# One int32 per device, in pinned host memory, that kernels set non-zero when a bounded device-side
+# wait gives up (a protocol error, never expected).  The device writes it with a system-wide store;
+# the host reads it without synchronising: the library on entry to every call (an earlier call's
+# failure makes the next one return FA_ETIMEOUT), and check_status() below on request.  The
+# reference's counterpart is the try/except around its launches (interface.py:331-348).
 _status_words: Dict[int, torch.Tensor] = {}
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx not in _status_words:
-        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32).pin_memory()
     return _status_words[idx]
 
 
-def check_status(device: Optional[torch.device] = None) -> None:
-    """Synchronise and raise if any kernel on `device` reported a timed-out wait."""
+def check_status(device: Optional[torch.device] = None, synchronize: bool = True) -> None:
+    """Raise if a kernel on `device` reported a timed-out wait.  `synchronize=True` waits for the
+    device's queued work first, so that the answer covers it; False only looks at what has been
+    reported so far (no synchronisation at all)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if synchronize:
+        torch.cuda.synchronize(device)
     word = _status_word(device)
-    code = int(word.item())
+    code = int(word[0])
     if code != 0:
         word.zero_()
         raise RuntimeError(f"flash_attention_v100: a device-side wait timed out (status {code}); "
@@ -150,11 +156,25 @@ def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal
     return p
 
 
+def _check_residual(o_residual: torch.Tensor, o: torch.Tensor) -> None:
+    if o_residual.shape != o.shape or o_residual.dtype != o.dtype or o_residual.device != o.device or \
+            (o_residual.numel() and o_residual.stride(3) != 1):
+        raise ValueError("o_residual must match the output in shape, dtype and device, with a contiguous last dim")
+
+
+def saves_output_residual(dtype: torch.dtype) -> bool:
+    """Whether the autograd op keeps the output's rounding residual for its backward.  bf16 only: its 8
+    significant bits make the saved output the largest error in dQ and dK of peaked attention rows."""
+    return dtype == torch.bfloat16
+
+
 def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None, bias=None,
-                   key_lengths=None, causal_shift=0, dropout_origin=None):
+                   key_lengths=None, causal_shift=0, dropout_origin=None, o_residual=None):
     """o, lse <- fa_b200_fwd.  Counterpart of flash_attention_forward_triton_enhanced
     (kernels/forward_kernel.py:246-387); returns (o, lse).  `out=(o, lse)` writes into
-    caller-owned buffers (o like q, lse (B, H, Nq) fp32 contiguous) instead of allocating."""
+    caller-owned buffers (o like q, lse (B, H, Nq) fp32 contiguous) instead of allocating.
+    `o_residual` (a tensor like o) receives what rounding the output to its dtype dropped; handed
+    to launch_backward it removes that rounding from the gradients."""
     if out is not None:
         o, lse = out
     else:
@@ -163,6 +183,9 @@ def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=
     p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift, dropout_origin)
     p.bias, _keep = _bias_operand(bias)        # scores = scale * q.k + bias (CUDA-core kernels)
     p.kv_lengths, _keep_len = _lengths_operand(key_lengths, q)
+    if o_residual is not None:
+        _check_residual(o_residual, o)
+        p.o_lo = _tensor4(o_residual)
     rc = _cabi.load().fa_b200_fwd(ctypes.byref(p))
     _cabi.raise_for_status(rc, "fa_b200_fwd")
     return o, lse
@@ -170,7 +193,7 @@ def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=
 
 def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None,
                     workspace=None, bias=None, d_scores=None, key_lengths=None, causal_shift=0,
-                    dropout_origin=None):
+                    dropout_origin=None, o_residual=None):
     """dq, dk, dv <- fa_b200_bwd.  Counterpart of
     flash_attention_backward_triton_enhanced (kernels/backward_kernel.py:208-318).
     `out=(dq, dk, dv)` and `workspace` (uint8, at least fa_b200_bwd_workspace_bytes)
@@ -186,6 +209,9 @@ def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, 
     p.d_o, p.dq, p.dk, p.dv = _tensor4(d_o), _tensor4(dq), _tensor4(dk), _tensor4(dv)
     p.bias, _keep = _bias_operand(bias)
     p.kv_lengths, _keep_len = _lengths_operand(key_lengths, q)
+    if o_residual is not None:
+        _check_residual(o_residual, o)
+        p.o_lo = _tensor4(o_residual)
     if d_scores is not None:
         # dense (B, H, Nq, Nk) fp32, zero-filled by the caller: receives d loss / d scores
         if d_scores.dtype != torch.float32 or not d_scores.is_contiguous() or \
@@ -276,10 +302,15 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
         # attends to its first key_lengths[b] keys only
         # causal_shift: key j is visible to query i iff j <= i + causal_shift (0: the reference's top-left
         # alignment; Nk - Nq: bottom-right)
+        # the backward of a bf16 call also gets what rounding the output to bf16 dropped
+        needs_grad = any(t.requires_grad for t in (q, k, v)) or (bias is not None and bias.requires_grad)
+        o_lo = torch.empty_like(q) if (needs_grad and saves_output_residual(q.dtype)) else None
         o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias, key_lengths=key_lengths,
-                                causal_shift=causal_shift, dropout_origin=dropout_origin)
+                                causal_shift=causal_shift, dropout_origin=dropout_origin, o_residual=o_lo)
         ctx.dropout_origin = dropout_origin
-        ctx.save_for_backward(q, k, v, o, lse, *([bias] if bias is not None else []))
+        ctx.has_bias, ctx.has_residual = bias is not None, o_lo is not None
+        ctx.save_for_backward(q, k, v, o, lse, *([bias] if bias is not None else []),
+                              *([o_lo] if o_lo is not None else []))
         ctx.key_lengths = key_lengths
         ctx.causal_shift = int(causal_shift)
         ctx.scale, ctx.causal, ctx.dropout_p = scale, bool(causal), float(dropout_p)
@@ -293,7 +324,8 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output: torch.Tensor, grad_softmax_lse: Optional[torch.Tensor] = None):
         q, k, v, o, lse, *rest = ctx.saved_tensors
-        bias = rest[0] if rest else None
+        bias = rest[0] if ctx.has_bias else None
+        o_lo = rest[-1] if ctx.has_residual else None
         d_scores = grad_bias = None
         if bias is not None and ctx.needs_input_grad[6]:
             # the reference returns zeros here (ops/attention.py:297-301); this is the real gradient:
@@ -303,7 +335,7 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
         dq, dk, dv = launch_backward(grad_output, q, k, v, o, lse, ctx.scale, ctx.causal,
                                      ctx.dropout_p, ctx.seed, ctx.offset, bias=bias, d_scores=d_scores,
                                      key_lengths=ctx.key_lengths, causal_shift=ctx.causal_shift,
-                                     dropout_origin=ctx.dropout_origin)
+                                     dropout_origin=ctx.dropout_origin, o_residual=o_lo)
         if d_scores is not None:
             dims = [i for i in range(4) if bias.shape[i] == 1 and d_scores.shape[i] != 1]
             grad_bias = (d_scores.sum(dim=dims, keepdim=True) if dims else d_scores).to(bias.dtype)
@@ -324,7 +356,8 @@ def flash_attention_forward_enhanced(q, k, v, scale: Optional[float] = None, cau
         seed, offset = kwargs.get("dropout_stream") or _next_dropout_stream()
     with torch.no_grad():
         o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias,
-                                key_lengths=kwargs.get("key_lengths"), dropout_origin=kwargs.get("dropout_origin"))
+                                key_lengths=kwargs.get("key_lengths"), dropout_origin=kwargs.get("dropout_origin"),
+                                o_residual=kwargs.get("output_residual"))
     return (o, lse) if kwargs.get("return_softmax_lse", False) else o
 
 
@@ -334,15 +367,17 @@ def flash_attention_backward_enhanced(grad_output, q, k, v, output, lse, max_val
                                       ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Explicit backward (reference ops/attention.py:536-600).  `max_vals` is
     accepted and ignored: the kernels recompute P from the log-sum-exp alone.
-    kwargs: dropout_p and dropout_stream=(seed, offset) to replay a mask; bias (the forward's additive
-    bias) and d_scores (zero-filled fp32 (B, H, Nq, Nk) that receives d loss / d scores)."""
+    kwargs: dropout_p and dropout_stream=(seed, offset) to replay a mask; output_residual (the tensor the
+    forward filled when it was given one: removes the output's rounding from dQ and dK); bias (the
+    forward's additive bias) and d_scores (zero-filled fp32 (B, H, Nq, Nk) that receives d loss / d scores)."""
     q, k, v, scale = validate_inputs(q, k, v, scale, kwargs.get("bias"), kwargs.get("dropout_p", 0.0))
     seed, offset = kwargs.get("dropout_stream", (0, 0))
     with torch.no_grad():
         return launch_backward(grad_output, q, k, v, _last_dim_contiguous(output), lse.contiguous(),
                                scale, causal, kwargs.get("dropout_p", 0.0), seed, offset,
                                bias=kwargs.get("bias"), d_scores=kwargs.get("d_scores"),
-                               key_lengths=kwargs.get("key_lengths"), dropout_origin=kwargs.get("dropout_origin"))
+                               key_lengths=kwargs.get("key_lengths"), dropout_origin=kwargs.get("dropout_origin"),
+                               o_residual=kwargs.get("output_residual"))
 
 
 def compare_with_pytorch_attention_enhanced(q, k, v, causal: bool = False,

@@ -113,6 +113,8 @@ class HostAttentionStep:
             for n in _IN + _OUT:
                 shape = self.k_shape if n in ("k", "v", "dk", "dv") else self.q_shape
                 self._dev[n] = torch.empty(shape, dtype=dtype, device=dev)
+            # what rounding the output to bf16 drops stays on the device for the backward (as in the autograd op)
+            self._o_lo = torch.empty(self.q_shape, dtype=dtype, device=dev) if _ops.saves_output_residual(dtype) else None
             # the log-sum-exp stays on the device: one dense (b, h, Nq) buffer per chunk
             self._lse = [torch.empty(b1 - b0, h1 - h0, Nq, dtype=torch.float32, device=dev)
                          for b0, b1, h0, h1 in self.chunks]
@@ -201,14 +203,16 @@ class HostAttentionStep:
                 sd, off = (int(seed), int(offset)) if self.dropout_p > 0 else (0, 0)
                 origin = (b, h0, self.q_shape[2])               # this chunk's place in the whole problem
                 lse_c = self._lse[c]
+                res = self._o_lo[qs] if self._o_lo is not None else None
                 _ops.launch_forward(d["q"][qs], d["k"][ks], d["v"][ks], self.scale, self.causal,
-                                    self.dropout_p, sd, off, out=(d["o"][qs], lse_c), dropout_origin=origin)
+                                    self.dropout_p, sd, off, out=(d["o"][qs], lse_c), dropout_origin=origin,
+                                    o_residual=res)
                 self._ev_fwd[c].record(self._s_run)
                 self._s_run.wait_event(self._ev_do[c])
                 _ops.launch_backward(d["d_o"][qs], d["q"][qs], d["k"][ks], d["v"][ks], d["o"][qs],
                                      lse_c, self.scale, self.causal, self.dropout_p, sd, off,
                                      out=(d["dq"][qs], d["dk"][ks], d["dv"][ks]), workspace=self._ws[c],
-                                     dropout_origin=origin)
+                                     dropout_origin=origin, o_residual=res)
                 self._ev_bwd[c].record(self._s_run)
             with torch.cuda.stream(self._s_out):
                 self._s_out.wait_event(self._ev_fwd[c])
@@ -224,7 +228,7 @@ class HostAttentionStep:
     def synchronize(self) -> None:
         """Block the host until the results of the last call are in host memory."""
         self._ev_done.synchronize()
-        _ops.check_status(self.device)
+        _ops.check_status(self.device, synchronize=False)      # the word is in host memory: no device sync
 
 
 __all__ = ["HostAttentionStep", "chunk_bounds", "plan_chunks"]

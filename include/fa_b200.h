@@ -92,8 +92,14 @@ typedef struct fa_b200_params {
     float*         lse;            /* (B, H, Nq) fp32; fwd output / bwd input      */
     void*          workspace;      /* backward scratch, >= fa_b200_bwd_workspace_bytes */
     size_t         workspace_bytes;
-    int32_t*       status_word;    /* optional device int32, set non-zero when a
-                                      bounded device-side wait gives up            */
+    int32_t*       status_word;    /* optional int32 the kernels set non-zero when a bounded
+                                      device-side wait gives up.  Device memory, or pinned
+                                      host memory (which the device can write): the library
+                                      then reads it, without synchronising, on entry to every
+                                      fa_b200_fwd / fa_b200_bwd* call, and a non-zero value
+                                      left by an EARLIER call makes the call return
+                                      FA_ETIMEOUT (detail in fa_b200_last_error) after
+                                      clearing the word, without launching anything     */
     void*          stream;         /* cudaStream_t                                 */
     uint64_t       seed, offset;   /* dropout stream (Philox key / counter word)   */
     int32_t        B, Nq, Nk, H, Hkv, D;
@@ -135,7 +141,17 @@ typedef struct fa_b200_params {
        exactly the mask the whole call draws.  The reference has no replayable stream at all
        (kernels/forward_kernel.py:198-203). */
     int32_t        rng_batch_offset, rng_head_offset, rng_heads;
-    int32_t        reserved0;
+    /* Limit of one device-side wait in milliseconds (0: the default, 2000).  A kernel whose wait on an
+       mbarrier runs out stops its pipeline, frees what it holds, returns normally and writes a non-zero
+       code to *status_word; it never traps and never waits longer. */
+    int32_t        wait_limit_ms;
+    /* Optional residual of the output, same shape and dtype as o (ptr = NULL: none).  The forward
+       writes o_lo = round(O - o), what the rounding of O to 16 bits dropped; the backward, given the
+       same tensor, forms delta = rowsum(dO o (o + o_lo)) instead of rowsum(dO o o).  For rows whose
+       attention is peaked, dS = P o (dP - delta) cancels nearly equal terms and the bf16 rounding of
+       the saved output (2^-9) is the largest error in dQ and dK; with the residual it is gone.  The
+       reference saves its output in the tensors' dtype only (ops/attention.py:209-214). */
+    fa_b200_tensor o_lo;
 } fa_b200_params;
 
 /* Static tile choice for a (D, dtype, causal) key; replaces the reference's
@@ -145,8 +161,13 @@ typedef struct fa_b200_tile {
     int32_t block_m;        /* query rows per tile                            */
     int32_t block_n;        /* key rows per tile                              */
     int32_t q_tiles_per_cta;
-    int32_t kv_stages;      /* shared-memory ring depth for K/V tiles         */
+    int32_t kv_stages;      /* ring depth: forward K and V tiles; backward, the
+                               streamed tile read twice per step (Q_i or K_j)  */
     int32_t num_warps;
+    int32_t w_stages;       /* backward: ring depth of the other streamed tile */
+    int32_t regs_softmax;   /* forward: registers per softmax thread ...        */
+    int32_t regs_other;     /* ... and per MMA / TMA / converting thread        */
+    int32_t one_kernel_backward;  /* backward: dK, dV and dQ from one kernel    */
 } fa_b200_tile;
 
 /* Forward: o, lse <- attention(q, k, v).  Replaces
@@ -273,6 +294,16 @@ float fa_b200_dropout_effective_p(float dropout_p);
 /* Raw Philox4x32-10 block (public algorithm, Salmon et al. 2011), exposed so
  * callers can check the generator against its published known answers. */
 void fa_b200_philox4x32_10(const uint32_t counter[4], const uint32_t key[2], uint32_t out[4]);
+
+/*
+ * Self-test of the bounded device-side wait, the mechanism behind FA_ETIMEOUT: launches one small
+ * kernel in which a thread waits, for at most `limit_ms` (1..1000) milliseconds, on an mbarrier that
+ * nothing ever arrives at.  The kernel returns normally and writes 9 to *status_word (device memory or
+ * pinned host memory).  With a word in pinned host memory the next fa_b200_fwd / fa_b200_bwd call that
+ * is given the same word then returns FA_ETIMEOUT.  No counterpart in the reference, whose error path
+ * is a Python try/except around the launch (interface.py:331-348).
+ */
+int fa_b200_selftest_wait_timeout(int32_t* status_word, int limit_ms, int device, void* stream);
 
 const char* fa_b200_strerror(int status);
 const char* fa_b200_last_error(void);

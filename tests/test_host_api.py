@@ -107,25 +107,78 @@ def test_workspace_estimates():
     assert est["total_memory_mb"] < 4 * 32 * 4096 * 4096 * 2 / 2 ** 20   # far below the N^2 scores
 
 
+def test_tile_table_reports_the_constants_the_kernels_are_compiled_from():
+    """The lookup and the kernels read one header (csrc/tile_config.cuh).  The header's numbers are
+    parsed here as text and compared with what the library reports; the kernel sources are checked to
+    take their stage counts, register split and warp counts from the header and not from literals."""
+    import re
+    csrc = os.path.join(ROOT, "flash-attn-v100_b200", "csrc")
+    hdr = open(os.path.join(csrc, "tile_config.cuh")).read()
+
+    def const(name):
+        return int(re.search(r"constexpr \w+ %s = ([0-9]+)" % name, hdr).group(1))
+
+    def fn(name):      # constexpr int f(...) { return <expr>; } evaluated with Python's ternary
+        body = re.search(r"constexpr int %s\(([^)]*)\) \{ return (.*?); \}" % name, hdr)
+        args = [a.split()[-1] for a in body.group(1).split(",")]
+        expr = re.sub(r"(\S+) == (\d+) \? (\d+) : ", r"\3 if \1 == \2 else ", body.group(2))
+        expr = re.sub(r"\((\w+) \? (\d+) : (\d+)\)", r"(\2 if \1 else \3)", expr)
+        return lambda *v: eval(expr, dict(zip(args, v)))
+
+    fwd_stages, u_stages, w_stages = fn("fwd_kv_stages"), fn("bwd_u_stages"), fn("bwd_w_stages")
+    for D in (64, 128):
+        for dt in (torch.float16, torch.bfloat16):
+            for causal in (False, True):
+                f = tile_table.lookup(D, dt, causal, False)
+                b = tile_table.lookup(D, dt, causal, True)
+                assert (f["BLOCK_M"], f["BLOCK_N"]) == (const("kBlockM"), const("kBlockN"))
+                assert f["NUM_STAGES"] == fwd_stages(D) and f["NUM_WARPS"] == const("kFwdWarps")
+                assert f["Q_TILES_PER_CTA"] == const("kFwdQTilesPerCta")
+                assert (f["REGS_SOFTMAX"], f["REGS_OTHER"]) == (const("kFwdRegsSoftmax"), const("kFwdRegsOther"))
+                assert b["NUM_STAGES"] == u_stages(D, False) and b["W_STAGES"] == w_stages(D)
+                assert b["NUM_WARPS"] == 4 * const("kBwdWarpgroups") + 4
+                assert b["ONE_KERNEL_BACKWARD"] == (D == 64)
+    assert fwd_stages(128) == 2 and fwd_stages(64) == 4 and u_stages(128, False) == 3 and u_stages(128, True) == 2
+    fwd = open(os.path.join(csrc, "fwd_sm100.cu")).read()
+    bwd = open(os.path.join(csrc, "bwd_sm100.cu")).read()
+    for needle in ("tile::fwd_kv_stages(D)", "tile::kFwdRegsSoftmax", "tile::kFwdWarps", "tile::kFwdHalfSignalAt"):
+        assert needle in fwd, needle
+    for needle in ("tile::bwd_u_stages(D, kMasks)", "tile::bwd_w_stages(D)", "tile::kBwdWarpgroups",
+                   "tile::kBwdOverlapMaxKvBytes", "tile::kBwdGroupBytes"):
+        assert needle in bwd, needle
+
+
 def test_workspace_size_follows_the_backward_variant():
-    """D = 64 in 16 bits: the one-kernel backward adds the fp32 dQ sums; the two-pass variant,
-    D = 128 and fp32 need the two per-row vectors only."""
+    """Regions (each starts on a 256-byte boundary): the two per-row vectors and the per-column ranges
+    (max |dO|, max |V|) for every tensor-core call; for bf16 the row exponents and the fp16 copies of Q,
+    dO and K the kernels stream; for the one-kernel backward (D = 64) the fp32 dQ sums instead of the
+    copy of K.  fp32 (CUDA-core tiles) needs one vector."""
     lib = _cabi.load()
+    B, N, H = 2, 300, 4
 
     def size(D, dtype, variant):
         p = _cabi.Params()
         p.struct_bytes = ctypes.sizeof(_cabi.Params)
-        p.B, p.Nq, p.Nk, p.H, p.Hkv, p.D = 2, 300, 300, 4, 4, D
+        p.B, p.Nq, p.Nk, p.H, p.Hkv, p.D = B, N, N, H, H, D
         p.dtype, p.scale, p.variant = dtype, 0.125, variant
         return int(lib.fa_b200_bwd_workspace_bytes(ctypes.byref(p)))
 
-    rows = 2 * 4 * 384                                   # B * H * ceil128(Nq)
-    vectors = 2 * rows * 4
-    bf16 = tile_table.dtype_enum(torch.bfloat16)
-    assert size(128, bf16, _cabi.VARIANT_AUTO) == vectors
-    assert size(64, bf16, _cabi.VARIANT_TCGEN05_2PASS) == vectors
-    assert size(64, bf16, _cabi.VARIANT_AUTO) == vectors + rows * 64 * 4
-    assert size(64, bf16, _cabi.VARIANT_TCGEN05) == vectors + rows * 64 * 4
+    up = lambda n: -(-n // 256) * 256
+    rows = B * H * 384 * 4                                # B * H * ceil128(Nq) floats
+    ranges = up(B * H * 2 * 4)
+    vectors = 2 * rows + ranges
+
+    def tensor(D):
+        return up(B * N * H * D * 2)
+
+    bf16, fp16 = tile_table.dtype_enum(torch.bfloat16), tile_table.dtype_enum(torch.float16)
+    assert rows % 256 == 0
+    assert size(128, fp16, _cabi.VARIANT_AUTO) == vectors
+    assert size(64, fp16, _cabi.VARIANT_TCGEN05_2PASS) == vectors
+    assert size(64, fp16, _cabi.VARIANT_AUTO) == vectors + rows * 64
+    assert size(128, bf16, _cabi.VARIANT_AUTO) == vectors + rows + 3 * tensor(128)
+    assert size(64, bf16, _cabi.VARIANT_TCGEN05_2PASS) == vectors + rows + 3 * tensor(64)
+    assert size(64, bf16, _cabi.VARIANT_TCGEN05) == vectors + rows + 2 * tensor(64) + rows * 64
     assert size(64, tile_table.dtype_enum(torch.float32), _cabi.VARIANT_AUTO) <= vectors
     assert _cabi.VARIANT_NAMES[_cabi.VARIANT_TCGEN05_2PASS] == "tcgen05_2pass"
 

@@ -72,9 +72,10 @@ def test_host_step_matches_one_call_over_the_whole_problem(chunks, dropout_p):
         assert len(step.chunks) == 6 and step.chunks[0] == (0, 1, 0, 2)
     seed, offset = (0x5EED, 3) if dropout_p > 0 else (0, 0)
     d = {n: t.to(dev) for n, t in host.items()}
-    o, lse = ops.launch_forward(d["q"], d["k"], d["v"], step.scale, True, dropout_p, seed, offset)
+    res = torch.empty_like(d["q"])            # bf16: the step keeps the output residual for its backward
+    o, lse = ops.launch_forward(d["q"], d["k"], d["v"], step.scale, True, dropout_p, seed, offset, o_residual=res)
     dq, dk, dv = ops.launch_backward(d["d_o"], d["q"], d["k"], d["v"], o, lse, step.scale, True, dropout_p,
-                                     seed, offset)
+                                     seed, offset, o_residual=res)
     for rep in range(2):                       # the second call reuses buffers while the first drains
         for t in out.values():
             t.fill_(float("nan"))

