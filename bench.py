@@ -449,12 +449,17 @@ def main():
                     help="N > 1: every rank runs the whole workload (weak scaling) instead of its shard of it")
     ap.add_argument("--batch", type=int, default=None, help="override the workload's batch (small profiling cases)")
     ap.add_argument("--heads", type=int, default=None, help="override the workload's head count")
+    ap.add_argument("--dtype", choices=("fp16", "bf16"), default=None, help="override the workload's dtype (A/B runs)")
     args = ap.parse_args()
     from flash_attention_v100.testing import WORKLOADS
     w = WORKLOADS[args.workload]
     if args.batch is not None or args.heads is not None:
         b, h = args.batch or w.B, args.heads or w.H
         w = w.shrink(B=b, H=h, name=f"{w.name} [reduced to B{b} H{h}: not the benchmark size]")
+    if args.dtype is not None:
+        dt = {"fp16": torch.float16, "bf16": torch.bfloat16}[args.dtype]
+        if dt != w.dtype:
+            w = w.shrink(dtype=dt, name=f"{w.name} [dtype overridden to {args.dtype}: not the benchmark dtype]")
     if args.impl == "reference":
         run_reference(args, w)
     else:

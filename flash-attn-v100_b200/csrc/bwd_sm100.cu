@@ -1170,63 +1170,66 @@ bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const 
         absmax16_commit<T>(m, ranges + 2 * (int64_t)col + 1, red);
         return;
     }
-    const int64_t row = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + lane / LPR;
-    const bool live = row < (int64_t)B * H * nq_pad;
-    const int i = live ? (int)(row % nq_pad) : 0;
-    const int64_t bh = live ? row / nq_pad : 0;
+    // a block takes one 128-row tile of one (b, h): kPasses passes of 256 / LPR rows, a pass's loads
+    // issued together; one reduction of max |dO| per block
+    constexpr int kRowsPerPass = 8 * RPW;
+    constexpr int kPasses = 128 / kRowsPerPass;
+    const int tiles_per_col = nq_pad / 128;
+    const int64_t bh = (int64_t)blockIdx.x / tiles_per_col;
+    const int i0 = ((int)blockIdx.x - (int)(bh * tiles_per_col)) * 128 + (int)(threadIdx.x >> 5) * RPW + lane / LPR;
     const int h = (int)(bh % H), b = (int)(bh / H);
-    float s = 0.f;
+    const T* op = o + b * o_sb + h * o_sh + sub * 8;
+    const T* gp = d_o + b * g_sb + h * g_sh + sub * 8;
+    const T* lp = cp.o_lo ? reinterpret_cast<const T*>(cp.o_lo) + b * cp.l_sb + h * cp.l_sh + sub * 8 : nullptr;
+    const T* qp = COPIES ? reinterpret_cast<const T*>(cp.q) + b * cp.q_sb + h * cp.q_sh + sub * 8 : nullptr;
     uint32_t m = 0u;
-    if (live && i < Nq) {
-        const uint4 vo = *reinterpret_cast<const uint4*>(o + b * o_sb + i * o_sn + h * o_sh + sub * 8);
-        const uint4 vg = *reinterpret_cast<const uint4*>(d_o + b * g_sb + i * g_sn + h * g_sh + sub * 8);
+#pragma unroll 2
+    for (int ps = 0; ps < kPasses; ++ps) {
+        const int i = i0 + ps * kRowsPerPass;
+        const int64_t row = bh * nq_pad + i;
+        const bool in = i < Nq;
+        uint4 vo = make_uint4(0, 0, 0, 0), vg = vo, vl = vo, vq = vo;
+        if (in) {
+            vo = *reinterpret_cast<const uint4*>(op + (int64_t)i * o_sn);
+            vg = *reinterpret_cast<const uint4*>(gp + (int64_t)i * g_sn);
+            if (lp) vl = *reinterpret_cast<const uint4*>(lp + (int64_t)i * cp.l_sn);
+            if (COPIES) vq = *reinterpret_cast<const uint4*>(qp + (int64_t)i * cp.q_sn);
+        }
         const T* eo = reinterpret_cast<const T*>(&vo);
         const T* eg = reinterpret_cast<const T*>(&vg);
-        if (cp.o_lo) {
-            // delta from the output as the forward computed it, not as 16 bits hold it
-            const uint4 vl = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(cp.o_lo) + b * cp.l_sb +
-                                                             i * cp.l_sn + h * cp.l_sh + sub * 8);
-            const T* el = reinterpret_cast<const T*>(&vl);
+        const T* el = reinterpret_cast<const T*>(&vl);
+        float s = 0.f;
+        // delta from the output as the forward computed it (o + o_lo) when the residual is there
 #pragma unroll
-            for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(eo[e]) + to_f32<T>(el[e]), to_f32<T>(eg[e]), s);
-        } else {
+        for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(eo[e]) + to_f32<T>(el[e]), to_f32<T>(eg[e]), s);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(eo[e]), to_f32<T>(eg[e]), s);
+        for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        const uint32_t m_mine = absmax16_acc(0u, vg);
+        m = max(m, max(m_mine & 0xFFFFu, m_mine >> 16));
+        int e_i = 0;
+        if (COPIES) {
+            // the row's largest |dO| (a bf16 bit pattern) over the lanes that share the row
+            uint32_t mr = max(m_mine & 0xFFFFu, m_mine >> 16);
+#pragma unroll
+            for (int off = LPR / 2; off > 0; off >>= 1) mr = max(mr, __shfl_xor_sync(0xffffffffu, mr, off));
+            e_i = log2_bound_bits(mr << 16) - 15;
+            if (in) {
+                const int64_t at = (((int64_t)b * Nq + i) * H + h) * D + sub * 8;
+                const uint64_t mul2 = f2_pack(pow2i(-e_i), pow2i(-e_i));
+                *reinterpret_cast<uint4*>(cp.q16 + at) = make_uint4(bf16x2_to_f16x2(vq.x), bf16x2_to_f16x2(vq.y),
+                                                                    bf16x2_to_f16x2(vq.z), bf16x2_to_f16x2(vq.w));
+                *reinterpret_cast<uint4*>(cp.do16 + at) = make_uint4(bf16x2_to_f16x2(vg.x, mul2), bf16x2_to_f16x2(vg.y, mul2),
+                                                                     bf16x2_to_f16x2(vg.z, mul2), bf16x2_to_f16x2(vg.w, mul2));
+            }
         }
-        m = absmax16_acc(m, vg);
-    }
-#pragma unroll
-    for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    int e_i = 0;
-    if (COPIES) {
-        // the row's largest |dO| (a bf16 bit pattern) over the lanes that share the row
-        uint32_t mr = max(m & 0xFFFFu, m >> 16);
-#pragma unroll
-        for (int off = LPR / 2; off > 0; off >>= 1) mr = max(mr, __shfl_xor_sync(0xffffffffu, mr, off));
-        e_i = log2_bound_bits(mr << 16) - 15;
-        if (live && i < Nq) {
-            const int64_t at = (((int64_t)b * Nq + i) * H + h) * D + sub * 8;
-            const uint64_t mul2 = f2_pack(pow2i(-e_i), pow2i(-e_i));
-            const T* qp = reinterpret_cast<const T*>(cp.q);
-            const uint4 vq = *reinterpret_cast<const uint4*>(qp + b * cp.q_sb + i * cp.q_sn + h * cp.q_sh + sub * 8);
-            const uint4 vg = *reinterpret_cast<const uint4*>(d_o + b * g_sb + i * g_sn + h * g_sh + sub * 8);
-            *reinterpret_cast<uint4*>(cp.q16 + at) = make_uint4(bf16x2_to_f16x2(vq.x), bf16x2_to_f16x2(vq.y),
-                                                                bf16x2_to_f16x2(vq.z), bf16x2_to_f16x2(vq.w));
-            *reinterpret_cast<uint4*>(cp.do16 + at) = make_uint4(bf16x2_to_f16x2(vg.x, mul2), bf16x2_to_f16x2(vg.y, mul2),
-                                                                 bf16x2_to_f16x2(vg.z, mul2), bf16x2_to_f16x2(vg.w, mul2));
+        if (sub == 0) {
+            if (in) { delta[row] = -s * pow2i(-e_i); lse2[row] = kPShift - lse[bh * Nq + i] * kLog2e + (float)e_i; }
+            else    { delta[row] = 0.f; lse2[row] = -INFINITY; }
+            if (COPIES) cp.erow[row] = in ? (float)e_i : 0.f;
         }
     }
-    if (live && sub == 0) {
-        if (i < Nq) { delta[row] = -s * pow2i(-e_i); lse2[row] = kPShift - lse[bh * Nq + i] * kLog2e + (float)e_i; }
-        else        { delta[row] = 0.f; lse2[row] = -INFINITY; }
-        if (COPIES) cp.erow[row] = (i < Nq) ? (float)e_i : 0.f;
-    }
-    // the block's first row decides the column (all its rows share it: 128 is a multiple of the rows per block)
-    const int64_t row0 = (int64_t)blockIdx.x * 8 * RPW;
-    const int64_t bh0 = row0 / nq_pad;
     const int group = H / Hkv;
-    const int64_t col0 = (bh0 / H) * Hkv + (bh0 % H) / group;
-    absmax16_commit<T>(m, ranges + 2 * col0, red);
+    absmax16_commit<T>(m, ranges + 2 * ((int64_t)b * Hkv + h / group), red);
 }
 
 // fused backward: fp32 dQ sums (tiles of [D/4][128 rows][4]) * scale -> dQ in the call's dtype and layout
@@ -1279,12 +1282,11 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     if (phases & 1) {
         if (fused) FA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, ws.dq_bytes, st));
         FA_CUDA_CHECK(cudaMemsetAsync(ranges, 0, ws.rng_bytes, st));
-        const int64_t rows = (int64_t)p.B * p.H * nq_pad;
-        constexpr int kRowsPerBlock = 8 * (256 / D);
-        const int n_row_blocks = (int)((rows + kRowsPerBlock - 1) / kRowsPerBlock);
+        const int64_t n_row_blocks64 = (int64_t)p.B * p.H * (nq_pad / 128);      // one block per 128-row tile
         const int v_slabs = (p.Nk + 255) / 256;
-        const int64_t n_blocks = (int64_t)n_row_blocks + (int64_t)p.B * p.Hkv * v_slabs;
-        if (rows + kRowsPerBlock > 0x7fffffff || n_blocks > 0x7fffffff) { set_error("problem too large for the preprocess grid"); return FA_EUNSUPPORTED; }
+        const int64_t n_blocks = n_row_blocks64 + (int64_t)p.B * p.Hkv * v_slabs;
+        if (n_blocks > 0x7fffffff) { set_error("problem too large for the preprocess grid"); return FA_EUNSUPPORTED; }
+        const int n_row_blocks = (int)n_row_blocks64;
         PreprocessCopies cp = {};
         cp.o_lo = p.o_lo.ptr; cp.l_sb = p.o_lo.stride_b; cp.l_sn = p.o_lo.stride_n; cp.l_sh = p.o_lo.stride_h;
         if (COPIES) {

@@ -55,12 +55,13 @@ def chunk_bounds(batch: int, chunks: int) -> List[Tuple[int, int]]:
 
 
 def plan_chunks(batch: int, heads: int, heads_kv: int, chunks: Optional[int] = None,
-                min_columns: int = 16, target: int = 16) -> List[Chunk]:
+                min_columns: int = 8, target: int = 16) -> List[Chunk]:
     """Cut the (batch x heads) grid into chunks, batch-major.
 
     `chunks=None` aims at `target` chunks of at least `min_columns` (batch, head) columns each (fewer
     columns leave SMs idle in the kernels; fewer chunks expose more of the first copy-in and the last
-    copy-out).  Up to `batch` chunks are whole batch entries; beyond that every batch entry is cut
+    copy-out).  Measured on B200 over PCIe, B4 N4096 H32 D128 bf16: 4 chunks 13.8 ms per step, 8 12.1,
+    16 11.6, 32 12.8, 64 18.0; B1 N16384 H32: 2 chunks 16.9, 4 14.1, 8 14.2, 16 15.1: eight columns a chunk.  Up to `batch` chunks are whole batch entries; beyond that every batch entry is cut
     into head groups, at multiples of the K/V group size H / Hkv so that a chunk owns its K/V heads.
     """
     if batch <= 0:

@@ -38,8 +38,9 @@ def test_plan_chunks_cover_the_grid_once():
                 assert len(plan) == chunks
     # a batch of one is cut along heads, so its copies can overlap its kernels
     assert len(hp.plan_chunks(1, 32, 32)) > 1
-    # the default keeps at least 16 columns per chunk
-    assert all((b1 - b0) * (h1 - h0) >= 16 for b0, b1, h0, h1 in hp.plan_chunks(4, 32, 32))
+    # the default keeps at least 8 columns per chunk
+    assert all((b1 - b0) * (h1 - h0) >= 8 for b0, b1, h0, h1 in hp.plan_chunks(4, 32, 32))
+    assert len(hp.plan_chunks(4, 32, 32)) == 16 and len(hp.plan_chunks(1, 32, 32)) == 4
 
 
 def test_needs_cuda():
