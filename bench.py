@@ -270,7 +270,7 @@ def run_ours(args, whole):
         if w.dropout_p > 0:
             fa.set_dropout_seed(*stream)
         o = fa.flash_attention_v100(q, k, v, causal=w.causal, scale=w.scale, dropout_p=w.dropout_p,
-                                    enable_multi_gpu=False, dropout_origin=origin,
+                                    enable_multi_gpu=False, dropout_origin=origin, optimization_strategy=args.strategy,
                                     dropout_stream=stream if origin is not None else None)
         o.backward(dev["d_o"])
         q.grad = k.grad = v.grad = None
@@ -327,6 +327,8 @@ def run_ours(args, whole):
     p.d_o = ops._tensor4(dev["d_o"])
     p.dq, p.dk, p.dv = (ops._tensor4(g) for g in grads)
     lib = _cabi.load()
+    if args.strategy == "speed":
+        p.variant = _cabi.VARIANT_TCGEN05
     nbytes = int(lib.fa_b200_bwd_workspace_bytes(ctypes.byref(p)))
     ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
     p.workspace, p.workspace_bytes = ws.data_ptr(), nbytes
@@ -341,9 +343,10 @@ def run_ours(args, whole):
 
     call(lib.fa_b200_bwd, 0)()
     ksteps = max(5, args.steps)
-    # D = 64 in fp16/bf16 takes the one-kernel backward: phase 2 is the kernel that produces dK, dV and
-    # the fp32 dQ sums (5 GEMMs), phase 4 the conversion of the sums to dQ
-    one_kernel = (w.D == 64 and w.dtype in (torch.float16, torch.bfloat16))
+    # --strategy speed at D = 64 in fp16/bf16 takes the one-kernel backward: phase 2 is the kernel that
+    # produces dK, dV and the fp32 dQ sums (5 GEMMs), phase 4 the conversion of the sums to dQ; the
+    # default is the deterministic two-pass form at every size
+    one_kernel = (args.strategy == "speed" and w.D == 64 and w.dtype in (torch.float16, torch.bfloat16))
     k2, k4 = ("bwd_dkdvdq", "bwd_dq_convert") if one_kernel else ("bwd_dkdv", "bwd_dq")
     kern_ms = {
         "fwd": time_steps(call(lib.fa_b200_fwd, 0), ksteps, device, world),
@@ -407,7 +410,7 @@ def run_ours(args, whole):
             "data": "synthetic",
             "config": {
                 "workload": whole.name, "B": whole.B, "N": whole.N, "H": whole.H, "D": whole.D,
-                "causal": whole.causal, "dropout_p": whole.dropout_p,
+                "causal": whole.causal, "dropout_p": whole.dropout_p, "optimization_strategy": args.strategy,
                 "split": split, "per_gpu": "B%d H%d of the workload, resident on the GPU" % (w.B, w.H),
                 "parallelism": f"(batch x heads) shards, {world} rank(s), no data-path collective",
                 "l2": ("not flushed: q, k, v, o, dO, dQ, dK, dV are %.0f MB each (working set %.0f MB), %s the 126 MB L2"
@@ -445,6 +448,8 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", default="cfg3")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--strategy", choices=("balanced", "speed"), default="balanced",
+                    help="optimization_strategy of the public entry: 'speed' allows the backward whose dQ is not bit-reproducible")
     ap.add_argument("--replicas", action="store_true",
                     help="N > 1: every rank runs the whole workload (weak scaling) instead of its shard of it")
     ap.add_argument("--batch", type=int, default=None, help="override the workload's batch (small profiling cases)")

@@ -198,7 +198,9 @@ int choose_variant(const fa_b200_params& p, bool backward, int* variant) {
         *variant = p.variant;
         return FA_OK;
     }
-    if (p.variant == FA_B200_VARIANT_AUTO && tc) { *variant = FA_B200_VARIANT_TCGEN05; return FA_OK; }
+    // AUTO is the deterministic form: every gradient element is summed by one CTA in a fixed order.
+    // The one-kernel backward (dQ tiles summed with unordered global additions) is opt-in (TCGEN05).
+    if (p.variant == FA_B200_VARIANT_AUTO && tc) { *variant = FA_B200_VARIANT_TCGEN05_2PASS; return FA_OK; }
     if (!simt_supports(p)) {
         set_error("no kernel covers D=%d (CUDA-core tiles need D <= 128; tensor-core tiles: %s)", p.D, why);
         return FA_EUNSUPPORTED;
@@ -295,7 +297,7 @@ size_t fa_b200_bwd_workspace_bytes(const fa_b200_params* p) {
     const char* why = "";
     q.variant = FA_B200_VARIANT_AUTO;
     if (p->variant != FA_B200_VARIANT_SIMT && sm100_supports(q, true, &why))
-        variant = (p->variant == FA_B200_VARIANT_TCGEN05_2PASS) ? FA_B200_VARIANT_TCGEN05_2PASS : FA_B200_VARIANT_TCGEN05;
+        variant = (p->variant == FA_B200_VARIANT_TCGEN05) ? FA_B200_VARIANT_TCGEN05 : FA_B200_VARIANT_TCGEN05_2PASS;
     return bwd_workspace_layout(*p, variant).total;
 }
 
@@ -410,7 +412,7 @@ int fa_b200_tile_config(int D, int dtype, int causal, int backward, fa_b200_tile
     memset(out, 0, sizeof(*out));
     bool tc = (dtype == FA_B200_F16 || dtype == FA_B200_BF16) && (D == 64 || D == 128);
     if (tc) {
-        out->variant = FA_B200_VARIANT_TCGEN05;
+        out->variant = FA_B200_VARIANT_TCGEN05_2PASS;     // what AUTO runs
         out->block_m = tile::kBlockM;
         out->block_n = tile::kBlockN;
         out->q_tiles_per_cta = backward ? 1 : tile::kFwdQTilesPerCta;
@@ -419,7 +421,7 @@ int fa_b200_tile_config(int D, int dtype, int causal, int backward, fa_b200_tile
         out->num_warps = backward ? tile::kBwdWarps : tile::kFwdWarps;
         out->regs_softmax = backward ? 0 : tile::kFwdRegsSoftmax;
         out->regs_other = backward ? 0 : tile::kFwdRegsOther;
-        out->one_kernel_backward = backward && tile::bwd_one_kernel(D) ? 1 : 0;
+        out->one_kernel_backward = backward && tile::bwd_one_kernel(D) ? 1 : 0;   // available on request (TCGEN05)
     } else {
         out->variant = FA_B200_VARIANT_SIMT;
         out->block_m = 64;

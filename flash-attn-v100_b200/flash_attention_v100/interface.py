@@ -283,8 +283,11 @@ def flash_attention_v100(
             problem, e.g. a rank that received its shard from `scatter_shards`: the shard's (batch offset,
             head offset, heads of the whole problem) and the whole problem's (seed, offset).  The shard
             then draws exactly the dropout mask the whole call would draw for its columns
-        block_size_m, block_size_n, enable_autotuning, optimization_strategy:
+        block_size_m, block_size_n, enable_autotuning:
             accepted for source compatibility; tiles come from the static table
+        optimization_strategy: "speed" lets the backward use its fastest kernels even where they sum dQ
+            in no fixed order (D = 64: one kernel for dK, dV and dQ); any other value ("balanced",
+            "memory") keeps every gradient bit-reproducible
         return_softmax_lse: also return the (B, H, Nq) fp32 log-sum-exp
         enable_multi_gpu: shard (batch x heads) over the visible GPUs (auto if None)
         enable_profiling: record CUDA-event timings in manager.performance_history
@@ -316,8 +319,8 @@ def flash_attention_v100(
     else:
         result = FlashAttentionV100Function.apply(q, k, v, scale, causal, dropout_p, bias, block_size_m,
                                                   block_size_n, enable_autotuning, return_softmax_lse,
-                                                  False, True, None, True, "balanced", False, 1, 0, key_lengths,
-                                                  shift, dropout_origin, dropout_stream)
+                                                  False, True, None, True, optimization_strategy, False, 1, 0,
+                                                  key_lengths, shift, dropout_origin, dropout_stream)
     if profile:
         end.record(torch.cuda.current_stream(q.device))
         end.synchronize()
@@ -392,7 +395,7 @@ def _execute_multi_gpu(q, k, v, scale, causal, dropout_p, bias, block_size_m, bl
             ll = key_lengths[shard[0]:shard[1]].to(dev, non_blocking=True) if key_lengths is not None else None
             res = FlashAttentionV100Function.apply(ql, kl, vl, scale, causal, dropout_p, bl, block_size_m,
                                                    block_size_n, enable_autotuning, return_softmax_lse,
-                                                   False, True, None, True, "balanced", False, 1, 0, ll, causal_shift,
+                                                   False, True, None, True, manager.optimization_strategy, False, 1, 0, ll, causal_shift,
                                                    (b_base + shard[0], h_base + shard[2], h_total), dropout_stream)
             o_l, lse_l = res if return_softmax_lse else (res, None)
             outs.append((shard, o_l.to(home, non_blocking=True)))

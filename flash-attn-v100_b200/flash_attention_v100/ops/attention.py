@@ -133,7 +133,7 @@ def _lengths_operand(key_lengths: Optional[torch.Tensor], q: torch.Tensor):
 
 
 def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift=0,
-                 dropout_origin=None) -> _cabi.Params:
+                 dropout_origin=None, variant=None) -> _cabi.Params:
     p = _cabi.Params()
     p.struct_bytes = ctypes.sizeof(_cabi.Params)
     p.q, p.k, p.v, p.o = _tensor4(q), _tensor4(k), _tensor4(v), _tensor4(o)
@@ -143,7 +143,9 @@ def _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal
     p.dtype = dtype_enum(q.dtype)
     p.causal = int(bool(causal))
     p.causal_shift = int(causal_shift) if causal else 0
-    p.variant = getattr(_variant_override, "value", _cabi.VARIANT_AUTO)
+    # an explicit kernel_variant() block wins; else the caller's choice (the autograd op's "speed" mode)
+    override = getattr(_variant_override, "value", _cabi.VARIANT_AUTO)
+    p.variant = override if override != _cabi.VARIANT_AUTO else (variant or _cabi.VARIANT_AUTO)
     p.device = q.device.index if q.device.index is not None else torch.cuda.current_device()
     p.scale = float(scale)
     p.dropout_p = float(dropout_p)
@@ -193,11 +195,12 @@ def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=
 
 def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None,
                     workspace=None, bias=None, d_scores=None, key_lengths=None, causal_shift=0,
-                    dropout_origin=None, o_residual=None):
+                    dropout_origin=None, o_residual=None, fast=False):
     """dq, dk, dv <- fa_b200_bwd.  Counterpart of
     flash_attention_backward_triton_enhanced (kernels/backward_kernel.py:208-318).
     `out=(dq, dk, dv)` and `workspace` (uint8, at least fa_b200_bwd_workspace_bytes)
-    use caller-owned buffers instead of allocating."""
+    use caller-owned buffers instead of allocating.  `fast`: allow the one-kernel backward where it
+    is faster (D = 64); dQ is then summed in no fixed order and is not bit-reproducible."""
     d_o = _last_dim_contiguous(d_o)
     if out is not None:
         dq, dk, dv = out
@@ -205,7 +208,8 @@ def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, 
         dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
         dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
-    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift, dropout_origin)
+    p = _base_params(q, k, v, o, lse, scale, causal, dropout_p, seed, offset, causal_shift, dropout_origin,
+                     variant=_cabi.VARIANT_TCGEN05 if fast else None)
     p.d_o, p.dq, p.dk, p.dv = _tensor4(d_o), _tensor4(dq), _tensor4(dk), _tensor4(dv)
     p.bias, _keep = _bias_operand(bias)
     p.kv_lengths, _keep_len = _lengths_operand(key_lengths, q)
@@ -309,6 +313,9 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
                                 causal_shift=causal_shift, dropout_origin=dropout_origin, o_residual=o_lo)
         ctx.dropout_origin = dropout_origin
         ctx.has_bias, ctx.has_residual = bias is not None, o_lo is not None
+        # performance_mode "speed" (the public entry's optimization_strategy) opts into the fastest
+        # backward, whose dQ is not bit-reproducible at D = 64; every other mode is deterministic
+        ctx.fast = performance_mode == "speed"
         ctx.save_for_backward(q, k, v, o, lse, *([bias] if bias is not None else []),
                               *([o_lo] if o_lo is not None else []))
         ctx.key_lengths = key_lengths
@@ -335,7 +342,7 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
         dq, dk, dv = launch_backward(grad_output, q, k, v, o, lse, ctx.scale, ctx.causal,
                                      ctx.dropout_p, ctx.seed, ctx.offset, bias=bias, d_scores=d_scores,
                                      key_lengths=ctx.key_lengths, causal_shift=ctx.causal_shift,
-                                     dropout_origin=ctx.dropout_origin, o_residual=o_lo)
+                                     dropout_origin=ctx.dropout_origin, o_residual=o_lo, fast=ctx.fast and bias is None)
         if d_scores is not None:
             dims = [i for i in range(4) if bias.shape[i] == 1 and d_scores.shape[i] != 1]
             grad_bias = (d_scores.sum(dim=dims, keepdim=True) if dims else d_scores).to(bias.dtype)
@@ -377,7 +384,8 @@ def flash_attention_backward_enhanced(grad_output, q, k, v, output, lse, max_val
                                scale, causal, kwargs.get("dropout_p", 0.0), seed, offset,
                                bias=kwargs.get("bias"), d_scores=kwargs.get("d_scores"),
                                key_lengths=kwargs.get("key_lengths"), dropout_origin=kwargs.get("dropout_origin"),
-                               o_residual=kwargs.get("output_residual"))
+                               o_residual=kwargs.get("output_residual"),
+                               fast=kwargs.get("performance_mode") == "speed")
 
 
 def compare_with_pytorch_attention_enhanced(q, k, v, causal: bool = False,

@@ -105,7 +105,9 @@ class HostAttentionStep:
         self.q_shape, self.k_shape, self.dtype = (B, Nq, H, D), (B, Nk, Hkv, D), dtype
         self.causal, self.dropout_p = bool(causal), float(dropout_p)
         self.scale = float(D ** -0.5 if scale is None else scale)
-        self.chunks: List[Chunk] = plan_chunks(B, H, Hkv, chunks)
+        # a chunk should also move enough bytes for a copy to run at PCIe speed: 8 MiB per tensor
+        col_bytes = max(1, max(Nq, Nk) * D * torch.empty((), dtype=dtype).element_size())
+        self.chunks: List[Chunk] = plan_chunks(B, H, Hkv, chunks, min_columns=max(8, -(-(8 << 20) // col_bytes)))
         self.bounds = self.chunks               # (b0, b1, h0, h1) per chunk
         self._group = H // Hkv
         dev = self.device

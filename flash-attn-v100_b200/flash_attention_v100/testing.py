@@ -113,10 +113,10 @@ def tolerance(dtype: torch.dtype, variant: str = "auto", head_dim: int = 128) ->
 
 def dq_is_bit_reproducible(variant: str, dtype: torch.dtype, head_dim: int, dropout_p: float = 0.0) -> bool:
     """Whether two backward calls on the same inputs return the same dQ bit for bit.
-    dK, dV, O and LSE always do.  The one-kernel tensor-core backward sums dQ
-    tiles with unordered fp32 additions; it serves fp16/bf16 with D = 64
-    unless the two-pass variant is asked for."""
-    if variant not in ("auto", "tcgen05"):
+    dK, dV, O and LSE always do, and so does dQ by default ("auto").  Only the opt-in
+    fast variant ("tcgen05": optimization_strategy="speed") sums dQ tiles with
+    unordered fp32 additions, for fp16/bf16 with D = 64."""
+    if variant != "tcgen05":
         return True
     return not (dtype in (torch.float16, torch.bfloat16) and head_dim == 64)
 

@@ -55,19 +55,22 @@ typedef enum fa_b200_status {
     FA_ETIMEOUT     = -6   /* a bounded device-side wait ran out (status word)     */
 } fa_b200_status;
 
-/* Which kernel family serves the call.  AUTO picks from the static tile table. */
+/* Which kernel family serves the call.  AUTO: the tensor-core family where it covers the call
+ * (fp16/bf16, D in {64, 128}, aligned tensors, no bias), in its deterministic form, else CUDA-core
+ * tiles. */
 typedef enum fa_b200_variant {
     FA_B200_VARIANT_AUTO    = 0,
     FA_B200_VARIANT_SIMT    = 1,  /* CUDA-core tiles: any D <= 128, all dtypes, fp32 exact */
-    FA_B200_VARIANT_TCGEN05 = 2,  /* TMA + tcgen05/TMEM: fp16/bf16, D in {64, 128}         */
+    FA_B200_VARIANT_TCGEN05 = 2,  /* TMA + tcgen05/TMEM, the fastest backward on offer: where it is
+                                     faster (D = 64) ONE kernel produces dK, dV and dQ, summing dQ
+                                     tiles into an fp32 buffer with unordered global additions (as the
+                                     reference does, kernels/backward_kernel.py:179-194): dQ is then
+                                     not bit-reproducible.  Forward: identical to 2PASS.          */
     FA_B200_VARIANT_TCGEN05_2PASS = 3
-                                  /* the same family with the two-pass backward: one kernel
-                                     for dK, dV and one for dQ, every output owned by one CTA,
-                                     so gradients are bit-reproducible.  TCGEN05 itself uses
-                                     one kernel that sums dQ tiles into an fp32 buffer with
-                                     unordered global additions (as the reference does,
-                                     kernels/backward_kernel.py:179-194) where that is
-                                     faster: D = 64.  Forward: identical.                   */
+                                  /* the same family with the two-pass backward (what AUTO runs):
+                                     one kernel for dK, dV and one for dQ, every output element
+                                     owned by one CTA and summed in a fixed order, so all
+                                     gradients are bit-reproducible.                              */
 } fa_b200_variant;
 
 /* One (B, N, H, D) tensor: base pointer and element strides (D stride is 1). */
@@ -176,7 +179,8 @@ int fa_b200_fwd(const fa_b200_params* p);
 
 /* Backward: dq, dk, dv <- grad(q, k, v, o, lse, dO).  Replaces
  * kernels/backward_kernel.py:208-318 (launcher) and :17-205 (kernel).
- * dq is reduced in a fixed order: two runs give bit-identical results. */
+ * With variant AUTO, SIMT or TCGEN05_2PASS every gradient element is summed in a fixed order: two
+ * runs give bit-identical dq, dk and dv.  Variant TCGEN05 at D = 64 trades that for speed (dq only). */
 int fa_b200_bwd(const fa_b200_params* p);
 
 /*

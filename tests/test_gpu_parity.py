@@ -529,3 +529,23 @@ def test_bounded_wait_runs_out_and_the_next_call_reports_it(device):
         ops.check_status(device)
     assert int(word[0]) == 0
 
+
+def test_default_gradients_are_deterministic_and_speed_mode_is_opt_in(device):
+    """D = 64, fp16: the default backward owns every dQ element in one CTA (two runs bit-equal);
+    optimization_strategy="speed" takes the one-kernel backward, whose dQ is summed in no fixed order
+    and agrees with the default to the reordering of fp32 sums."""
+    g = torch.Generator().manual_seed(11)
+    qc, kc, vc, gc = (torch.randn(2, 700, 3, 64, generator=g).half() for _ in range(4))
+
+    def grads(strategy):
+        q, k, v = (t.to(device).requires_grad_(True) for t in (qc, kc, vc))
+        o = fa.flash_attention_v100(q, k, v, causal=True, optimization_strategy=strategy, enable_multi_gpu=False)
+        o.backward(gc.to(device))
+        return q.grad, k.grad, v.grad
+
+    a, b = grads("balanced"), grads("balanced")
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    f = grads("speed")
+    assert torch.equal(f[1], a[1]) and torch.equal(f[2], a[2])
+    assert rel_l2(f[0], a[0]) <= 1e-3
+

@@ -90,7 +90,7 @@ def test_tile_table_keys_and_families():
     cfg = fa.get_enhanced_config(4096, 128, dtype=torch.bfloat16, causal=True)
     for key in ("BLOCK_M", "BLOCK_N", "BLOCK_K", "NUM_STAGES", "NUM_WARPS"):   # reference config.py:288-348
         assert key in cfg
-    assert cfg["BLOCK_K"] == 128 and cfg["VARIANT"] == "tcgen05"
+    assert cfg["BLOCK_K"] == 128 and cfg["VARIANT"] == "tcgen05_2pass"     # what AUTO runs: the deterministic form
     assert tile_table.lookup(64, torch.float32)["VARIANT"] == "simt"
     assert tile_table.lookup(96, torch.float16)["VARIANT"] == "simt"
     with pytest.raises(ValueError):
@@ -175,7 +175,8 @@ def test_workspace_size_follows_the_backward_variant():
     assert rows % 256 == 0
     assert size(128, fp16, _cabi.VARIANT_AUTO) == vectors
     assert size(64, fp16, _cabi.VARIANT_TCGEN05_2PASS) == vectors
-    assert size(64, fp16, _cabi.VARIANT_AUTO) == vectors + rows * 64
+    assert size(64, fp16, _cabi.VARIANT_AUTO) == vectors                  # AUTO is the two-pass form
+    assert size(64, fp16, _cabi.VARIANT_TCGEN05) == vectors + rows * 64
     assert size(128, bf16, _cabi.VARIANT_AUTO) == vectors + rows + 3 * tensor(128)
     assert size(64, bf16, _cabi.VARIANT_TCGEN05_2PASS) == vectors + rows + 3 * tensor(64)
     assert size(64, bf16, _cabi.VARIANT_TCGEN05) == vectors + rows + 2 * tensor(64) + rows * 64
@@ -189,8 +190,10 @@ def test_dq_reproducibility_table():
     assert dq_is_bit_reproducible("simt", torch.float16, 64)
     assert dq_is_bit_reproducible("auto", torch.bfloat16, 128)
     assert dq_is_bit_reproducible("auto", torch.float32, 64)
-    assert not dq_is_bit_reproducible("auto", torch.float16, 64)
+    assert dq_is_bit_reproducible("auto", torch.float16, 64)          # the default is deterministic
+    assert not dq_is_bit_reproducible("tcgen05", torch.float16, 64)   # the opt-in fast variant is not, at D = 64
     assert not dq_is_bit_reproducible("tcgen05", torch.bfloat16, 64, 0.1)
+    assert dq_is_bit_reproducible("tcgen05", torch.bfloat16, 128)
 
 
 def test_public_signatures_match_the_reference():
