@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(os.path.dirname(HERE), "flash_attention_v100", "lib")
 OUT = os.path.join(OUT_DIR, "libfa_b200.so")
-SOURCES = ["host_api.cu", "simt_kernels.cu", "fwd_sm100.cu", "bwd_sm100.cu", "combine.cu"]
+SOURCES = ["host_api.cu", "simt_kernels.cu", "fwd_sm100.cu", "fwd_tf32_sm100.cu", "bwd_sm100.cu", "combine.cu"]
 HEADERS = ["fa_common.cuh", "philox.cuh", "sm100_ptx.cuh", "tma_host.cuh", "tile_config.cuh",
            os.path.join("..", "..", "include", "fa_b200.h")]
 NVCC_FLAGS = [

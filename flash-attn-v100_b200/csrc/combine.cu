@@ -118,6 +118,9 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineArgs a) {
                 wa = __fdividef(wa, s);
                 wp = __fdividef(wp, s);
             }
+            // every lane of the row has read the old log-sum-exp above before one of them replaces it
+            // (independent thread scheduling gives no such order by itself)
+            __syncwarp(__activemask());
             if (c == 0) a.lse_acc[li] = ln;
         }
         float x[8], y[8];

@@ -87,6 +87,9 @@ bool simt_supports(const fa_b200_params& p);
 int sm100_fwd(const fa_b200_params& p);
 int sm100_bwd(const fa_b200_params& p, const BwdWorkspace& ws);
 bool sm100_supports(const fa_b200_params& p, bool backward, const char** why);
+// fp32 forward on the tensor cores (fwd_tf32_sm100.cu): TF32 products taken three times
+int sm100_tf32_fwd(const fa_b200_params& p);
+bool sm100_tf32_fwd_supports(const fa_b200_params& p, const char** why);
 // Whether the one-kernel backward (dQ summed with global additions) covers a call the family supports.
 bool sm100_bwd_fused_supported(const fa_b200_params& p);
 

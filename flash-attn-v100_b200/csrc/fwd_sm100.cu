@@ -650,7 +650,12 @@ bool tensor_ok(const fa_b200_tensor& t, int64_t B, int64_t N, int64_t H) {
 
 // Which calls the tensor-core family covers.  `why` names the first reason it does not.
 bool sm100_supports(const fa_b200_params& p, bool backward, const char** why) {
-    if (p.dtype != FA_B200_F16 && p.dtype != FA_B200_BF16) { *why = "dtype must be fp16 or bf16"; return false; }
+    if (p.dtype == FA_B200_F32) {
+        // fp32: the forward has a tensor-core kernel (TF32 products taken three times); the backward is CUDA-core tiles
+        if (backward) { *why = "the fp32 backward is served by the CUDA-core kernels"; return false; }
+        return sm100_tf32_fwd_supports(p, why);
+    }
+    if (p.dtype != FA_B200_F16 && p.dtype != FA_B200_BF16) { *why = "dtype must be fp16, bf16 or fp32"; return false; }
     if (p.bias.ptr) { *why = "an additive bias is served by the CUDA-core kernels"; return false; }
     if (p.D != 64 && p.D != 128) { *why = "head_dim must be 64 or 128"; return false; }
     if (!(p.scale > 0.f) || !(p.scale < 1e30f)) { *why = "scale must be positive and finite"; return false; }
@@ -668,6 +673,7 @@ bool sm100_supports(const fa_b200_params& p, bool backward, const char** why) {
 }
 
 int sm100_fwd(const fa_b200_params& p) {
+    if (p.dtype == FA_B200_F32) return sm100_tf32_fwd(p);
     if (p.dtype == FA_B200_BF16) return p.D == 128 ? launch<128, true>(p) : launch<64, true>(p);
     return p.D == 128 ? launch<128, false>(p) : launch<64, false>(p);
 }

@@ -170,7 +170,7 @@ int refuse_after_timeout(const fa_b200_params* p, const char* what) {
     const int code = take_host_status(p->status_word);
     if (code == 0) return FA_OK;
     set_error("%s: an earlier call's device-side wait ran out (status %d: 1 forward, 2 dK/dV, 3 dQ, 4 one-kernel "
-              "backward, 8 shared memory, 9 self-test); its results are invalid.  The word has been cleared", what, code);
+              "backward, 5 fp32 forward, 8 shared memory, 9 self-test); its results are invalid.  The word has been cleared", what, code);
     return FA_ETIMEOUT;
 }
 

@@ -115,11 +115,6 @@ __device__ __forceinline__ void red_add_v4_f32(float* gptr, float x, float y, fl
                  ::"l"(gptr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
 }
 
-// Ask for the 128-byte line holding `gptr` to be brought into L1.
-__device__ __forceinline__ void prefetch_l1(const void* gptr) {
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(gptr));
-}
-
 // ---- TMA ----------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -141,15 +136,6 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void*
                                              int c0, int c1, int c2, int c3) {
     asm volatile(
         "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)),
-          "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-        : "memory");
-}
-// 4-D tiled reduce-add shared -> global (fp32 accumulate in L2).
-__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const void* smem_src,
-                                                  int c0, int c1, int c2, int c3) {
-    asm volatile(
-        "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
         ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)),
           "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
@@ -230,15 +216,22 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(bool a_bf16, bool b_bf16, 
 // K-major operand:  stride = 1024 (next 8 rows); leading offset unused.
 // MN-major operand: stride = 1024 (next 8 K rows); leading = bytes to the next
 //                   64-element chunk along M/N.
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t leading_bytes,
-                                                         uint32_t stride_bytes) {
+// `layout`: bits 61-63, 2 = 128-byte swizzle in 16-byte pieces; 1 = 128-byte swizzle in 32-byte
+// pieces (the only arrangement of an MN-major 32-bit operand: rows of 128 bytes, 4-row groups of
+// 512 bytes; stride = bytes to the next 4 K rows).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t leading_bytes,
+                                                   uint32_t stride_bytes, uint32_t layout) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
     d |= (uint64_t)((leading_bytes >> 4) & 0x3FFFu) << 16;
     d |= (uint64_t)((stride_bytes >> 4) & 0x3FFFu) << 32;
     d |= 1ull << 46;
-    d |= 2ull << 61;
+    d |= (uint64_t)layout << 61;
     return d;
+}
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t leading_bytes,
+                                                         uint32_t stride_bytes) {
+    return make_smem_desc(smem_addr, leading_bytes, stride_bytes, 2u);
 }
 
 // ---- tcgen05: TMEM <-> registers ---------------------------------------------------

@@ -31,12 +31,13 @@ inline EncodeTiledFn encode_tiled_fn() {
 
 // Tensor map over a (B, N, H, D) tensor with element strides (sb, sn, sh, 1):
 // dimensions ordered (D, H, N, B); a box is `box_rows` sequence positions of
-// one head by `box_cols` elements of D, 128-byte swizzled (box_cols * elem
-// size must be 128 bytes) or unswizzled.  Out-of-range rows read as zero.
+// one head by `box_cols` elements of D; `swizzle`: 0 none, 1 the 128-byte swizzle (16-byte
+// pieces; box_cols * elem size must be 128 bytes), 2 the 128-byte swizzle in 32-byte pieces (what
+// tcgen05.mma wants for an MN-major 32-bit operand).  Out-of-range rows read as zero.
 // Returns 0 on success, else the CUresult (or -1 if the driver entry point is missing).
 inline int make_tmap_bnhd(CUtensorMap* map, const void* ptr, CUtensorMapDataType dt, size_t elem_bytes,
                           int64_t B, int64_t N, int64_t H, int64_t D, int64_t sb, int64_t sn, int64_t sh,
-                          int box_rows, int box_cols, bool swizzle128) {
+                          int box_rows, int box_cols, int swizzle) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return -1;
     // size-1 dimensions may carry arbitrary strides in a tensor view: give them a legal one
@@ -49,7 +50,8 @@ inline int make_tmap_bnhd(CUtensorMap* map, const void* ptr, CUtensorMapDataType
     cuuint32_t box[4] = {(cuuint32_t)box_cols, 1u, (cuuint32_t)box_rows, 1u};
     cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
     CUresult r = fn(map, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                 : (swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE),
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return (int)r;
 }
@@ -78,20 +80,20 @@ static_assert(sizeof(TmapKey) % 8 == 0, "the key is hashed and compared as 64-bi
 
 inline int cached_tmap_bnhd(CUtensorMap* map, const void* ptr, CUtensorMapDataType dt, size_t elem_bytes,
                             int64_t B, int64_t N, int64_t H, int64_t D, int64_t sb, int64_t sn, int64_t sh,
-                            int box_rows, int box_cols, bool swizzle128) {
+                            int box_rows, int box_cols, int swizzle) {
     static std::mutex mu;
     static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
     TmapKey key;
     memset(&key, 0, sizeof(key));
     key.ptr = (uint64_t)(uintptr_t)ptr;
     key.B = B; key.N = N; key.H = H; key.D = D; key.sb = sb; key.sn = sn; key.sh = sh;
-    key.dt = (int32_t)dt; key.box_rows = box_rows; key.box_cols = box_cols; key.swizzle = swizzle128 ? 1 : 0;
+    key.dt = (int32_t)dt; key.box_rows = box_rows; key.box_cols = box_cols; key.swizzle = swizzle;
     {
         std::lock_guard<std::mutex> lock(mu);
         auto it = cache.find(key);
         if (it != cache.end()) { *map = it->second; return 0; }
     }
-    const int r = make_tmap_bnhd(map, ptr, dt, elem_bytes, B, N, H, D, sb, sn, sh, box_rows, box_cols, swizzle128);
+    const int r = make_tmap_bnhd(map, ptr, dt, elem_bytes, B, N, H, D, sb, sn, sh, box_rows, box_cols, swizzle);
     if (r == 0) {
         std::lock_guard<std::mutex> lock(mu);
         if (cache.size() >= 4096) cache.clear();          // bounded: start over rather than grow for ever

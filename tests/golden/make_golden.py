@@ -2,7 +2,7 @@
 
 Run in the build container (where the reference tree is mounted):
 
-    python tests/golden/make_golden.py [/path/to/parent/of/reference]
+    python tests/golden/make_golden.py /path/to/parent/of/reference
 
 It imports the reference package (whose top-level `flash_attention_v100` is the
 PyTorch math path, reference __init__.py:30-55), runs it and autograd through
@@ -33,7 +33,9 @@ CASES = [
 
 
 def main():
-    parent = sys.argv[1] if len(sys.argv) > 1 else "/root"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python make_golden.py <directory that holds the reference checkout as 'reference/'>")
+    parent = sys.argv[1]
     sys.path.insert(0, parent)
     with redirect_stdout(io.StringIO()):      # the reference prints a no-CUDA warning on import
         import reference

@@ -33,8 +33,10 @@ def _tc_ok(dtype, D):
 def _variants(dtype, D):
     """Kernel families to run a case on; FA_B200_TEST_VARIANTS=simt narrows a debugging run."""
     allowed = os.environ.get("FA_B200_TEST_VARIANTS", "simt,tcgen05").split(",")
-    out = [v for v in (["simt", "tcgen05", "tcgen05_2pass"] if _tc_ok(dtype, D) else ["simt"])
-           if v.split("_")[0] in allowed]
+    names = ["simt", "tcgen05", "tcgen05_2pass"] if _tc_ok(dtype, D) else ["simt"]
+    if dtype == torch.float32 and D == 64 and "tcgen05" in allowed:
+        names.append("auto")       # fp32, D = 64: the forward takes the TF32 tensor-core kernel, the backward CUDA-core tiles
+    out = [v for v in names if v == "auto" or v.split("_")[0] in allowed]
     assert out
     return out
 
@@ -320,15 +322,23 @@ def test_softmax_range_stress_rows(device):
             _check(f"{variant}:{name} (autograd)", got, ref_auto, 1e-2)
 
 
-def test_cfg1_quickstart_shape_fp32_forward(device):
-    """B2 N1024 H12 D64 fp32 causal, seed 0: O against the reference's stored rows, LSE against the oracle."""
+@pytest.mark.parametrize("variant", ["tcgen05", "simt"], ids=["tf32-tensor-cores", "cuda-cores"])
+def test_cfg1_quickstart_shape_fp32_forward(device, variant):
+    """B2 N1024 H12 D64 fp32 causal, seed 0: O against the reference's stored rows, LSE against the oracle,
+    1e-5 on both kernel families: the tensor-core one (tcgen05.mma kind::tf32, every product taken three
+    times; what AUTO runs for this shape) and the CUDA-core tiles."""
     w = WORKLOADS["cfg1"]
     t = make_inputs(w)
     z = np.load(os.path.join(GOLDEN, "math_path_cfg1_rows.npz"))
-    o, lse = launch_forward(t["q"].to(device), t["k"].to(device), t["v"].to(device), w.scale, True)
+    with kernel_variant(variant):
+        o, lse = launch_forward(t["q"].to(device), t["k"].to(device), t["v"].to(device), w.scale, True)
     _check("o rows", o[:, ::int(z["row_step"])], torch.from_numpy(z["o_rows"]), 1e-5)
     _, rlse = ao.chunked(ao.attention_forward, t["q"], t["k"], t["v"], heads_per_chunk=4, causal=True, scale=w.scale)
     _check("lse", lse, rlse, 1e-5)
+    if variant == "tcgen05":
+        # AUTO takes the same kernel: bit-identical
+        o2, lse2 = launch_forward(t["q"].to(device), t["k"].to(device), t["v"].to(device), w.scale, True)
+        assert torch.equal(o, o2) and torch.equal(lse, lse2)
 
 
 def test_error_codes_on_device(device):
