@@ -118,10 +118,10 @@ def measured_peak():
         return FALLBACK_BF16_TFLOPS, "fallback (earlier measurement on this pool)", {}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
-# profiles/ncu_full_fwd_bwd_cfg3_batch1.md: measured at batch 1 of the default workload and scaled by
-# the batch (traffic is proportional to the number of independent (batch, head) columns).
-NCU_DRAM_BYTES_PER_BATCH = {"fwd": 111.5e6, "bwd_dkdv": 175.9e6, "bwd_dq": 155.3e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from an ncu capture of these kernels at batch 1
+# of the default workload (32 (batch, head) columns of N4096 D128 bf16 causal), scaled by the number of
+# columns: traffic is proportional to it, every column being independent.
+NCU_DRAM_BYTES_PER_BATCH = {"fwd": 127.4e6, "bwd_preprocess": 213.5e6, "bwd_dkdv": 202.5e6, "bwd_dq": 158.2e6}
 
 
 def ncu_traffic(kernel: str, w):

@@ -31,6 +31,9 @@ namespace fa {
 struct PhiloxKey {
     uint32_t k0, k1;   // key words
     uint32_t c3;       // fourth counter word (offset_lo)
+    // the ten round keys (k0 + r W0, k1 + r W1): the same for every block of a call, so they are
+    // worked out once on the host and reach the kernels as launch constants
+    uint32_t r0[10], r1[10];
 };
 
 FA_HD PhiloxKey philox_make_key(uint64_t seed, uint64_t offset) {
@@ -38,6 +41,10 @@ FA_HD PhiloxKey philox_make_key(uint64_t seed, uint64_t offset) {
     k.k0 = (uint32_t)seed;
     k.k1 = (uint32_t)(seed >> 32) ^ (uint32_t)(offset >> 32);
     k.c3 = (uint32_t)offset;
+    for (int r = 0; r < 10; ++r) {
+        k.r0[r] = k.k0 + (uint32_t)r * 0x9E3779B9u;
+        k.r1[r] = k.k1 + (uint32_t)r * 0xBB67AE85u;
+    }
     return k;
 }
 
@@ -53,15 +60,11 @@ FA_HD uint32_t dropout_column(const DropoutOrigin& o, int b, int h) {
     return (uint32_t)((b + o.b0) * o.heads + h + o.h0);
 }
 
+// both halves of the 64-bit product (one wide multiply on the device)
 FA_HD void philox_mulhilo(uint32_t a, uint32_t b, uint32_t& hi, uint32_t& lo) {
-#if defined(__CUDA_ARCH__)
-    lo = a * b;
-    hi = __umulhi(a, b);
-#else
     uint64_t p = (uint64_t)a * (uint64_t)b;
     lo = (uint32_t)p;
     hi = (uint32_t)(p >> 32);
-#endif
 }
 
 FA_HD void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
@@ -81,10 +84,25 @@ FA_HD void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
     out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
 }
 
+// The same ten rounds with the round keys taken from the table in `key`.
+FA_HD void philox4x32_10_keyed(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, const PhiloxKey& key, uint32_t out[4]) {
+    const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u;
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        uint32_t hi0, lo0, hi1, lo1;
+        philox_mulhilo(M0, c0, hi0, lo0);
+        philox_mulhilo(M1, c2, hi1, lo1);
+        uint32_t n0 = hi1 ^ c1 ^ key.r0[r];
+        uint32_t n2 = hi0 ^ c3 ^ key.r1[r];
+        c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
 // 16 random bytes for keys [16*jblk, 16*jblk+16) of query row i of head bh.
 FA_HD void dropout_block(const PhiloxKey& key, uint32_t bh, uint32_t i, uint32_t jblk,
                          uint32_t out[4]) {
-    philox4x32_10(jblk, i, bh, key.c3, key.k0, key.k1, out);
+    philox4x32_10_keyed(jblk, i, bh, key.c3, key, out);
 }
 
 // Threshold in [0, 256]: a byte is dropped iff byte < threshold.
