@@ -58,7 +58,6 @@
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
 #include "tile_config.cuh"
-#include <stdlib.h>
 #include <type_traits>
 
 namespace fa {
