@@ -332,6 +332,11 @@ def run_ours(args, whole):
     nbytes = int(lib.fa_b200_bwd_workspace_bytes(ctypes.byref(p)))
     ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
     p.workspace, p.workspace_bytes = ws.data_ptr(), nbytes
+    # dropout: the keep bits are written once (by the forward) and read by all three kernels
+    nbits = int(lib.fa_b200_dropout_bits_bytes(ctypes.byref(p)))
+    bits = torch.empty(max(nbits, 16), dtype=torch.uint8, device=device)
+    if nbits:
+        p.dropout_bits, p.dropout_bits_bytes = bits.data_ptr(), nbits
 
     def call(fn, phases):
         def run():
@@ -341,8 +346,11 @@ def run_ours(args, whole):
                 _cabi.raise_for_status(rc, "bench")
         return run
 
+    call(lib.fa_b200_fwd, 0)()         # fills the keep bits (dropout_bits_ready = 0)
     call(lib.fa_b200_bwd, 0)()
     ksteps = max(5, args.steps)
+    fwd_and_bits_ms = time_steps(call(lib.fa_b200_fwd, 0), ksteps, device, world) if nbits else None
+    p.dropout_bits_ready = 1
     # --strategy speed at D = 64 in fp16/bf16 takes the one-kernel backward: phase 2 is the kernel that
     # produces dK, dV and the fp32 dQ sums (5 GEMMs), phase 4 the conversion of the sums to dQ; the
     # default is the deterministic two-pass form at every size
@@ -354,6 +362,8 @@ def run_ours(args, whole):
         k2: time_steps(call(lib.fa_b200_bwd, 2), ksteps, device, world),
         k4: time_steps(call(lib.fa_b200_bwd, 4), ksteps, device, world),
     }
+    if nbits:
+        kern_ms["dropout_bits"] = max(0.0, fwd_and_bits_ms - kern_ms["fwd"])     # its own launch before the forward
     p.bwd_phases = 0
     status = ops._status_word(device)
 
@@ -430,7 +440,8 @@ def run_ours(args, whole):
                     "single_stream_ms_per_step": ms_e2e_serial,
                     "host_gbs_per_rank": host_gbs_rank, "host_gbs_all_ranks": float(host_gbs.item()),
                     "ranks_bound_to_gpu_numa_node": int(bound.item())},
-            "gpu_launches": 4 * args.steps,     # per step: 1 forward + 3 backward kernels of this library
+            # per step: 1 forward + 3 backward kernels of this library (+ 1 that writes the dropout bits)
+            "gpu_launches": (5 if nbits else 4) * args.steps,
             "clocks": clock_info,
             "status_word": int(status[0]),
         }

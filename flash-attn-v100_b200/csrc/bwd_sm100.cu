@@ -78,12 +78,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 // time at all (it can only start when the last reader has finished and is needed at once); W is
 // done within one step.  D = 128 has room for three U stages and two W stages, except that the
 // key-stationary dropout instance needs 4 KB for its masks and stays at two and two.
-template <int D, int MODE, bool DROP>
+// DROP: 0 no dropout; 1 keep bits drawn by the kernel's own threads; 2 loaded from the call's bit buffer.
+template <int D, int MODE, int DROP>
 struct BwdCfg {
     static constexpr int kNBox = D / 64;
     static constexpr int kTileBytes = kNBox * kBoxBytes;
     static constexpr bool kFused = (MODE == 2);
-    static constexpr bool kMasks = DROP && MODE != 1;            // masks are built in shared memory when keys are rows
+    static constexpr bool kMasks = DROP == 1 && MODE != 1;       // masks are built in shared memory when keys are rows
     static constexpr int kUStages = tile::bwd_u_stages(D, kMasks);
     static constexpr int kWStages = tile::bwd_w_stages(D);
     static constexpr int kMaskBytes = 2 * 128 * 8 * 2;          // two buffers of 128 x 8 uint16 keep masks
@@ -140,6 +141,10 @@ struct BwdArgs {
     float inv_keep;
     PhiloxKey key;
     DropoutOrigin rng;
+    // DROP = 2, the call's keep bits as dropout_bits_kernel lays them out:
+    const uint4* bits_q;           // [(b*H + h) * ceil128(Nk)/128 + key tile][nq_pad]: 128 keys of one query row
+    const uint32_t* bits_k;        // [((b*H + h) * nq_pad/128 + query tile) * 4 + g][nk_pad]: 32 queries of one key row
+    int nk_pad;
 };
 
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -232,7 +237,7 @@ __device__ __forceinline__ CtaWork cta_work(int cols_per_group) {
 // INLINE (bf16 inputs only): the streamed tiles arrive as bf16 and the two spare warps convert them;
 // otherwise bf16 calls stream the fp16 copies the preprocess launch (Q, dO) and the dK/dV kernel (K:
 // map_aux, a by-product of its stationary tile) have written to the workspace.
-template <int D, bool BF16, int MODE, int NWG, bool DROP, bool INLINE>
+template <int D, bool BF16, int MODE, int NWG, int DROP, bool INLINE>
 __global__ void __launch_bounds__(128 * NWG + kExtraThreads, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                  const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
@@ -605,7 +610,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const int tid = wg * 128 + r;                          // 0 .. 128*NWG-1
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const int row_g = tile * kTile + r;                    // MODE 0: key index; MODE 1: query index
-        constexpr bool drop = DROP;
+        constexpr bool drop = DROP != 0;
         float my_nlse2 = 0.f, my_ndelta = 0.f;      // -lse*log2(e) and -delta of my query row (MODE 1)
         if (MODE == 1) {
             const int64_t off = ((int64_t)b * a.H + head_x) * a.nq_pad + row_g;
@@ -681,7 +686,22 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             uint32_t kb[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};
             if (drop) {
                 kb[0] = 0u; kb[1] = 0u;
-                if (MODE == 1) {
+                if constexpr (DROP == 2) {
+                    static_assert(CPT % 32 == 0, "a thread's columns are whole words of the bit buffer");
+                    if (MODE == 1) {
+                        // my query row's bits for this key tile: the words of my CPT columns
+                        const uint32_t* w = reinterpret_cast<const uint32_t*>(
+                            a.bits_q + ((int64_t)(b * a.H + head_q) * (a.nk_pad / kTile) + strm_tile) * a.nq_pad + row_g);
+#pragma unroll
+                        for (int g = 0; g < CPT / 32; ++g) kb[g] = w[cb / 32 + g];
+                    } else if (FUSED) {
+                        // my key row's bits for this query tile, 32 queries a word
+                        const uint32_t* w = a.bits_k + (((int64_t)(b * a.H + head_q) * (a.nq_pad / kTile) + strm_tile) * 4 +
+                                                        cb / 32) * (int64_t)a.nk_pad + row_g;
+#pragma unroll
+                        for (int g = 0; g < CPT / 32; ++g) kb[g] = w[(int64_t)g * a.nk_pad];
+                    }
+                } else if (MODE == 1) {
 #pragma unroll
                     for (int g = 0; g < CPT / 16; ++g) {
                         const uint32_t w = dropout_keep_bits(a.key, bh, (uint32_t)row_g, (uint32_t)((col_g0 >> 4) + g),
@@ -730,7 +750,21 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tmem_ld_16x256b_x4(tT1 + t_hi, pf[1]);
             tmem_wait_ld();
             uint32_t kbits = 0xFFFFFFFFu;                           // keep bit of element (h, j, k, e): bit 16h + 4j + 2k + e
-            if (drop) {
+            if constexpr (DROP == 2) {
+                // one word per key row of mine: bit q = query 32 (cb / 32) + q of this tile
+                const uint32_t* w = a.bits_k + (((int64_t)(b * a.H + head_q) * (a.nq_pad / kTile) + strm_tile) * 4 +
+                                                cb / 32) * (int64_t)a.nk_pad + tile * kTile + rbase;
+                kbits = 0u;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const uint32_t word = w[16 * h + 8 * k] >> ((cb & 31) + 2 * lq);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            kbits |= ((word >> (8 * j)) & 3u) << (16 * h + 4 * j + 2 * k);
+                    }
+            } else if (drop) {
                 const uint16_t* mbuf = sMask + (it & 1) * (128 * 8);
                 kbits = 0u;
 #pragma unroll
@@ -1260,6 +1294,18 @@ bwd_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, int Nq,
 
 // INLINE: bf16 call without room for the fp16 copies (the workspace-free entry point): the main kernels
 // convert their tiles themselves.
+// the kernel instance and its shared memory for a dropout form (0 none, 1 drawn in the kernel, 2 loaded;
+// the converting-in-kernel instances, which serve the entry without a workspace, never load)
+template <int D, bool BF16, int MODE, bool INLINE>
+auto pick_kernel(int drop) {
+    if (drop == 2 && !INLINE) return bwd_sm100_kernel<D, BF16, MODE, kNWG, INLINE ? 1 : 2, INLINE>;
+    return drop ? bwd_sm100_kernel<D, BF16, MODE, kNWG, 1, INLINE> : bwd_sm100_kernel<D, BF16, MODE, kNWG, 0, INLINE>;
+}
+template <int D, int MODE>
+int pick_smem(int drop) {
+    return drop == 2 ? BwdCfg<D, MODE, 2>::kSmemBytes : (drop ? BwdCfg<D, MODE, 1>::kSmemBytes : BwdCfg<D, MODE, 0>::kSmemBytes);
+}
+
 template <int D, bool BF16, bool INLINE>
 int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
@@ -1275,7 +1321,10 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
 
     const bool fused = ws.dq_bytes > 0;
     float* dq_acc = fused ? (float*)(wsp + ws.dq_off) : nullptr;
-    const bool drop = dropout_threshold(p.dropout_p) != 0u;
+    // dropout: 0 none, 1 the kernels draw their bits, 2 they load them from the call's bit buffer
+    int drop = dropout_threshold(p.dropout_p) != 0u ? 1 : 0;
+    const size_t bits_one = dropout_bits_bytes(p);
+    if (!INLINE && drop && p.dropout_bits && p.dropout_bits_bytes >= 2 * bits_one) drop = 2;
 
     const int phases = p.bwd_phases ? p.bwd_phases : 7;
     if (phases & 1) {
@@ -1344,17 +1393,24 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
     a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
     a.key = philox_make_key(p.seed, p.offset);
     a.rng = dropout_origin_of(p);
+    a.bits_q = (const uint4*)p.dropout_bits;
+    a.bits_k = (const uint32_t*)((const char*)p.dropout_bits + bits_one);
+    a.nk_pad = (int)align_up((size_t)p.Nk, 128);
+    if (drop == 2 && !p.dropout_bits_ready && (phases & 1)) {
+        int rc = launch_dropout_bits(p, (void*)a.bits_q, (void*)a.bits_k);
+        if (rc) return rc;
+    }
 
     static std::mutex smem_mu;             // per (D, dtype, INLINE) instance of this function
-    static uint64_t smem_done[6] = {};     // [kernel mode and dropout flag] -> devices whose limit is set
+    static uint64_t smem_done[9] = {};     // [kernel mode x dropout form] -> devices whose limit is set
     constexpr int kThreads = 128 * kNWG + kExtraThreads;
     const dim3 grid_kv((p.Nk + kTile - 1) / kTile, p.Hkv, p.B);
     const dim3 grid_q((p.Nq + kTile - 1) / kTile, p.H, p.B);
     if constexpr (D == 64) if (fused) {
         // one key-stationary kernel for dK, dV and the fp32 dQ sums, then the conversion of dQ
-        auto k2 = drop ? bwd_sm100_kernel<D, BF16, 2, kNWG, true, INLINE> : bwd_sm100_kernel<D, BF16, 2, kNWG, false, INLINE>;
-        const int smem2 = drop ? BwdCfg<D, 2, true>::kSmemBytes : BwdCfg<D, 2, false>::kSmemBytes;
-        FA_CUDA_CHECK(set_smem_limit_once(k2, smem2, p.device, &smem_done[drop ? 5 : 4], &smem_mu));
+        auto k2 = pick_kernel<D, BF16, 2, INLINE>(drop);
+        const int smem2 = pick_smem<D, 2>(drop);
+        FA_CUDA_CHECK(set_smem_limit_once(k2, smem2, p.device, &smem_done[6 + drop], &smem_mu));
         if (phases & 2) {
             k2<<<grid_kv, kThreads, smem2, st>>>(mk, mv, mq16, mg16, mdk, mdv, mdk, a);
             FA_CUDA_CHECK(cudaGetLastError());
@@ -1368,12 +1424,11 @@ int launch(const fa_b200_params& p, const BwdWorkspace& ws) {
         return FA_OK;
     }
     if (COPIES && ws.k16_bytes == 0) { set_error("workspace layout lacks the fp16 copy of K"); return FA_EWORKSPACE; }
-    auto k0 = drop ? bwd_sm100_kernel<D, BF16, 0, kNWG, true, INLINE> : bwd_sm100_kernel<D, BF16, 0, kNWG, false, INLINE>;
-    auto k1 = drop ? bwd_sm100_kernel<D, BF16, 1, kNWG, true, INLINE> : bwd_sm100_kernel<D, BF16, 1, kNWG, false, INLINE>;
-    const int smem0 = drop ? BwdCfg<D, 0, true>::kSmemBytes : BwdCfg<D, 0, false>::kSmemBytes;
-    const int smem1 = drop ? BwdCfg<D, 1, true>::kSmemBytes : BwdCfg<D, 1, false>::kSmemBytes;
-    FA_CUDA_CHECK(set_smem_limit_once(k0, smem0, p.device, &smem_done[drop ? 1 : 0], &smem_mu));
-    FA_CUDA_CHECK(set_smem_limit_once(k1, smem1, p.device, &smem_done[drop ? 3 : 2], &smem_mu));
+    auto k0 = pick_kernel<D, BF16, 0, INLINE>(drop);
+    auto k1 = pick_kernel<D, BF16, 1, INLINE>(drop);
+    const int smem0 = pick_smem<D, 0>(drop), smem1 = pick_smem<D, 1>(drop);
+    FA_CUDA_CHECK(set_smem_limit_once(k0, smem0, p.device, &smem_done[drop], &smem_mu));
+    FA_CUDA_CHECK(set_smem_limit_once(k1, smem1, p.device, &smem_done[3 + drop], &smem_mu));
     if (phases & 2) {
         // stationary K_j, V_j; streamed Q_i, dO_i (bf16 with copies: their fp16 copies; the kernel leaves
         // the fp16 copy of K behind for the dQ kernel)

@@ -98,5 +98,8 @@ int sm_count(int device);
 
 int launch_dropout_mask(uint64_t seed, uint64_t offset, float p, int B, int H, int Nq, int Nk,
                         uint8_t* out, cudaStream_t stream);
+// The call's keep bits for the tensor-core kernels (simt_kernels.cu): mq query-major, mk key-major, either may be null.
+size_t dropout_bits_bytes(const fa_b200_params& p);
+int launch_dropout_bits(const fa_b200_params& p, void* mq, void* mk);
 
 }  // namespace fa

@@ -113,6 +113,8 @@ struct FwdArgs {
     float inv_keep;
     PhiloxKey key;
     DropoutOrigin rng;
+    const uint4* mq;               // DROP = 2: keep bits, [(b*H + h) * n_kblocks + key block][padded query row]
+    int nq_pad, n_kblocks;
 };
 
 struct Pair { int pair, h, b; };
@@ -147,7 +149,9 @@ __device__ __forceinline__ int num_blocks(const FwdArgs& a, int pair, int t, int
 // stays below 2^14 in fp16 and entries down to 2^-20 of the row's largest keep full precision.
 constexpr float kPShift = 6.0f;
 
-template <int D, bool BF16, bool DROP>
+// DROP: 0 no dropout; 1 the keep bits are drawn here, by the softmax threads (no workspace);
+// 2 they are loaded from the workspace, where dropout_bits_kernel has written the call's bits.
+template <int D, bool BF16, int DROP>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const FwdArgs a) {
@@ -422,6 +426,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 float m = -INFINITY, l = 0.f;
 
                 for (int j = 0; j < n; ++j) {
+                    // DROP = 2: the block's 128 keep bits of my row, asked for before the wait for S
+                    uint4 kb4 = make_uint4(0u, 0u, 0u, 0u);
+                    if constexpr (DROP == 2)
+                        kb4 = a.mq[((int64_t)(pr.b * a.H + pr.h) * a.n_kblocks + j) * a.nq_pad + i];
                     ok = mbar_wait(&bars[Cfg::kSFull + t], (uint32_t)s_waits & 1u, abort_flag);
                     ok = __all_sync(0xffffffffu, ok);      // the TMEM accesses below are warp-collective
                     if (!ok) break;
@@ -484,7 +492,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         for (int cc = 0; cc < 64; cc += 4) {
                             const int c = c0 * 64 + cc;
                             float x0, x1, x2, x3, p0, p1, p2, p3;
-                            if (!DROP && c0 == 1 && cc == kHalfSignalAt) {
+                            if (DROP != 1 && c0 == 1 && cc == kHalfSignalAt) {
                                 // the first half's store has had these groups' time to complete
                                 tmem_wait_st();
                                 tc_fence_before_sync();
@@ -497,21 +505,30 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             else { p2 = ex2(x2); p3 = ex2(x3); }
                             la = f2_add(la, f2_pack(p0, p1));
                             lb = f2_add(lb, f2_pack(p2, p3));
-                            if constexpr (DROP) {
+                            if constexpr (DROP == 1) {
                                 SSET(c, p0); SSET(c + 1, p1); SSET(c + 2, p2); SSET(c + 3, p3);
                             } else {
+                                if constexpr (DROP == 2) {
+                                    // dropped entries leave the MMA's operand, not the row sum above
+                                    const uint32_t word = (c >> 5) == 0 ? kb4.x : ((c >> 5) == 1 ? kb4.y : ((c >> 5) == 2 ? kb4.z : kb4.w));
+                                    const uint32_t kw = word >> (c & 31);
+                                    if (!(kw & 1u)) p0 = 0.f;
+                                    if (!(kw & 2u)) p1 = 0.f;
+                                    if (!(kw & 4u)) p2 = 0.f;
+                                    if (!(kw & 8u)) p3 = 0.f;
+                                }
                                 pk[cc / 2] = pack2<P_BF16>(p0, p1);
                                 pk[cc / 2 + 1] = pack2<P_BF16>(p2, p3);
                             }
                         }
-                        if constexpr (!DROP) tmem_st_32x32(tS + c0 * 32, pk);
+                        if constexpr (DROP != 1) tmem_st_32x32(tS + c0 * 32, pk);
                     }
                     {
                         float s0, s1, s2, s3;
                         f2_unpack(la, s0, s1); f2_unpack(lb, s2, s3);
                         l += (s0 + s1) + (s2 + s3);
                     }
-                    if constexpr (DROP) {
+                    if constexpr (DROP == 1) {
 #pragma unroll
                         for (int g = 0; g < 8; ++g) {
                             const uint32_t bits = dropout_keep_bits(a.key, bh, (uint32_t)i, (uint32_t)(j * 8 + g), a.drop_thr);
@@ -531,7 +548,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #undef SSET
                     tmem_wait_st();
                     tc_fence_before_sync();
-                    if (DROP) mbar_arrive_warp(&bars[Cfg::kPHalf + t]);
+                    if (DROP == 1) mbar_arrive_warp(&bars[Cfg::kPHalf + t]);
                     mbar_arrive_warp(&bars[Cfg::kPFull + t]);
                 }
                 if (!ok) break;
@@ -624,11 +641,27 @@ int launch(const fa_b200_params& p) {
     a.inv_keep = 1.f / (1.f - dropout_effective_p(p.dropout_p));
     a.key = philox_make_key(p.seed, p.offset);
     a.rng = dropout_origin_of(p);
-    auto kernel = a.drop_thr ? fwd_sm100_kernel<D, BF16, true> : fwd_sm100_kernel<D, BF16, false>;
+    // dropout: with a bit buffer the call's keep bits are written there first (unless an earlier call
+    // left them) and the kernel loads them
+    int drop = a.drop_thr ? 1 : 0;
+    a.mq = nullptr;
+    a.nq_pad = (int)align_up((size_t)p.Nq, 128);
+    a.n_kblocks = (int)(align_up((size_t)p.Nk, 128) / 128);
+    const size_t bits_one = dropout_bits_bytes(p);
+    if (drop && p.dropout_bits && p.dropout_bits_bytes >= bits_one) {
+        if (!p.dropout_bits_ready) {
+            void* by_key = p.dropout_bits_bytes >= 2 * bits_one ? (char*)p.dropout_bits + bits_one : nullptr;
+            int rc = launch_dropout_bits(p, p.dropout_bits, by_key);
+            if (rc) return rc;
+        }
+        a.mq = (const uint4*)p.dropout_bits;
+        drop = 2;
+    }
+    auto kernel = drop == 2 ? fwd_sm100_kernel<D, BF16, 2> : (drop == 1 ? fwd_sm100_kernel<D, BF16, 1> : fwd_sm100_kernel<D, BF16, 0>);
     {
         static std::mutex mu;
-        static uint64_t done[2] = {0, 0};
-        FA_CUDA_CHECK(set_smem_limit_once(kernel, Cfg::kSmemBytes, p.device, &done[a.drop_thr ? 1 : 0], &mu));
+        static uint64_t done[3] = {0, 0, 0};
+        FA_CUDA_CHECK(set_smem_limit_once(kernel, Cfg::kSmemBytes, p.device, &done[drop], &mu));
     }
     const int sms = sm_count(p.device);
     if (sms <= 0) { set_error("cannot read the SM count of device %d", p.device); return FA_ECUDA; }

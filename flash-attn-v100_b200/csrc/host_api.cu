@@ -121,6 +121,7 @@ int validate_common(const fa_b200_params* p, bool backward) {
         return FA_EINVAL;
     }
     if (p->wait_limit_ms < 0) { set_error("wait_limit_ms must not be negative"); return FA_EINVAL; }
+    if (p->dropout_bits && ((uintptr_t)p->dropout_bits & 15u)) { set_error("dropout_bits must be 16-byte aligned"); return FA_EALIGN; }
     if (p->bwd_phases < 0 || p->bwd_phases > 7) { set_error("bwd_phases must be a mask in [0, 7]"); return FA_EINVAL; }
     if (p->B == 0 || p->Nq == 0) return FA_OK;   // empty problem: nothing else to check
     int rc;
@@ -299,6 +300,17 @@ size_t fa_b200_bwd_workspace_bytes(const fa_b200_params* p) {
     if (p->variant != FA_B200_VARIANT_SIMT && sm100_supports(q, true, &why))
         variant = (p->variant == FA_B200_VARIANT_TCGEN05) ? FA_B200_VARIANT_TCGEN05 : FA_B200_VARIANT_TCGEN05_2PASS;
     return bwd_workspace_layout(*p, variant).total;
+}
+
+size_t fa_b200_dropout_bits_bytes(const fa_b200_params* p) {
+    if (!p || p->struct_bytes != sizeof(fa_b200_params)) return 0;
+    if (p->B <= 0 || p->Nq <= 0 || p->Nk <= 0 || p->H <= 0 || p->Hkv <= 0 || p->D <= 0) return 0;
+    if (dropout_threshold(p->dropout_p) == 0u || p->variant == FA_B200_VARIANT_SIMT) return 0;
+    fa_b200_params q = *p;
+    q.variant = FA_B200_VARIANT_AUTO;
+    const char* why = "";
+    if (!sm100_supports(q, false, &why) && !sm100_supports(q, true, &why)) return 0;
+    return 2 * dropout_bits_bytes(*p);
 }
 
 int fa_b200_bwd(const fa_b200_params* p) {

@@ -459,6 +459,54 @@ __global__ void dropout_mask_kernel(PhiloxKey key, uint32_t thr, int H, int Nq, 
     for (int c = 0; c < 16 && jb * 16 + c < Nk; ++c) dst[c] = (bits >> c) & 1u;
 }
 
+// Transpose of a 32 x 32 bit matrix held one row per lane: afterwards lane k holds column k, bit q = the
+// bit lane q held at position k.  Five exchanges of half-blocks (16, 8, 4, 2, 1 wide).
+__device__ __forceinline__ uint32_t transpose_bits_32x32(uint32_t x, int lane) {
+    const uint32_t masks[5] = {0x0000FFFFu, 0x00FF00FFu, 0x0F0F0F0Fu, 0x33333333u, 0x55555555u};
+#pragma unroll
+    for (int t = 0; t < 5; ++t) {
+        const int s = 16 >> t;
+        const uint32_t m = masks[t];
+        const uint32_t y = __shfl_xor_sync(0xffffffffu, x, s);
+        x = (lane & s) ? ((x & ~m) | ((y & ~m) >> s)) : ((x & m) | ((y & m) << s));
+    }
+    return x;
+}
+
+// The keep bits of a whole call, written once for the tensor-core kernels to load (drawing them inside
+// those kernels costs their softmax / elementwise threads as many instructions as the attention math
+// itself; here every SM draws at full integer rate, and the forward's bits serve the backward too).
+// One warp per (column, 32 queries, 128 keys): lane = query, eight Philox blocks of 16 keys each.
+//   mq[(col * NJ + j128) * nq_pad + i]            uint4: bit c of the 128 = key j128*128 + c   (query-major)
+//   mk[((col * NI + i128) * 4 + g) * nk_pad + k]  uint32: bit q = query i128*128 + 32 g + q     (key-major:
+//       the 32 x 32 transposes of the warp's four words)
+// Tiles the causal mask hides completely are skipped (nobody reads their bits: P is zero there).
+__global__ void __launch_bounds__(256)
+dropout_bits_kernel(PhiloxKey key, uint32_t thr, DropoutOrigin rng, int H, int Nq, int nq_pad, int nk_pad,
+                    int causal, int shift, int64_t n_items, uint4* __restrict__ mq, uint32_t* __restrict__ mk) {
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= n_items) return;                                     // whole warps leave together
+    const int NJ = nk_pad / 128, NIB = nq_pad / 32;
+    const int j128 = (int)(item % NJ);
+    const int64_t rest = item / NJ;
+    const int ib = (int)(rest % NIB);
+    const int64_t col = rest / NIB;                                   // local b * H + h
+    if (causal && (int64_t)j128 * 128 > (int64_t)ib * 32 + 31 + shift) return;
+    const int i = ib * 32 + lane;
+    const uint32_t column = dropout_column(rng, (int)(col / H), (int)(col % H));
+    uint32_t w4[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+        w4[g >> 1] |= dropout_keep_bits(key, column, (uint32_t)i, (uint32_t)(j128 * 8 + g), thr) << (16 * (g & 1));
+    if (mq) mq[(col * NJ + j128) * (int64_t)nq_pad + i] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+    if (mk) {
+        uint32_t* dst = mk + ((col * (nq_pad / 128) + (ib >> 2)) * 4 + (ib & 3)) * (int64_t)nk_pad + j128 * 128 + lane;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) dst[32 * x] = transpose_bits_32x32(w4[x], lane);
+    }
+}
+
 SimtArgs make_args(const fa_b200_params& p, float* delta) {
     SimtArgs a;
     a.q = p.q; a.k = p.k; a.v = p.v; a.o = p.o; a.d_o = p.d_o; a.dq = p.dq; a.dk = p.dk; a.dv = p.dv;
@@ -541,6 +589,24 @@ int simt_bwd(const fa_b200_params& p, const BwdWorkspace& ws) {
         case FA_B200_F32:  return launch_bwd<float>(p, ws);
     }
     return FA_EINVAL;
+}
+
+// Bytes of one orientation of a call's keep bits: B*H columns x ceil128(Nq) x ceil128(Nk) bits.
+size_t dropout_bits_bytes(const fa_b200_params& p) {
+    return (size_t)p.B * p.H * align_up((size_t)p.Nq, 128) * (align_up((size_t)p.Nk, 128) / 8);
+}
+
+int launch_dropout_bits(const fa_b200_params& p, void* mq, void* mk) {
+    const int nq_pad = (int)align_up((size_t)p.Nq, 128), nk_pad = (int)align_up((size_t)p.Nk, 128);
+    const int64_t n_items = (int64_t)p.B * p.H * (nq_pad / 32) * (nk_pad / 128);
+    const int64_t blocks = (n_items + 7) / 8;
+    if (blocks > 0x7fffffff) { set_error("problem too large for the dropout-bits grid"); return FA_EUNSUPPORTED; }
+    if (blocks == 0 || (!mq && !mk)) return FA_OK;
+    dropout_bits_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)p.stream>>>(
+        philox_make_key(p.seed, p.offset), dropout_threshold(p.dropout_p), dropout_origin_of(p), p.H, p.Nq, nq_pad,
+        nk_pad, p.causal, p.causal ? p.causal_shift : 0, n_items, (uint4*)mq, (uint32_t*)mk);
+    FA_CUDA_CHECK(cudaGetLastError());
+    return FA_OK;
 }
 
 int launch_dropout_mask(uint64_t seed, uint64_t offset, float p, int B, int H, int Nq, int Nk,

@@ -14,7 +14,7 @@ import threading
 _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG_DIR, "lib", "libfa_b200.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 FA_B200_F16, FA_B200_BF16, FA_B200_F32 = 0, 1, 2
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_TCGEN05, VARIANT_TCGEN05_2PASS = 0, 1, 2, 3
 VARIANT_NAMES = {VARIANT_AUTO: "auto", VARIANT_SIMT: "simt", VARIANT_TCGEN05: "tcgen05",
@@ -26,7 +26,7 @@ EXPORTS = (
     "fa_b200_fwd", "fa_b200_bwd", "fa_b200_bwd_static", "fa_b200_bwd_workspace_bytes", "fa_b200_tile_config",
     "fa_b200_dropout_mask_host", "fa_b200_dropout_mask_device", "fa_b200_dropout_effective_p",
     "fa_b200_philox4x32_10", "fa_b200_strerror", "fa_b200_last_error", "fa_b200_version", "fa_b200_combine",
-    "fa_b200_copy_rows", "fa_b200_selftest_wait_timeout",
+    "fa_b200_copy_rows", "fa_b200_selftest_wait_timeout", "fa_b200_dropout_bits_bytes",
 )
 
 
@@ -55,6 +55,8 @@ class Params(ctypes.Structure):
         ("rng_batch_offset", ctypes.c_int32), ("rng_head_offset", ctypes.c_int32), ("rng_heads", ctypes.c_int32),
         ("wait_limit_ms", ctypes.c_int32),
         ("o_lo", Tensor4),
+        ("dropout_bits", ctypes.c_void_p), ("dropout_bits_bytes", ctypes.c_size_t),
+        ("dropout_bits_ready", ctypes.c_int32),
     ]
 
 
@@ -111,6 +113,8 @@ def load():
         lib.fa_b200_bwd_static.restype = ctypes.c_int
         lib.fa_b200_bwd_workspace_bytes.argtypes = [pp]
         lib.fa_b200_bwd_workspace_bytes.restype = ctypes.c_size_t
+        lib.fa_b200_dropout_bits_bytes.argtypes = [pp]
+        lib.fa_b200_dropout_bits_bytes.restype = ctypes.c_size_t
         lib.fa_b200_combine.argtypes = [ctypes.POINTER(CombineParams)]
         lib.fa_b200_combine.restype = ctypes.c_int
         lib.fa_b200_copy_rows.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t,

@@ -170,13 +170,37 @@ def saves_output_residual(dtype: torch.dtype) -> bool:
     return dtype == torch.bfloat16
 
 
+def _dropout_bits_operand(p, keep_bits, forward_only=False):
+    """Point the call at a buffer for its dropout keep bits.  `keep_bits`: None (the kernels draw their
+    bits themselves), "new" (allocate; returned for a later call to reuse), or (tensor, ready) with a
+    uint8 tensor from an earlier call and whether that call has filled it."""
+    if keep_bits is None:
+        return None
+    nbytes = int(_cabi.load().fa_b200_dropout_bits_bytes(ctypes.byref(p)))
+    if nbytes == 0:
+        return None                      # no dropout, or the CUDA-core kernels serve the call
+    if isinstance(keep_bits, str):
+        # a forward that no backward follows needs the query-major half only
+        buf, ready = torch.empty(nbytes // 2 if forward_only else nbytes, dtype=torch.uint8, device="cuda:%d" % p.device), False
+    else:
+        buf, ready = keep_bits
+        if buf.numel() < (nbytes // 2 if forward_only else nbytes):
+            raise ValueError(f"keep-bit buffer holds {buf.numel()} bytes, the call needs {nbytes}")
+    p.dropout_bits, p.dropout_bits_bytes, p.dropout_bits_ready = buf.data_ptr(), buf.numel(), int(bool(ready))
+    return buf
+
+
 def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None, bias=None,
-                   key_lengths=None, causal_shift=0, dropout_origin=None, o_residual=None):
+                   key_lengths=None, causal_shift=0, dropout_origin=None, o_residual=None, keep_bits=None,
+                   forward_only=True):
     """o, lse <- fa_b200_fwd.  Counterpart of flash_attention_forward_triton_enhanced
     (kernels/forward_kernel.py:246-387); returns (o, lse).  `out=(o, lse)` writes into
     caller-owned buffers (o like q, lse (B, H, Nq) fp32 contiguous) instead of allocating.
     `o_residual` (a tensor like o) receives what rounding the output to its dtype dropped; handed
-    to launch_backward it removes that rounding from the gradients."""
+    to launch_backward it removes that rounding from the gradients.  `keep_bits="new"` (or a
+    (uint8 tensor, ready) pair) has the call's dropout bits written to a buffer once instead of drawn
+    inside the kernel; the call then returns (o, lse, buffer), and launch_backward given
+    keep_bits=(buffer, True) reads the same bits (`forward_only=False` sizes the buffer for that)."""
     if out is not None:
         o, lse = out
     else:
@@ -188,19 +212,23 @@ def launch_forward(q, k, v, scale, causal, dropout_p=0.0, seed=0, offset=0, out=
     if o_residual is not None:
         _check_residual(o_residual, o)
         p.o_lo = _tensor4(o_residual)
+    bits = _dropout_bits_operand(p, keep_bits, forward_only)
     rc = _cabi.load().fa_b200_fwd(ctypes.byref(p))
     _cabi.raise_for_status(rc, "fa_b200_fwd")
+    if keep_bits is not None:
+        return o, lse, bits
     return o, lse
 
 
 def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, offset=0, out=None,
                     workspace=None, bias=None, d_scores=None, key_lengths=None, causal_shift=0,
-                    dropout_origin=None, o_residual=None, fast=False):
+                    dropout_origin=None, o_residual=None, fast=False, keep_bits=None):
     """dq, dk, dv <- fa_b200_bwd.  Counterpart of
     flash_attention_backward_triton_enhanced (kernels/backward_kernel.py:208-318).
     `out=(dq, dk, dv)` and `workspace` (uint8, at least fa_b200_bwd_workspace_bytes)
     use caller-owned buffers instead of allocating.  `fast`: allow the one-kernel backward where it
-    is faster (D = 64); dQ is then summed in no fixed order and is not bit-reproducible."""
+    is faster (D = 64); dQ is then summed in no fixed order and is not bit-reproducible.
+    `keep_bits`: as in launch_forward; (buffer, True) reuses the bits the forward wrote."""
     d_o = _last_dim_contiguous(d_o)
     if out is not None:
         dq, dk, dv = out
@@ -231,6 +259,7 @@ def launch_backward(d_o, q, k, v, o, lse, scale, causal, dropout_p=0.0, seed=0, 
         if ws.numel() < nbytes:
             raise ValueError(f"workspace holds {ws.numel()} bytes, the call needs {nbytes}")
     p.workspace, p.workspace_bytes = ws.data_ptr(), nbytes
+    _bits = _dropout_bits_operand(p, keep_bits)
     rc = lib.fa_b200_bwd(ctypes.byref(p))
     _cabi.raise_for_status(rc, "fa_b200_bwd")
     return dq, dk, dv
@@ -309,8 +338,12 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
         # the backward of a bf16 call also gets what rounding the output to bf16 dropped
         needs_grad = any(t.requires_grad for t in (q, k, v)) or (bias is not None and bias.requires_grad)
         o_lo = torch.empty_like(q) if (needs_grad and saves_output_residual(q.dtype)) else None
-        o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias, key_lengths=key_lengths,
-                                causal_shift=causal_shift, dropout_origin=dropout_origin, o_residual=o_lo)
+        # with dropout the call's keep bits are written to a buffer once; the backward reads the same bits
+        res = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias, key_lengths=key_lengths,
+                             causal_shift=causal_shift, dropout_origin=dropout_origin, o_residual=o_lo,
+                             keep_bits="new" if dropout_p > 0.0 else None, forward_only=not needs_grad)
+        o, lse = res[0], res[1]
+        ctx.keep_bits = res[2] if (len(res) > 2 and needs_grad) else None
         ctx.dropout_origin = dropout_origin
         ctx.has_bias, ctx.has_residual = bias is not None, o_lo is not None
         # performance_mode "speed" (the public entry's optimization_strategy) opts into the fastest
@@ -342,7 +375,8 @@ class EnhancedFlashAttentionV100Function(torch.autograd.Function):
         dq, dk, dv = launch_backward(grad_output, q, k, v, o, lse, ctx.scale, ctx.causal,
                                      ctx.dropout_p, ctx.seed, ctx.offset, bias=bias, d_scores=d_scores,
                                      key_lengths=ctx.key_lengths, causal_shift=ctx.causal_shift,
-                                     dropout_origin=ctx.dropout_origin, o_residual=o_lo, fast=ctx.fast and bias is None)
+                                     dropout_origin=ctx.dropout_origin, o_residual=o_lo, fast=ctx.fast and bias is None,
+                                     keep_bits=(ctx.keep_bits, True) if ctx.keep_bits is not None else None)
         if d_scores is not None:
             dims = [i for i in range(4) if bias.shape[i] == 1 and d_scores.shape[i] != 1]
             grad_bias = (d_scores.sum(dim=dims, keepdim=True) if dims else d_scores).to(bias.dtype)
@@ -364,7 +398,8 @@ def flash_attention_forward_enhanced(q, k, v, scale: Optional[float] = None, cau
     with torch.no_grad():
         o, lse = launch_forward(q, k, v, scale, causal, dropout_p, seed, offset, bias=bias,
                                 key_lengths=kwargs.get("key_lengths"), dropout_origin=kwargs.get("dropout_origin"),
-                                o_residual=kwargs.get("output_residual"))
+                                o_residual=kwargs.get("output_residual"),
+                                keep_bits="new" if dropout_p > 0.0 else None)[:2]
     return (o, lse) if kwargs.get("return_softmax_lse", False) else o
 
 

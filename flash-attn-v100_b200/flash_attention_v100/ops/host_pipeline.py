@@ -122,6 +122,13 @@ class HostAttentionStep:
             self._lse = [torch.empty(b1 - b0, h1 - h0, Nq, dtype=torch.float32, device=dev)
                          for b0, b1, h0, h1 in self.chunks]
             self._ws = [self._workspace(b1 - b0, h1 - h0) for b0, b1, h0, h1 in self.chunks]
+            # dropout: one buffer for the keep bits of the chunk in flight (the kernels of all chunks run
+            # on one stream): the chunk's forward fills it, its backward reads it
+            self._bits = None
+            if self.dropout_p > 0.0:
+                cols = max(((b1 - b0) * (h1 - h0) for b0, b1, h0, h1 in self.chunks), default=0)
+                pad = lambda n: -(-n // 128) * 128
+                self._bits = torch.empty(max(1, cols * pad(Nq) * pad(Nk) // 4), dtype=torch.uint8, device=dev)
             self._s_in, self._s_run, self._s_out = (torch.cuda.Stream(dev) for _ in range(3))
             n = len(self.chunks)
             ev = lambda: [torch.cuda.Event() for _ in range(n)]
@@ -207,15 +214,17 @@ class HostAttentionStep:
                 origin = (b, h0, self.q_shape[2])               # this chunk's place in the whole problem
                 lse_c = self._lse[c]
                 res = self._o_lo[qs] if self._o_lo is not None else None
+                bits = (self._bits, False) if self._bits is not None else None
                 _ops.launch_forward(d["q"][qs], d["k"][ks], d["v"][ks], self.scale, self.causal,
                                     self.dropout_p, sd, off, out=(d["o"][qs], lse_c), dropout_origin=origin,
-                                    o_residual=res)
+                                    o_residual=res, keep_bits=bits, forward_only=False)
                 self._ev_fwd[c].record(self._s_run)
                 self._s_run.wait_event(self._ev_do[c])
                 _ops.launch_backward(d["d_o"][qs], d["q"][qs], d["k"][ks], d["v"][ks], d["o"][qs],
                                      lse_c, self.scale, self.causal, self.dropout_p, sd, off,
                                      out=(d["dq"][qs], d["dk"][ks], d["dv"][ks]), workspace=self._ws[c],
-                                     dropout_origin=origin, o_residual=res)
+                                     dropout_origin=origin, o_residual=res,
+                                     keep_bits=(self._bits, True) if self._bits is not None else None)
                 self._ev_bwd[c].record(self._s_run)
             with torch.cuda.stream(self._s_out):
                 self._s_out.wait_event(self._ev_fwd[c])

@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define FA_B200_ABI_VERSION 2
+#define FA_B200_ABI_VERSION 3
 
 typedef enum fa_b200_dtype {
     FA_B200_F16  = 0,
@@ -155,6 +155,19 @@ typedef struct fa_b200_params {
        the saved output (2^-9) is the largest error in dQ and dK; with the residual it is gone.  The
        reference saves its output in the tensors' dtype only (ops/attention.py:209-214). */
     fa_b200_tensor o_lo;
+    /* Optional buffer for the call's dropout keep bits (NULL: the kernels draw their bits themselves,
+       which costs the tensor-core kernels' softmax threads about as many instructions as the attention
+       math).  With a buffer of fa_b200_dropout_bits_bytes(&p) bytes (16-byte aligned) a separate kernel
+       writes every keep bit of the call once, packed in the two orientations the kernels read (by query
+       row for the forward and dQ, by key row for dK/dV), and the tensor-core kernels load them.
+       dropout_bits_ready = 0: this call fills the buffer first; 1: the buffer holds the bits an earlier
+       call with the same (seed, offset, dropout_p, sizes, causal mask, rng_* origin) wrote, e.g. the
+       forward's, and is only read.  Half the size serves a forward alone (no backward follows).  The
+       mask is the one fa_b200_dropout_mask_host describes either way.  Ignored without dropout and by
+       the CUDA-core kernels. */
+    void*          dropout_bits;
+    size_t         dropout_bits_bytes;
+    int32_t        dropout_bits_ready;
 } fa_b200_params;
 
 /* Static tile choice for a (D, dtype, causal) key; replaces the reference's
@@ -270,6 +283,11 @@ int fa_b200_copy_rows(void* dst, size_t dst_pitch, const void* src, size_t src_p
  * accumulator, ...).  Counterpart of the 'delta' entry of
  * ops/memory.py:653-760 allocate_attention_workspace_enhanced. */
 size_t fa_b200_bwd_workspace_bytes(const fa_b200_params* p);
+
+/* Bytes of fa_b200_params.dropout_bits for this problem (both orientations: B*H * ceil128(Nq) *
+ * ceil128(Nk) / 4), or 0 when the call has no dropout or would not be served by the tensor-core
+ * kernels.  Pointers in *p may be null.  No counterpart in the reference, which keeps no mask. */
+size_t fa_b200_dropout_bits_bytes(const fa_b200_params* p);
 
 /* Tile table lookup; counterpart of config.py:288-348 get_enhanced_config. */
 int fa_b200_tile_config(int D, int dtype, int causal, int backward, fa_b200_tile* out);

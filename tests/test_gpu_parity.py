@@ -221,6 +221,62 @@ def test_dropout_mask_replayed_by_forward_and_backward(device, dtype, D):
             assert np.array_equal(kept_bwd, keep), variant
 
 
+@pytest.mark.parametrize("dtype,D,B,Nq,Nk,H,Hkv,causal,shift,origin", [
+    (torch.bfloat16, 64, 2, 256, 256, 4, 4, True, 0, None),
+    (torch.float16, 64, 1, 200, 333, 4, 2, False, 0, None),          # ragged sizes, grouped K/V heads
+    (torch.bfloat16, 128, 2, 130, 260, 2, 2, True, 130, (3, 5, 16)), # bottom-right mask, a shard's origin
+    (torch.float16, 128, 1, 384, 384, 3, 1, True, 0, None),
+])
+def test_keep_bit_buffer_gives_the_results_of_the_inline_draw(device, dtype, D, B, Nq, Nk, H, Hkv, causal, shift, origin):
+    """Keep bits written once to a buffer and loaded by the kernels = the bits the kernels draw
+    themselves: outputs and gradients agree bit for bit, whether the backward reuses the forward's
+    buffer or fills its own."""
+    p, seed, offset = 0.3, 991, 4
+    q = _rand((B, Nq, H, D), dtype, 1).to(device)
+    k = _rand((B, Nk, Hkv, D), dtype, 2).to(device)
+    v = _rand((B, Nk, Hkv, D), dtype, 3).to(device)
+    g = _rand((B, Nq, H, D), dtype, 4).to(device)
+    kw = dict(causal_shift=shift, dropout_origin=origin)
+    for variant in ("tcgen05_2pass", "tcgen05"):
+        with kernel_variant(variant):
+            fast = variant == "tcgen05"
+            o0, lse0 = launch_forward(q, k, v, D ** -0.5, causal, p, seed, offset, **kw)
+            d0 = launch_backward(g, q, k, v, o0, lse0, D ** -0.5, causal, p, seed, offset, fast=fast, **kw)
+            o1, lse1, bits = launch_forward(q, k, v, D ** -0.5, causal, p, seed, offset, keep_bits="new",
+                                            forward_only=False, **kw)
+            assert bits is not None and bits.numel() == B * H * (-(-Nq // 128) * 128) * (-(-Nk // 128) * 128) // 4
+            assert torch.equal(o0, o1) and torch.equal(lse0, lse1), variant
+            d1 = launch_backward(g, q, k, v, o0, lse0, D ** -0.5, causal, p, seed, offset, fast=fast,
+                                 keep_bits=(bits, True), **kw)
+            d2 = launch_backward(g, q, k, v, o0, lse0, D ** -0.5, causal, p, seed, offset, fast=fast,
+                                 keep_bits="new", **kw)
+            # a forward alone takes half the buffer
+            o3, _, half = launch_forward(q, k, v, D ** -0.5, causal, p, seed, offset, keep_bits="new", **kw)
+            assert half.numel() * 2 == bits.numel() and torch.equal(o0, o3)
+            exact = dq_is_bit_reproducible(variant, dtype, D, p)
+            for a, b, c, name in zip(d0, d1, d2, ("dq", "dk", "dv")):
+                if name == "dq" and not exact:
+                    assert_same_dq(a, b, False)
+                    assert_same_dq(a, c, False)
+                else:
+                    assert torch.equal(a, b), (variant, name, "forward's bits")
+                    assert torch.equal(a, c), (variant, name, "own bits")
+
+
+def test_keep_bit_buffer_is_not_asked_for_where_it_is_not_read(device):
+    lib = _cabi.load()
+    from flash_attention_v100.ops.attention import _base_params
+    import ctypes
+    q = _rand((1, 128, 2, 64), torch.float16, 1).to(device)
+    o = torch.empty_like(q)
+    lse = torch.empty(1, 2, 128, dtype=torch.float32, device=device)
+    sized = lambda t, p, **kw: int(lib.fa_b200_dropout_bits_bytes(ctypes.byref(_base_params(t, t, t, o.to(t.dtype), lse, 0.125, False, p, 1, 2, 0, None, **kw))))
+    assert sized(q, 0.0) == 0                                          # no dropout
+    assert sized(q, 0.5) == 2 * 128 * 128 // 4
+    assert sized(q, 0.5, variant=_cabi.VARIANT_SIMT) == 0              # CUDA-core kernels draw their own
+    assert sized(q.float(), 0.5) == 0                                  # fp32 with dropout: CUDA-core kernels
+
+
 def test_strided_head_and_batch_views_are_consumed_in_place(device):
     B, N, H, D = 3, 160, 6, 64
     dtype = torch.bfloat16
