@@ -736,13 +736,23 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             // 32 x 32 block (rows lane/4 + {0, 8, 16, 24}, columns 8j + 2(lane%4) + {0, 1}, j = 0..3) instead
             // of 1 row x 32 columns, so it needs the -lse / -delta values of 8 query columns, four 8-byte
             // loads that one wavefront serves, instead of 32 values through eight broadcast 16-byte loads.
+            const int lq = lane & 3, lr = lane >> 2;
+            const int rbase = (warp & 3) * 32 + lr;                 // my first row inside the tile
+            // DROP = 2: one word of keep bits per key row of mine, asked for before the wait for S^T
+            uint32_t kwr[2][2] = {{0u, 0u}, {0u, 0u}};
+            if constexpr (DROP == 2) {
+                const uint32_t* w = a.bits_k + (((int64_t)(b * a.H + head_q) * (a.nq_pad / kTile) + strm_tile) * 4 +
+                                                cb / 32) * (int64_t)a.nk_pad + tile * kTile + rbase;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) kwr[h][k] = w[16 * h + 8 * k];
+            }
             ok = mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag);
             if (ok) ok = mbar_wait(&bars[Cfg::kVFull + (it & 1)], (uint32_t)(it >> 1) & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            const int lq = lane & 3, lr = lane >> 2;
-            const int rbase = (warp & 3) * 32 + lr;                 // my first row inside the tile
             const uint32_t t_lo = lane_off + cb, t_hi = lane_off + (16u << 16) + cb;
             // element (h, j, k, e): row rbase + 16h + 8k, column 8j + 2lq + e, register [h][4j + 2k + e]
             uint32_t pf[2][16];
@@ -751,19 +761,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tmem_wait_ld();
             uint32_t kbits = 0xFFFFFFFFu;                           // keep bit of element (h, j, k, e): bit 16h + 4j + 2k + e
             if constexpr (DROP == 2) {
-                // one word per key row of mine: bit q = query 32 (cb / 32) + q of this tile
-                const uint32_t* w = a.bits_k + (((int64_t)(b * a.H + head_q) * (a.nq_pad / kTile) + strm_tile) * 4 +
-                                                cb / 32) * (int64_t)a.nk_pad + tile * kTile + rbase;
-                kbits = 0u;
+                // shifted so that bit 8j + e is my column 8j + 2lq + e
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
 #pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        const uint32_t word = w[16 * h + 8 * k] >> ((cb & 31) + 2 * lq);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            kbits |= ((word >> (8 * j)) & 3u) << (16 * h + 4 * j + 2 * k);
-                    }
+                    for (int k = 0; k < 2; ++k) kwr[h][k] >>= ((cb & 31) + 2 * lq);
             } else if (drop) {
                 const uint16_t* mbuf = sMask + (it & 1) * (128 * 8);
                 kbits = 0u;
@@ -829,7 +831,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             const int i0 = 4 * (2 * hf + jj) + 2 * k;
                             float z0 = __uint_as_float(pf[h][i0]), z1 = __uint_as_float(pf[h][i0 + 1]);
                             if (drop) {
-                                const uint32_t kw = kbits >> (16 * h + i0);
+                                const uint32_t kw = DROP == 2 ? kwr[h][k] >> (8 * (i0 >> 2)) : kbits >> (16 * h + i0);
                                 if (!(kw & 1u)) z0 = 0.f;
                                 if (!(kw & 2u)) z1 = 0.f;
                             }
@@ -871,7 +873,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                                 const uint64_t dp = f2_pack(__uint_as_float(df[h][i0]), __uint_as_float(df[h][i0 + 1]));
                                 uint64_t tt;
                                 if (drop) {
-                                    const uint32_t kw = kbits >> (16 * h + i0);
+                                    const uint32_t kw = DROP == 2 ? kwr[h][k] >> (8 * j) : kbits >> (16 * h + i0);
                                     tt = f2_fma(dp, f2_pack((kw & 1u) ? zk : 0.f, (kw & 2u) ? zk : 0.f), nd);
                                 } else {
                                     tt = f2_fma(dp, ttm2, nd);
