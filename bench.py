@@ -466,6 +466,7 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="override the workload's batch (small profiling cases)")
     ap.add_argument("--heads", type=int, default=None, help="override the workload's head count")
     ap.add_argument("--dtype", choices=("fp16", "bf16"), default=None, help="override the workload's dtype (A/B runs)")
+    ap.add_argument("--dropout-p", type=float, default=None, help="override the workload's dropout rate (A/B runs)")
     args = ap.parse_args()
     from flash_attention_v100.testing import WORKLOADS
     w = WORKLOADS[args.workload]
@@ -476,6 +477,9 @@ def main():
         dt = {"fp16": torch.float16, "bf16": torch.bfloat16}[args.dtype]
         if dt != w.dtype:
             w = w.shrink(dtype=dt, name=f"{w.name} [dtype overridden to {args.dtype}: not the benchmark dtype]")
+    if args.dropout_p is not None and args.dropout_p != w.dropout_p:
+        w = w.shrink(dropout_p=args.dropout_p,
+                     name=f"{w.name} [dropout overridden to {args.dropout_p}: not the benchmark's rate]")
     if args.impl == "reference":
         run_reference(args, w)
     else:

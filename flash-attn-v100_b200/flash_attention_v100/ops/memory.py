@@ -34,6 +34,15 @@ def backward_workspace_bytes(batch_size: int, seq_len_q: int, seq_len_k: int, nu
     return int(_cabi.load().fa_b200_bwd_workspace_bytes(ctypes.byref(p)))
 
 
+def dropout_bits_bytes(batch_size: int, seq_len_q: int, seq_len_k: int, num_heads: int, head_dim: int,
+                       dtype: torch.dtype, dropout_p: float, num_heads_kv: int = None) -> int:
+    """Bytes of the buffer that holds a call's dropout keep bits (two bits of storage per score: one per
+    orientation), or 0 where the kernels draw their bits themselves (no dropout, CUDA-core kernels)."""
+    p = _sizes_params(batch_size, seq_len_q, seq_len_k, num_heads, head_dim, dtype, num_heads_kv)
+    p.dropout_p = float(dropout_p)
+    return int(_cabi.load().fa_b200_dropout_bits_bytes(ctypes.byref(p)))
+
+
 def allocate_attention_workspace(batch_size: int, seq_len_q: int, seq_len_k: int, num_heads: int,
                                  head_dim: int, dtype: torch.dtype, device: torch.device,
                                  include_backward: bool = True, enable_multi_gpu: bool = False,
@@ -61,10 +70,11 @@ def free_attention_workspace(workspace: Dict[str, torch.Tensor], defer_cleanup: 
 
 def estimate_peak_memory_usage(batch_size: int, seq_len_q: int, seq_len_k: int, num_heads: int,
                                head_dim: int, dtype: torch.dtype, include_gradients: bool = True,
-                               **_ignored) -> Dict[str, float]:
+                               dropout_p: float = 0.0, **_ignored) -> Dict[str, float]:
     """Bytes the op holds at its peak, in the reference's result keys
     (ops/memory.py:786-896: *_mb entries and total_memory_mb).  O(N) in the
-    sequence length: no (N x N) score tensor is ever materialised."""
+    sequence length: no (N x N) score tensor is ever materialised; with dropout on
+    the tensor-core kernels the call's keep bits are (Nq x Nk / 4 bytes per head)."""
     es = torch.empty((), dtype=dtype).element_size()
     t_q = batch_size * seq_len_q * num_heads * head_dim * es
     t_k = batch_size * seq_len_k * num_heads * head_dim * es
@@ -74,9 +84,14 @@ def estimate_peak_memory_usage(batch_size: int, seq_len_q: int, seq_len_k: int, 
     if include_gradients:
         bwd = t_q * 2 + t_k * 2                        # dO, dQ, dK, dV
         bwd += backward_workspace_bytes(batch_size, seq_len_q, seq_len_k, num_heads, head_dim, dtype)
+    bits = dropout_bits_bytes(batch_size, seq_len_q, seq_len_k, num_heads, head_dim, dtype, dropout_p) \
+        if dropout_p > 0.0 else 0
+    if not include_gradients:
+        bits //= 2                                     # a forward alone keeps one orientation
     mb = 1.0 / (1024 ** 2)
     return {"input_memory_mb": (t_q + 2 * t_k) * mb, "output_memory_mb": (t_q + lse) * mb,
-            "gradient_memory_mb": bwd * mb, "total_memory_mb": (fwd + bwd) * mb}
+            "gradient_memory_mb": bwd * mb, "dropout_bits_memory_mb": bits * mb,
+            "total_memory_mb": (fwd + bwd + bits) * mb}
 
 
 def get_memory_statistics(device=None) -> Dict[str, float]:

@@ -105,6 +105,14 @@ def test_workspace_estimates():
     est = memory.estimate_peak_memory_usage(4, 4096, 4096, 32, 128, torch.bfloat16)
     assert est["total_memory_mb"] > 8 * 128          # eight 134 MB tensors at least
     assert est["total_memory_mb"] < 4 * 32 * 4096 * 4096 * 2 / 2 ** 20   # far below the N^2 scores
+    # dropout on the tensor-core kernels: the call's keep bits, two bits of storage per score
+    bits = memory.dropout_bits_bytes(32, 2048, 2048, 16, 64, torch.bfloat16, 0.1)
+    assert bits == 32 * 16 * 2048 * 2048 // 4
+    assert memory.dropout_bits_bytes(32, 2048, 2048, 16, 64, torch.bfloat16, 0.0) == 0
+    assert memory.dropout_bits_bytes(2, 200, 333, 4, 64, torch.float16, 0.5, num_heads_kv=2) == 2 * 4 * 256 * 384 // 4
+    assert memory.dropout_bits_bytes(2, 256, 256, 4, 64, torch.float32, 0.5) == 0      # CUDA-core kernels
+    with_p = memory.estimate_peak_memory_usage(32, 2048, 2048, 16, 64, torch.bfloat16, dropout_p=0.1)
+    assert abs(with_p["dropout_bits_memory_mb"] - bits / 2 ** 20) < 1e-6
 
 
 def test_tile_table_reports_the_constants_the_kernels_are_compiled_from():
