@@ -1030,11 +1030,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         uint64_t dpb = f2_pack(__uint_as_float(dr[c >> 5][(c + 2) & 31]), __uint_as_float(dr[c >> 5][(c + 3) & 31]));
                         uint64_t ta, tb;
                         if (drop) {
+                            // dropped entries: dS = P o (-delta), selected after the FMA
                             const uint32_t kw = kb[c >> 5] >> (c & 31);
-                            const uint64_t za = f2_pack((kw & 1u) ? zk : 0.f, (kw & 2u) ? zk : 0.f);
-                            const uint64_t zb = f2_pack((kw & 4u) ? zk : 0.f, (kw & 8u) ? zk : 0.f);
-                            ta = f2_fma(dpa, za, nd.x);
-                            tb = f2_fma(dpb, zb, nd.y);
+                            const uint64_t zk2 = f2_pack(zk, zk);
+                            float t0, t1, t2, t3, n0, n1, n2, n3;
+                            f2_unpack(f2_fma(dpa, zk2, nd.x), t0, t1);
+                            f2_unpack(f2_fma(dpb, zk2, nd.y), t2, t3);
+                            f2_unpack(nd.x, n0, n1);
+                            f2_unpack(nd.y, n2, n3);
+                            ta = f2_pack((kw & 1u) ? t0 : n0, (kw & 2u) ? t1 : n1);
+                            tb = f2_pack((kw & 4u) ? t2 : n2, (kw & 8u) ? t3 : n3);
                         } else {
                             ta = f2_fma(dpa, ttm2, nd.x);
                             tb = f2_fma(dpb, ttm2, nd.y);

@@ -124,13 +124,24 @@ FA_HD uint32_t dropout_keep_bits(const PhiloxKey& key, uint32_t bh, uint32_t i, 
     dropout_block(key, bh, i, jblk, w);
     uint32_t bits = 0;
 #if defined(__CUDA_ARCH__)
-    // four byte compares per instruction, then gather the four 0/1 results into a nibble
-    const uint32_t thr4 = threshold * 0x01010101u;
+    // byte >= threshold <=> byte + (256 - threshold) carries out of its eight bits.  The even and the odd
+    // bytes of a word go to the two 16-bit lanes of a register each; the add (scaled by 64 or 128, so
+    // that the four carries of a word end up at bits 14, 15, 30, 31) cannot cross a lane: (255 + 255) * 128
+    // < 2^16.  One high-half multiply per word then moves its four flags to bits 4q .. 4q + 3 (the two
+    // partial products that matter land at 32 + 4q and 34 + 4q, the other two below bit 32 and above bit
+    // 47).  17 logic operations and 12 multiply-adds for the 16 bytes; 8 % off the kernel that writes a
+    // call's bits against four emulated per-byte compares.
+    const uint32_t nt = 256u - threshold;                    // threshold is 1 .. 255 here
+    const uint32_t k6 = nt * 0x00400040u, k7 = nt * 0x00800080u;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-        const uint32_t ge = __vcmpgeu4(w[q], thr4) & 0x01010101u;
-        bits |= (((ge * 0x01020408u) >> 24) & 0xFu) << (4 * q);
+        const uint32_t even = w[q] & 0x00FF00FFu;
+        const uint32_t odd = __byte_perm(w[q], 0u, 0x4341);  // bytes 1 and 3, each in the low byte of a lane
+        const uint32_t se = even * 64u + k6, so = odd * 128u + k7;
+        const uint32_t flags = (se & 0x40004000u) | (so & 0x80008000u);
+        bits += __umulhi(flags, (1u << (18 + 4 * q)) + (1u << (4 + 4 * q)));
     }
+    bits &= 0xFFFFu;
 #else
     for (int q = 0; q < 4; ++q) {
         for (int b = 0; b < 4; ++b) {

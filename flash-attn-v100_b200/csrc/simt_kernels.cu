@@ -480,19 +480,36 @@ __device__ __forceinline__ uint32_t transpose_bits_32x32(uint32_t x, int lane) {
 //   mq[(col * NJ + j128) * nq_pad + i]            uint4: bit c of the 128 = key j128*128 + c   (query-major)
 //   mk[((col * NI + i128) * 4 + g) * nk_pad + k]  uint32: bit q = query i128*128 + 32 g + q     (key-major:
 //       the 32 x 32 transposes of the warp's four words)
-// Tiles the causal mask hides completely are skipped (nobody reads their bits: P is zero there).
-__global__ void __launch_bounds__(256)
+// Tiles the causal mask hides completely hold no bits (nobody reads them: P is zero there).  Under the
+// usual mask (square, key j visible to query i iff j <= i) the 32-query blocks are dealt in pairs, block p
+// with block NIB-1-p: together they have NJ + 1 live key blocks whatever p, so every warp of the grid has
+// work (a grid over all (block, key block) items, half of them hidden, measured 0.36 against 0.33 ms on
+// B32 H16 N2048; a fixed grid that strides over the items 0.56 ms).  Other shapes walk all items and skip.
+__global__ void __launch_bounds__(256, 8)
 dropout_bits_kernel(PhiloxKey key, uint32_t thr, DropoutOrigin rng, int H, int Nq, int nq_pad, int nk_pad,
-                    int causal, int shift, int64_t n_items, uint4* __restrict__ mq, uint32_t* __restrict__ mk) {
+                    int causal, int shift, int paired, int64_t n_items, uint4* __restrict__ mq,
+                    uint32_t* __restrict__ mk) {
     const int lane = threadIdx.x & 31;
     const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (item >= n_items) return;                                     // whole warps leave together
     const int NJ = nk_pad / 128, NIB = nq_pad / 32;
-    const int j128 = (int)(item % NJ);
-    const int64_t rest = item / NJ;
-    const int ib = (int)(rest % NIB);
-    const int64_t col = rest / NIB;                                   // local b * H + h
-    if (causal && (int64_t)j128 * 128 > (int64_t)ib * 32 + 31 + shift) return;
+    int j128, ib;
+    int64_t col;                                                      // local b * H + h
+    if (paired) {
+        const int s = (int)(item % (NJ + 1));
+        const int64_t rest = item / (NJ + 1);
+        const int pr = (int)(rest % (NIB / 2));
+        col = rest / (NIB / 2);
+        const int live_lo = pr / 4 + 1;                               // live key blocks of the pair's first block
+        ib = s < live_lo ? pr : NIB - 1 - pr;
+        j128 = s < live_lo ? s : s - live_lo;
+    } else {
+        j128 = (int)(item % NJ);
+        const int64_t rest = item / NJ;
+        ib = (int)(rest % NIB);
+        col = rest / NIB;
+        if (causal && (int64_t)j128 * 128 > (int64_t)ib * 32 + 31 + shift) return;
+    }
     const int i = ib * 32 + lane;
     const uint32_t column = dropout_column(rng, (int)(col / H), (int)(col % H));
     uint32_t w4[4] = {0u, 0u, 0u, 0u};
@@ -598,13 +615,17 @@ size_t dropout_bits_bytes(const fa_b200_params& p) {
 
 int launch_dropout_bits(const fa_b200_params& p, void* mq, void* mk) {
     const int nq_pad = (int)align_up((size_t)p.Nq, 128), nk_pad = (int)align_up((size_t)p.Nk, 128);
-    const int64_t n_items = (int64_t)p.B * p.H * (nq_pad / 32) * (nk_pad / 128);
+    const int shift = p.causal ? p.causal_shift : 0;
+    // the usual causal mask on a square problem: pairs of query blocks, no hidden items (see the kernel)
+    const int paired = (p.causal && shift == 0 && nq_pad == nk_pad) ? 1 : 0;
+    const int64_t per_column = paired ? (int64_t)(nq_pad / 64) * (nk_pad / 128 + 1) : (int64_t)(nq_pad / 32) * (nk_pad / 128);
+    const int64_t n_items = (int64_t)p.B * p.H * per_column;
     const int64_t blocks = (n_items + 7) / 8;
     if (blocks > 0x7fffffff) { set_error("problem too large for the dropout-bits grid"); return FA_EUNSUPPORTED; }
     if (blocks == 0 || (!mq && !mk)) return FA_OK;
     dropout_bits_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)p.stream>>>(
         philox_make_key(p.seed, p.offset), dropout_threshold(p.dropout_p), dropout_origin_of(p), p.H, p.Nq, nq_pad,
-        nk_pad, p.causal, p.causal ? p.causal_shift : 0, n_items, (uint4*)mq, (uint32_t*)mk);
+        nk_pad, p.causal, shift, paired, n_items, (uint4*)mq, (uint32_t*)mk);
     FA_CUDA_CHECK(cudaGetLastError());
     return FA_OK;
 }
