@@ -12,7 +12,8 @@ reduction of the timings.  Rank 0 prints ONE JSON line.  `--replicas` instead
 gives every rank the whole workload (weak scaling).
 
 A step is one forward + backward pass of the workload (default: B4 N4096 H32
-D128 bf16 causal, the Llama-7B-like layer) through the public API.  `value` is
+D128 bf16 causal, the Llama-7B-like layer) through the public API; the timed
+steps replay a CUDA graph of one such step (`--no-graph`: eager).  `value` is
 device-resident throughput in TFLOP/s (4*B*H*N^2*D forward, 2.5x that backward,
 halved when causal); `e2e` repeats the measurement with the step's inputs
 copied from pinned host memory and its results copied back inside the timed
@@ -302,8 +303,26 @@ def run_ours(args, whole):
         for n, t in (("o", o.detach()), ("dq", qq.grad), ("dk", kk.grad), ("dv", vv.grad)):
             back[n].copy_(t, non_blocking=True)
 
+    # The device-resident step is replayed from a CUDA graph of one public-API step (forward + backward
+    # through autograd): at 8 GPUs a rank's step is 0.33 ms of kernels, and eight Python processes on one
+    # host's cores cannot issue the launches and allocations of an eager step that fast (0.386 ms eager).
+    eager_step, launch = step, "eager"
     for _ in range(max(3, args.warmup)):
         step()
+    if not args.no_graph:
+        torch.cuda.synchronize(device)
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            eager_step()
+        torch.cuda.current_stream(device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            eager_step()
+        step, launch = graph.replay, "CUDA graph of one step through the public API, replayed"
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize(device)
     with ClockSampler(local) as clocks:
         ms_step = time_steps(step, args.steps, device, world)
         # nvidia-smi takes ~100 ms to start and then samples every 50 ms: keep the same load on the GPU
@@ -421,7 +440,7 @@ def run_ours(args, whole):
             "config": {
                 "workload": whole.name, "B": whole.B, "N": whole.N, "H": whole.H, "D": whole.D,
                 "causal": whole.causal, "dropout_p": whole.dropout_p, "optimization_strategy": args.strategy,
-                "split": split, "per_gpu": "B%d H%d of the workload, resident on the GPU" % (w.B, w.H),
+                "launch": launch, "split": split, "per_gpu": "B%d H%d of the workload, resident on the GPU" % (w.B, w.H),
                 "parallelism": f"(batch x heads) shards, {world} rank(s), no data-path collective",
                 "l2": ("not flushed: q, k, v, o, dO, dQ, dK, dV are %.0f MB each (working set %.0f MB), %s the 126 MB L2"
                        % (tb / 1e6, 8 * tb / 1e6, "larger than" if tb > 126 * 2 ** 20 else
@@ -466,6 +485,7 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="override the workload's batch (small profiling cases)")
     ap.add_argument("--heads", type=int, default=None, help="override the workload's head count")
     ap.add_argument("--dtype", choices=("fp16", "bf16"), default=None, help="override the workload's dtype (A/B runs)")
+    ap.add_argument("--no-graph", action="store_true", help="time eager steps instead of replaying a CUDA graph of one")
     ap.add_argument("--dropout-p", type=float, default=None, help="override the workload's dropout rate (A/B runs)")
     args = ap.parse_args()
     from flash_attention_v100.testing import WORKLOADS
