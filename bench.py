@@ -310,19 +310,24 @@ def run_ours(args, whole):
     for _ in range(max(3, args.warmup)):
         step()
     if not args.no_graph:
-        torch.cuda.synchronize(device)
-        side = torch.cuda.Stream(device)
-        side.wait_stream(torch.cuda.current_stream(device))
-        with torch.cuda.stream(side):
-            eager_step()
-        torch.cuda.current_stream(device).wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            eager_step()
-        step, launch = graph.replay, "CUDA graph of one step through the public API, replayed"
-        for _ in range(3):
-            step()
-        torch.cuda.synchronize(device)
+        try:
+            torch.cuda.synchronize(device)
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                eager_step()
+            torch.cuda.current_stream(device).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                eager_step()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize(device)
+            step, launch = graph.replay, "CUDA graph of one step through the public API, replayed"
+        except Exception as exc:                      # time eager steps and say so in the line
+            print(f"bench: graph capture failed ({exc!r}); timing eager steps", file=sys.stderr)
+            launch = f"eager (graph capture failed: {type(exc).__name__})"
+            torch.cuda.synchronize(device)
     with ClockSampler(local) as clocks:
         ms_step = time_steps(step, args.steps, device, world)
         # nvidia-smi takes ~100 ms to start and then samples every 50 ms: keep the same load on the GPU
