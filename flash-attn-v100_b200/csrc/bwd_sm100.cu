@@ -354,10 +354,20 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const BwdScales sc = make_scales(a.ranges + 2 * ((int64_t)b * a.Hkv + head_kv), D, a.inv_keep, a.scale,
                                      !(CONV && KS) ? kDoAsIs : (INLINE ? kDoInline : kDoRowCopy));
 
+    // Registers: without dropout the launch allocation of 96 per thread lets no role spill, and moving
+    // registers from the MMA / TMA warps to the elementwise ones (104 / 64, 104 / 40) made one side or the
+    // other spill and measured the same or slower.  The dK/dV kernel's dropout instances do spill in the
+    // elementwise loop at 96 (28 local loads and 24 stores per step and warp, 8 % of the kernel's
+    // instructions under ncu): they take 104 and leave 64 to the other warpgroup (1.272 -> 1.216 ms at
+    // B32 H16 N2048 D64; the one-kernel backward got slower with the same split, 1.439 -> 1.466, and keeps 96).
+    constexpr bool kMoveRegs = DROP != 0 && MODE == 0 && !INLINE;
+    // The pool is what the CTA was launched with (96 per thread): a split that asks for more makes
+    // setmaxnreg.inc wait for ever (112 / 40 did: 62464 > 61440).
+    constexpr int kRegsElementwiseMoved = 104, kRegsOtherMoved = 64, kRegsLaunch = 96;
+    static_assert(128 * NWG * kRegsElementwiseMoved + kExtraThreads * kRegsOtherMoved <= (128 * NWG + kExtraThreads) * kRegsLaunch,
+                  "register split exceeds the launch allocation");
     if (warp >= kMmaWarp) {
-      // No setmaxnreg in this kernel: with the launch allocation of 96 registers per thread no role
-      // spills; moving registers from these warps to the elementwise ones (104 / 64, 104 / 40) made one
-      // side or the other spill and measured the same or slower.
+      if constexpr (kMoveRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOtherMoved));
       if (warp == kTmaWarp) {
         // ---------------------------------------------------------------- TMA producer
         if (elect_one()) {
@@ -603,6 +613,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
     } else {
         // ---------------------------------------------------------------- P / dS and epilogue
+        if constexpr (kMoveRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsElementwiseMoved));
         constexpr int NLD = CPT / 32;                          // 32-column TMEM loads per thread and phase
         const int wg = warp >> 2;                              // which CPT-column slice
         const int r = (warp & 3) * 32 + lane;                  // TMEM lane = row of T1/T2
