@@ -277,6 +277,51 @@ def test_keep_bit_buffer_is_not_asked_for_where_it_is_not_read(device):
     assert sized(q.float(), 0.5) == 0                                  # fp32 with dropout: CUDA-core kernels
 
 
+@pytest.mark.parametrize("dtype,D,p", [(torch.bfloat16, 128, 0.0), (torch.float16, 64, 0.2)])
+def test_a_step_replayed_from_a_cuda_graph_equals_the_eager_step(device, dtype, D, p):
+    """fa_b200_fwd / fa_b200_bwd (through the public entry and autograd) captured into a CUDA graph after
+    one eager call: the replay gives the eager results bit for bit, also with new values in the same
+    input buffers."""
+    B, N, H = 2, 384, 4
+    q, k, v = (_rand((B, N, H, D), dtype, s).to(device).requires_grad_(True) for s in (1, 2, 3))
+    g = _rand((B, N, H, D), dtype, 4).to(device)
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        o = fa.flash_attention_v100(q, k, v, causal=True, dropout_p=p, enable_multi_gpu=False,
+                                    dropout_stream=(11, 3) if p > 0 else None)
+        o.backward(g)
+        return o
+
+    def eager():
+        o = step()
+        return [t.detach().clone() for t in (o, q.grad, k.grad, v.grad)]
+
+    ref = eager()
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream(device).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o_static = step()
+    graph.replay()
+    torch.cuda.synchronize(device)
+    for a, b in zip(ref, (o_static, q.grad, k.grad, v.grad)):
+        assert torch.equal(a, b)
+    # new values in the captured buffers
+    with torch.no_grad():
+        q.copy_(_rand((B, N, H, D), dtype, 9).to(device))
+        g.copy_(_rand((B, N, H, D), dtype, 10).to(device))
+    graph.replay()
+    torch.cuda.synchronize(device)
+    got = [t.detach().clone() for t in (o_static, q.grad, k.grad, v.grad)]
+    for a, b in zip(eager(), got):
+        assert torch.equal(a, b)
+    fa.check_status(device) if hasattr(fa, "check_status") else None
+
+
 def test_strided_head_and_batch_views_are_consumed_in_place(device):
     B, N, H, D = 3, 160, 6, 64
     dtype = torch.bfloat16
