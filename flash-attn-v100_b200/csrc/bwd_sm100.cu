@@ -535,23 +535,39 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     mma_commit(&bars[Cfg::kWEmpty + ws]);                        // dO_i: dP^T(i) earlier, dV(i) last
                     if (more) { issue_t(tT1, sX_u, nxt_u, idesc_t1); mma_commit(&bars[Cfg::kT1Full]); }
                 } else if (more) {
-                    // dQ needs no second accumulator, so S is double-buffered in its columns: S(it+1)
-                    // goes to the buffer S(it-1) left, which phase A(it-1) finished reading before the
-                    // dS(it-1) hand-off this thread waited for in the previous step
+                    // dQ needs no second accumulator, and P never goes back to tensor memory here: S has one
+                    // buffer, free again as soon as the threads hold S(it) in registers, and dP / dS have
+                    // two (T2 and the columns a second accumulator would take).  S(it+1) and dP(it+1) are
+                    // both issued before this thread waits for dS(it), so the threads find their next
+                    // inputs ready; with one dP buffer, dP(it+1) could only follow dQ(it), and
+                    // dS -> dQ -> dP -> dS was the loop that set the step time.
+                    ok = mbar_wait(&bars[Cfg::kPReady], (uint32_t)it & 1u, abort_flag);     // S(it) is in registers
+                    if (!ok) break;
                     tc_fence_after_sync();
-                    issue_t(((it + 1) & 1) ? tAcc2 : tT1, sX_u, nxt_u, idesc_t1);
-                    // a barrier per buffer: its previous phase, S(it-1), was observed by every warp
-                    // before the dS(it-1) hand-off, so this completion cannot lap a waiter
-                    mma_commit(&bars[Cfg::kT1Full + ((it + 1) & 1)]);
+                    issue_t(tT1, sX_u, nxt_u, idesc_t1);
+                    mma_commit(&bars[Cfg::kT1Full]);
+                    ok = mbar_wait(&bars[kWReady + nws], nwph & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    // the buffer of step it+1 held dS(it-1), which dQ(it-1) read: issued before, in order
+                    issue_t(((it + 1) & 1) ? tAcc2 : tT2, sY_u, nxt_w, idesc_t2);
+                    mma_commit(&bars[((it + 1) & 1) ? Cfg::kT1Full + 1 : Cfg::kT2Full]);
+                    mma_commit(&bars[Cfg::kWEmpty + nws]);
                 }
-                ok = mbar_wait(&bars[Cfg::kDsHalf], (uint32_t)it & 1u, abort_flag);
+                // query-stationary: a barrier pair per dP / dS buffer (phase = uses of that buffer), which
+                // the threads cannot lap: dS(it+2) needs dP(it+2), issued after these waits
+                const int b_half = (!KS && (it & 1)) ? Cfg::kPHalf : Cfg::kDsHalf;
+                const int b_ready = (!KS && (it & 1)) ? Cfg::kDqRead : Cfg::kDsReady;
+                const uint32_t ds_par = KS ? ((uint32_t)it & 1u) : ((uint32_t)(it >> 1) & 1u);
+                const uint32_t tDs = (!KS && (it & 1)) ? tAcc2 : tT2;
+                ok = mbar_wait(&bars[b_half], ds_par, abort_flag);
                 if (!ok) break;
                 tc_fence_after_sync();
-                issue_acc_half(tAcc1, tT2, cur_u, it > 0, 0);                    // dK += dS^T Q  /  dQ += dS K
-                ok = mbar_wait(&bars[Cfg::kDsReady], (uint32_t)it & 1u, abort_flag);
+                issue_acc_half(tAcc1, tDs, cur_u, it > 0, 0);                    // dK += dS^T Q  /  dQ += dS K
+                ok = mbar_wait(&bars[b_ready], ds_par, abort_flag);
                 if (!ok) break;
                 tc_fence_after_sync();
-                issue_acc_half(tAcc1, tT2, cur_u, it > 0, 1);
+                issue_acc_half(tAcc1, tDs, cur_u, it > 0, 1);
                 mma_commit(&bars[Cfg::kUEmpty + us]);                            // last reader of U(it)
                 if (FUSED) {
                     // dQ tile of this step = dS K_j: A is the dS^T tile the threads left in shared memory,
@@ -572,13 +588,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         tc_fence_after_sync();
                     }
                 }
-                if (more) {
+                if (KS && more) {
                     ok = mbar_wait(&bars[kWReady + nws], nwph & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after_sync();
                     issue_t(tT2, sY_u, nxt_w, idesc_t2);
                     mma_commit(&bars[Cfg::kT2Full]);
-                    if (!KS) mma_commit(&bars[Cfg::kWEmpty + nws]);
                 }
                 us = nus; uph = nuph; ws = nws; wph = nwph;
             }
@@ -912,8 +927,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             // written with 16-byte stores from this layout (with the fragment layout above it measured
             // 5-10 % slower)
             // ---- phase A: P from T1
-            ok = (KS) ? mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag)
-                             : mbar_wait(&bars[Cfg::kT1Full + (it & 1)], (uint32_t)(it >> 1) & 1u, abort_flag);
+            ok = mbar_wait(&bars[Cfg::kT1Full], (uint32_t)it & 1u, abort_flag);
             if (KS && ok) ok = mbar_wait(&bars[Cfg::kVFull + (it & 1)], (uint32_t)(it >> 1) & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -921,10 +935,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             uint32_t pr[NLD][32];      // P of my columns (fp32 bits), kept for phase B
 #define PF(c) __uint_as_float(pr[(c) >> 5][(c) & 31])
 #define PSET(c, x) pr[(c) >> 5][(c) & 31] = __float_as_uint(x)
-            const uint32_t tS = (MODE == 1 && (it & 1)) ? tAcc2 : tT1;      // MODE 1 double-buffers S
 #pragma unroll
-            for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tS + lane_off + cb + q * 32, pr[q]);
+            for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tT1 + lane_off + cb + q * 32, pr[q]);
             tmem_wait_ld();
+            if (!KS) {
+                // query-stationary: P stays in registers, so S's columns are free for S(it+1) from here on
+                tc_fence_before_sync();
+                mbar_arrive_warp(&bars[Cfg::kPReady]);
+            }
             const uint64_t sc2 = f2_pack(a.scale_log2, a.scale_log2);
             if (KS) {
                 // P = 2^(S*c - lse): the staged vector holds -lse*log2(e), two columns per 64-bit word.
@@ -1005,8 +1023,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         if (c >= seen) PSET(c, 0.f);
                 }
             }
-            tc_fence_before_sync();
-            mbar_arrive_warp(&bars[Cfg::kPReady]);
+            if (KS) {
+                tc_fence_before_sync();
+                mbar_arrive_warp(&bars[Cfg::kPReady]);
+            }
 
             if (FUSED && it > 0) {
                 // dQ of the previous step: its MMAs ran while phase A above did
@@ -1015,14 +1035,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
 
             // ---- phase B: dS from T2
-            ok = mbar_wait(&bars[Cfg::kT2Full], (uint32_t)it & 1u, abort_flag);
+            // query-stationary: dP / dS alternate between two buffers, each with its own barriers
+            const bool odd_buf = !KS && (it & 1);
+            const uint32_t tD = odd_buf ? tAcc2 : tT2;
+            const int b_half = odd_buf ? Cfg::kPHalf : Cfg::kDsHalf, b_ready = odd_buf ? Cfg::kDqRead : Cfg::kDsReady;
+            ok = KS ? mbar_wait(&bars[Cfg::kT2Full], (uint32_t)it & 1u, abort_flag)
+                    : mbar_wait(&bars[odd_buf ? Cfg::kT1Full + 1 : Cfg::kT2Full], (uint32_t)(it >> 1) & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
             {
                 uint32_t dr[NLD][32];
 #pragma unroll
-                for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tT2 + lane_off + cb + q * 32, dr[q]);
+                for (int q = 0; q < NLD; ++q) tmem_ld_32x32(tD + lane_off + cb + q * 32, dr[q]);
                 tmem_wait_ld();
                 // dS = P o (dP o Z - delta); the staged vector holds -delta.  Two halves, as in phase A:
                 // the first is stored and handed over while the second is computed.
@@ -1064,9 +1089,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     if (hf == 1) {
                         tmem_wait_st();
                         tc_fence_before_sync();
-                        mbar_arrive_warp(&bars[Cfg::kDsHalf]);
+                        mbar_arrive_warp(&bars[b_half]);
                     }
-                    tmem_st_32x8(tT2 + lane_off + cb + hf * (CPT / 4), pk);
+                    tmem_st_32x8(tD + lane_off + cb + hf * (CPT / 4), pk);
                     if (FUSED) {
                         // the same dS^T values as a shared-memory tile [key row][query], 64-query boxes with
                         // the 128-byte swizzle: the A operand (MN-major) of the dQ MMA.  The previous
@@ -1085,7 +1110,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #undef PF
 #undef PSET
             tc_fence_before_sync();
-            mbar_arrive_warp(&bars[Cfg::kDsReady]);
+            mbar_arrive_warp(&bars[b_ready]);
             }
             if (KS) mbar_arrive_warp(&bars[Cfg::kVEmpty + (it & 1)]);      // this step's lse / delta rows are read
             prev_tile = strm_tile; prev_head = head_q;
