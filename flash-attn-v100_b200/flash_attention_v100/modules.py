@@ -8,7 +8,11 @@ the kernels underneath:
 
 * the projections' outputs are handed to the attention op as (B, N, H, D)
   views, no transposes or copies;
-* masks become the smallest bias that expresses them - a key-padding mask is a
+* a boolean key-padding mask on its own (no attn_mask, no causal mask) costs no bias at all:
+  attention does not depend on the order of the keys, so the kept keys of every batch entry are
+  moved to the front (one gather of K and V, undone for dK and dV by autograd) and the call runs
+  on the tensor-core kernels with per-batch key counts;
+* other masks become the smallest bias that expresses them - a key-padding mask is a
   (B, 1, 1, Nk) bias, a 2-D attn_mask a (1, 1, Nq, Nk) one - instead of a dense
   (B, H, Nq, Nk) tensor (reference :228-250); boolean masks hide where True,
   float masks are added to the scores;
@@ -57,6 +61,23 @@ def masks_to_bias(attn_mask: Optional[torch.Tensor], key_padding_mask: Optional[
     return bias
 
 
+def compact_keys(k: torch.Tensor, v: torch.Tensor, key_padding_mask: torch.Tensor
+                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Kept keys first: (k', v', counts) such that attention over the first counts[b] keys of k'[b], v'[b]
+    equals attention over k[b], v[b] with the keys where key_padding_mask[b] is True hidden.
+
+    k, v: (B, Nk, H, D); key_padding_mask: (B, Nk) bool.  The kept keys keep their order (a stable sort
+    of the mask); nothing is read back to the host.  An entry whose keys are all hidden keeps a count
+    of 1 (it attends to its first key) instead of producing the NaN a softmax over nothing gives."""
+    if key_padding_mask.dtype != torch.bool or key_padding_mask.dim() != 2 or \
+            tuple(key_padding_mask.shape) != (k.shape[0], k.shape[1]):
+        raise ValueError("key_padding_mask must be a boolean (B, Nk) tensor")
+    order = torch.argsort(key_padding_mask.to(torch.uint8), dim=1, stable=True)
+    counts = (~key_padding_mask).sum(dim=1).clamp_(min=1).to(torch.int32)
+    index = order.view(order.shape[0], order.shape[1], 1, 1).expand(-1, -1, k.shape[2], k.shape[3])
+    return k.gather(1, index), v.gather(1, index), counts
+
+
 class EnhancedMultiHeadAttention(nn.Module):
     def __init__(self, embed_dim: int, num_heads: int, dropout: float = 0.0, bias: bool = True,
                  batch_first: bool = True, optimization_strategy: str = "balanced",
@@ -94,8 +115,10 @@ class EnhancedMultiHeadAttention(nn.Module):
                 key_lengths: Optional[torch.Tensor] = None
                 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """Reference signature plus key_lengths (B,): for right-padded batches, the number of real keys
-        of each batch entry.  Unlike a key_padding_mask (which becomes a bias and runs on the CUDA-core
-        kernels) it keeps the call on the tensor-core kernels and skips the padding's key blocks."""
+        of each batch entry; the call stays on the tensor-core kernels and skips the padding's key
+        blocks.  A boolean key_padding_mask alone (no attn_mask, is_causal False) gets there too, by moving
+        the kept keys to the front (compact_keys); combined with other masks, or as a float mask, it
+        becomes a bias and runs on the CUDA-core kernels."""
         if not self.batch_first:
             query = query.transpose(0, 1)
             key = key.transpose(0, 1) if key is not None else None
@@ -108,6 +131,12 @@ class EnhancedMultiHeadAttention(nn.Module):
         q = self.q_proj(query).view(batch, seq_q, self.num_heads, self.head_dim)
         k = self.k_proj(key).view(batch, seq_k, self.num_heads, self.head_dim)
         v = self.v_proj(value).view(batch, seq_k, self.num_heads, self.head_dim)
+        if key_padding_mask is not None and key_padding_mask.dtype == torch.bool and attn_mask is None \
+                and not is_causal and key_lengths is None:
+            if tuple(key_padding_mask.shape) != (batch, seq_k):
+                raise ValueError(f"key_padding_mask shape {tuple(key_padding_mask.shape)}, expected {(batch, seq_k)}")
+            k, v, key_lengths = compact_keys(k, v, key_padding_mask)
+            key_padding_mask = None
         bias = masks_to_bias(attn_mask, key_padding_mask, batch, seq_q, seq_k)
         if need_weights:
             warnings.warn("need_weights=True: attention weights are never materialised by these kernels; "
@@ -129,4 +158,4 @@ class EnhancedMultiHeadAttention(nn.Module):
         return {"forward_count": self.forward_count}
 
 
-__all__ = ["EnhancedMultiHeadAttention", "masks_to_bias"]
+__all__ = ["EnhancedMultiHeadAttention", "masks_to_bias", "compact_keys"]
