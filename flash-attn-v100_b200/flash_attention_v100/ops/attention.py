@@ -170,6 +170,11 @@ def saves_output_residual(dtype: torch.dtype) -> bool:
     return dtype == torch.bfloat16
 
 
+# The keep bits of a call take Nq * Nk / 4 bytes per (batch, head) column (34 GB at B1 H32 N65536): beyond
+# this size a buffer the caller did not supply is not allocated and the kernels draw their bits themselves.
+KEEP_BITS_MAX_BYTES = 4 << 30
+
+
 def _dropout_bits_operand(p, keep_bits, forward_only=False):
     """Point the call at a buffer for its dropout keep bits.  `keep_bits`: None (the kernels draw their
     bits themselves), "new" (allocate; returned for a later call to reuse), or (tensor, ready) with a
@@ -180,6 +185,8 @@ def _dropout_bits_operand(p, keep_bits, forward_only=False):
     if nbytes == 0:
         return None                      # no dropout, or the CUDA-core kernels serve the call
     if isinstance(keep_bits, str):
+        if nbytes > KEEP_BITS_MAX_BYTES:
+            return None
         # a forward that no backward follows needs the query-major half only
         buf, ready = torch.empty(nbytes // 2 if forward_only else nbytes, dtype=torch.uint8, device="cuda:%d" % p.device), False
     else:

@@ -263,6 +263,17 @@ def test_keep_bit_buffer_gives_the_results_of_the_inline_draw(device, dtype, D, 
                     assert torch.equal(a, c), (variant, name, "own bits")
 
 
+def test_keep_bit_buffer_is_not_allocated_beyond_the_size_cap(device, monkeypatch):
+    from flash_attention_v100.ops import attention as ops
+    q = _rand((1, 256, 2, 64), torch.float16, 1).to(device)
+    monkeypatch.setattr(ops, "KEEP_BITS_MAX_BYTES", 1024)          # this call's bits take 2 * 256 * 256 / 4 bytes
+    o, lse, bits = launch_forward(q, q, q, 0.125, True, 0.5, 5, 6, keep_bits="new", forward_only=False)
+    assert bits is None                                            # the kernel drew its own bits
+    monkeypatch.setattr(ops, "KEEP_BITS_MAX_BYTES", 4 << 30)
+    o2, lse2, bits2 = launch_forward(q, q, q, 0.125, True, 0.5, 5, 6, keep_bits="new", forward_only=False)
+    assert bits2 is not None and torch.equal(o, o2) and torch.equal(lse, lse2)
+
+
 def test_keep_bit_buffer_is_not_asked_for_where_it_is_not_read(device):
     lib = _cabi.load()
     from flash_attention_v100.ops.attention import _base_params
