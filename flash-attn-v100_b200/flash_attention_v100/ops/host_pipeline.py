@@ -128,7 +128,9 @@ class HostAttentionStep:
             if self.dropout_p > 0.0:
                 cols = max(((b1 - b0) * (h1 - h0) for b0, b1, h0, h1 in self.chunks), default=0)
                 pad = lambda n: -(-n // 128) * 128
-                self._bits = torch.empty(max(1, cols * pad(Nq) * pad(Nk) // 4), dtype=torch.uint8, device=dev)
+                nbits = cols * pad(Nq) * pad(Nk) // 4
+                if 0 < nbits <= _ops.KEEP_BITS_MAX_BYTES:          # beyond the cap the kernels draw their own bits
+                    self._bits = torch.empty(nbits, dtype=torch.uint8, device=dev)
             self._s_in, self._s_run, self._s_out = (torch.cuda.Stream(dev) for _ in range(3))
             n = len(self.chunks)
             ev = lambda: [torch.cuda.Event() for _ in range(n)]
