@@ -42,7 +42,8 @@
 //
 //   warps 0-15       four elementwise warpgroups; a thread owns one TMEM lane (row)
 //                    and warpgroup g owns columns [32g, 32g+32) of T1/T2
-//   warp 16          MMA issuer; order  T1(0) T2(0) | ACC2(i) T1(i+1) ACC1(i) T2(i+1) ...
+//   warp 16          MMA issuer; order  T1(0) T2(0) | ACC2(i) T1(i+1) ACC1(i) T2(i+1) ...  (MODE 0, 2)
+//                                       T1(0) T2(0) | T1(i+1) T2(i+1) ACC1(i) ...          (MODE 1)
 //   warp 17          TMA producer: U and W tiles into rings of their own (U is read again by the
 //                    step's last MMA, so it gets three stages where shared memory allows and its
 //                    next load overlaps a whole step; W gets two), and in the key-stationary
@@ -51,8 +52,10 @@
 //                    f16 x f16, with P and dS rounded to fp16; see "number formats" below); else idle
 //
 // TMEM columns: T1 [0,128)  T2 [128,256)  ACC1 [256,256+D)  ACC2 [384,384+D).
-// MODE 1 has no ACC2 and uses [384,512) as a second S buffer: S(i+1) is computed
-// while the threads still work on S(i).  MODE 2 (D = 64) puts the dQ tile at [448,512).
+// MODE 1 has no ACC2 and never writes P back (only dS is an MMA operand there): S has the one buffer
+// T1, free again once the threads hold S(i) in registers, and dP / dS alternate between T2 and
+// [384,512), so that S(i+1) and dP(i+1) are both computed while the threads work on step i.
+// MODE 2 (D = 64) puts the dQ tile at [448,512).
 // Every mbarrier wait is bounded; see sm100_ptx.cuh.
 #include "fa_common.cuh"
 #include "sm100_ptx.cuh"
