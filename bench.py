@@ -318,7 +318,10 @@ def run_ours(args, whole):
                 eager_step()
             torch.cuda.current_stream(device).wait_stream(side)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            # thread_local: a CUDA call by another thread of the process (NCCL's watchdog polls events)
+            # must not invalidate the capture; the step's own launches, the autograd thread's
+            # included, go to the capturing stream either way
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 eager_step()
             for _ in range(3):
                 graph.replay()
