@@ -820,6 +820,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                 for (int jj = 0; jj < 2; ++jj) {
                     const int j = 2 * hf + jj;
+                    if (hf == 1 && jj == 0) {
+                        // the first half's stores were issued a quarter-phase ago: hand it over now, so that
+                        // its MMAs are done when the second half arrives
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        mbar_arrive_warp(&bars[Cfg::kPHalf]);
+                    }
                     uint64_t L = *reinterpret_cast<const uint64_t*>(lse_s + cb + 8 * j + 2 * lq);
                     if (ROWFORM) L = f2_add(L, ladd2);
 #pragma unroll
@@ -866,11 +873,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             }
                             pk[h][2 * jj + k] = pack2<false>(z0, z1);
                         }
-                if (hf == 1) {
-                    tmem_wait_st();                                 // the first half's stores were issued a half-phase ago
-                    tc_fence_before_sync();
-                    mbar_arrive_warp(&bars[Cfg::kPHalf]);
-                }
                 tmem_st_16x128b_x2(tT1 + t_lo + hf * 8, pk[0]);
                 tmem_st_16x128b_x2(tT1 + t_hi + hf * 8, pk[1]);
             }
@@ -893,6 +895,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                     for (int jj = 0; jj < 2; ++jj) {
                         const int j = 2 * hf + jj;
+                        if (hf == 1 && jj == 0) {
+                            tmem_wait_st();                        // first half: stored a quarter-phase ago
+                            tc_fence_before_sync();
+                            mbar_arrive_warp(&bars[Cfg::kDsHalf]);
+                        }
                         const uint64_t nd = f2_mul(*reinterpret_cast<const uint64_t*>(del_s + cb + 8 * j + 2 * lq), ndm2);
 #pragma unroll
                         for (int h = 0; h < 2; ++h)
@@ -911,11 +918,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                                 f2_unpack(f2_mul(f2_pack(__uint_as_float(pf[h][i0]), __uint_as_float(pf[h][i0 + 1])), tt), d0, d1);
                                 pk[h][2 * jj + k] = pack2<false>(d0, d1);
                             }
-                    }
-                    if (hf == 1) {
-                        tmem_wait_st();
-                        tc_fence_before_sync();
-                        mbar_arrive_warp(&bars[Cfg::kDsHalf]);
                     }
                     tmem_st_16x128b_x2(tT2 + t_lo + hf * 8, pk[0]);
                     tmem_st_16x128b_x2(tT2 + t_hi + hf * 8, pk[1]);
@@ -956,6 +958,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 const bool diag = a.causal && strm_tile * kTile + a.shift < tile * kTile + kTile - 1;
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
+                    if (hf == 1) {
+                        // hand the first half over before the second is computed: its MMAs are then done
+                        // when the second half arrives (the chain MMA -> threads -> MMA feels every cycle)
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        mbar_arrive_warp(&bars[Cfg::kPHalf]);
+                    }
 #pragma unroll
                     for (int c4 = hf * (CPT / 8); c4 < (hf + 1) * (CPT / 8); ++c4) {
                         ulonglong2 L = l2[c4];
@@ -988,12 +997,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             if (!((kb[(c + 1) >> 5] >> ((c + 1) & 31)) & 1u)) x1 = 0.f;
                         }
                         pk[e] = pack2<false>(x0, x1);
-                    }
-                    if (hf == 1) {
-                        // the first half's store was issued a half-phase ago
-                        tmem_wait_st();
-                        tc_fence_before_sync();
-                        mbar_arrive_warp(&bars[Cfg::kPHalf]);
                     }
                     tmem_st_32x8(tT1 + lane_off + cb + hf * (CPT / 4), pk);
                 }
@@ -1059,6 +1062,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     uint32_t pk[CPT / 4];
+                    if (hf == 1) {
+                        tmem_wait_st();                            // the first half, stored just now
+                        tc_fence_before_sync();
+                        mbar_arrive_warp(&bars[b_half]);
+                    }
 #pragma unroll
                     for (int c4 = hf * (CPT / 8); c4 < (hf + 1) * (CPT / 8); ++c4) {
                         ulonglong2 nd;
@@ -1088,11 +1096,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         f2_unpack(f2_mul(f2_pack(PF(c + 2), PF(c + 3)), tb), d2v, d3);
                         pk[(c4 - hf * (CPT / 8)) * 2 + 0] = pack2<false>(d0, d1);
                         pk[(c4 - hf * (CPT / 8)) * 2 + 1] = pack2<false>(d2v, d3);
-                    }
-                    if (hf == 1) {
-                        tmem_wait_st();
-                        tc_fence_before_sync();
-                        mbar_arrive_warp(&bars[b_half]);
                     }
                     tmem_st_32x8(tD + lane_off + cb + hf * (CPT / 4), pk);
                     if (FUSED) {
