@@ -820,9 +820,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                 for (int jj = 0; jj < 2; ++jj) {
                     const int j = 2 * hf + jj;
-                    if (hf == 1 && jj == 0) {
-                        // the first half's stores were issued a quarter-phase ago: hand it over now, so that
-                        // its MMAs are done when the second half arrives
+                    if (!drop && hf == 1 && jj == 0) {
+                        // hand the first half over before the second is computed, so that its MMAs are done
+                        // when the second half arrives (dK/dV 0.971 -> 0.933 ms at B4 N4096 H32 D128: the chain
+                        // MMA -> threads -> MMA feels every cycle).  With dropout the threads are the slower
+                        // side and the wait for the stores just issued costs more than it gains (1.24 against
+                        // 1.22 ms at B32 N2048 H16 D64): there the hand-off stays behind the second half's math.
                         tmem_wait_st();
                         tc_fence_before_sync();
                         mbar_arrive_warp(&bars[Cfg::kPHalf]);
@@ -873,6 +876,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             }
                             pk[h][2 * jj + k] = pack2<false>(z0, z1);
                         }
+                if (drop && hf == 1) {
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive_warp(&bars[Cfg::kPHalf]);
+                }
                 tmem_st_16x128b_x2(tT1 + t_lo + hf * 8, pk[0]);
                 tmem_st_16x128b_x2(tT1 + t_hi + hf * 8, pk[1]);
             }
@@ -895,8 +903,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                     for (int jj = 0; jj < 2; ++jj) {
                         const int j = 2 * hf + jj;
-                        if (hf == 1 && jj == 0) {
-                            tmem_wait_st();                        // first half: stored a quarter-phase ago
+                        if (!drop && hf == 1 && jj == 0) {
+                            tmem_wait_st();                        // the first half, as for P above
                             tc_fence_before_sync();
                             mbar_arrive_warp(&bars[Cfg::kDsHalf]);
                         }
@@ -918,6 +926,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                                 f2_unpack(f2_mul(f2_pack(__uint_as_float(pf[h][i0]), __uint_as_float(pf[h][i0 + 1])), tt), d0, d1);
                                 pk[h][2 * jj + k] = pack2<false>(d0, d1);
                             }
+                    }
+                    if (drop && hf == 1) {
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        mbar_arrive_warp(&bars[Cfg::kDsHalf]);
                     }
                     tmem_st_16x128b_x2(tT2 + t_lo + hf * 8, pk[0]);
                     tmem_st_16x128b_x2(tT2 + t_hi + hf * 8, pk[1]);
