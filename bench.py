@@ -122,7 +122,7 @@ def measured_peak():
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from an ncu capture of these kernels at batch 1
 # of the default workload (32 (batch, head) columns of N4096 D128 bf16 causal), scaled by the number of
 # columns: traffic is proportional to it, every column being independent.
-NCU_DRAM_BYTES_PER_BATCH = {"fwd": 127.2e6, "bwd_preprocess": 213.8e6, "bwd_dkdv": 203.3e6, "bwd_dq": 158.2e6}
+NCU_DRAM_BYTES_PER_BATCH = {"fwd": 127.6e6, "bwd_preprocess": 214.8e6, "bwd_dkdv": 202.2e6, "bwd_dq": 157.9e6}
 
 
 def ncu_traffic(kernel: str, w):
